@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark of the affine-Q4 projection path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation
+    python bench.py --impl reference ...                      # the reference arithmetic on the host CPU
+
+Workload (config 4 of BASELINE.json; it repeats the grouped decode set of config 1 sixty-four
+times): a synthetic 64-layer projection stack, M=1 decode, plus an lm_head of 248320 rows -- 13.75 GB
+of packed Q4 weights generated in HBM from a seed. One step is one token: per layer one grouped launch
+of nine K=5120 projections sharing one activation, SwiGLU, the K=17408 down projection, a weightless
+RMS-norm; then lm_head and argmax. Half of the projections start 2 bytes off a 16-byte boundary.
+With N GPUs the output rows of every projection are sharded N ways and the outputs that feed the next
+projection are all-gathered (NCCL) -- strong scaling.
+
+The metric is weight-stream bandwidth: algorithmic bytes of one token (packed weights + scales +
+biases) x steps / time, aggregated over all GPUs. tokens/s is the same number divided by 13.75 GB.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "q4_gemv_hbm_gbs"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+SEED = 20260
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_sample(oracle, threads: int, budget_s: float):
+    """The oracle's kernel-form arithmetic on the host cores over one gate projection (17408 x 5120),
+    repeated until about `budget_s` seconds of CPU work have been done."""
+    n, k = 17408, 5120
+    w, s, b = oracle.synth_q4(SEED, 7, n, k)
+    x = oracle.bf16_to_f32(oracle.synth_bf16(SEED, 10_000, k))
+    nbytes = n * (k // 2) + 2 * n * (k // 64) * 2
+    oracle.matmul_factored_f32(x, w, s, b, n, threads=threads)  # warm
+    t0 = time.perf_counter()
+    passes = 0
+    while True:
+        oracle.matmul_factored_f32(x, w, s, b, n, threads=threads)
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or passes >= 10_000:
+            break
+    return nbytes * passes / dt / 1e9, f"gate projection 17408x5120 ({nbytes / 1e6:.1f} MB), {passes} passes, {dt:.1f} s", dt / passes
+
+
+def run_reference(args) -> int:
+    """The reference's arithmetic for this path on the host CPU (the reference itself needs Metal and a
+    Rust toolchain, so the CPU oracle -- a restatement of its kernel, oracle/q4_oracle.c -- is timed)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import q4_oracle as oracle
+
+    threads = os.cpu_count() or 1
+    per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    values, sample, ms = [], "", []
+    for i in range(args.warmup + args.steps):
+        v, sample, per_pass = cpu_sample(oracle, threads, per_step_budget)
+        if i >= args.warmup:
+            values.append(v)
+            ms.append(per_step_budget * 1e3)
+    value = sum(values) / len(values)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sum(ms) / len(ms), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config4-full-stack-decode (CPU: bounded sample of its weight stream)",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_ours(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    from qwen38_metal_b200 import build, capi
+    from qwen38_metal_b200.runtime import CudaRuntime
+    from qwen38_metal_b200.stack import SyntheticStack, token_bytes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    build.build()
+    rt = CudaRuntime(local_rank)
+    stack = SyntheticStack(rt, layers=args.layers, rank=rank, world=world, seed=SEED, device=local_rank)
+    total_bytes = token_bytes(layers=args.layers)
+
+    gather = None
+    if world > 1:
+        def gather(tensor, proj):
+            rows = proj.total_rows // world
+            if rows * world != proj.total_rows:
+                raise SystemExit("row counts must divide the GPU count in this benchmark")
+            dist.all_gather_into_tensor(tensor[:proj.total_rows], tensor[proj.row0:proj.row0 + rows])
+
+    stream = torch.cuda.Stream()
+    host_x = torch.empty(stack.hidden, dtype=torch.bfloat16).pin_memory()
+    host_tok = torch.empty(2, dtype=torch.int32).pin_memory()
+    with torch.cuda.stream(stream):
+        stack.reset_input(stream.cuda_stream)
+        stack.decode_token(stream.cuda_stream, gather)  # sizes every scratch pool before capture
+        stream.synchronize()
+        host_x.copy_(stack.x)  # any bf16 vector will do as the per-step input
+        stream.synchronize()
+        launches_before = rt.launch_count()
+        pairs = torch.zeros(world, 2, dtype=torch.float32, device=stack.device)
+
+        def lm_head_pick():
+            """Each rank holds the best token of its vocabulary slice; every rank gathers the (value, id)
+            pairs and keeps the greatest value, ties to the lowest id."""
+            if world == 1:
+                return
+            pairs[rank, 0:1].copy_(stack.best)
+            pairs[rank, 1:2].copy_(stack.token.to(torch.float32))
+            dist.all_gather_into_tensor(pairs.view(-1), pairs[rank])
+            top = pairs[:, 0].max()
+            ids = torch.where(pairs[:, 0] == top, pairs[:, 1], torch.full_like(pairs[:, 1], 3.0e38))
+            stack.token.copy_(ids.min().to(torch.int32).reshape(1))
+
+        lm_head_pick()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            stack.decode_token(stream.cuda_stream, gather)
+            lm_head_pick()
+        launches_per_token = rt.launch_count() - launches_before
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: K graph replays --------------------------------------------
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        # ---- end to end: input activation from pinned host memory, token back, every step -------
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(stream)
+        for _ in range(args.steps):
+            stack.x.copy_(host_x, non_blocking=True)
+            graph.replay()
+            host_tok[:1].copy_(stack.token, non_blocking=True)
+            stream.synchronize()
+        e3.record(stream)
+        barrier()
+        ms_e2e = e2.elapsed_time(e3)
+        clocks = sampler.stop()
+        # ---- per-kernel timing of the projection kernel (no graph: events around each launch) -----
+        rt.profile_begin()
+        stack.decode_token(stream.cuda_stream, gather)
+        stream.synchronize()
+        prof = rt.profile_end()
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = t.tolist()
+    value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e_value = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    peak, peak_source = measured_peaks()
+    achieved = prof["bytes"] / (prof["ms"] * 1e-3) / 1e9 if prof["ms"] > 0 else 0.0
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x u4 -> f32", "data": "synthetic",
+            "config": {"workload": "config4-full-stack-decode: 64 x config1 grouped decode set + lm_head, M=1",
+                       "layers": args.layers, "hidden": stack.hidden, "intermediate": stack.inter,
+                       "vocab": stack.vocab, "bytes_per_token": total_bytes, "seed": SEED,
+                       "row_sharding": f"{world}-way", "l2": "13.75 GB streamed per step, far larger than L2",
+                       "misaligned": "every other projection starts 2 bytes off a 16-byte boundary"},
+            "tokens_per_s": args.steps / (ms * 1e-3),
+            "frac_of_8TBs": value / (NOMINAL_HBM_GBS * world),
+            "frac_of_measured_hbm": value / (peak * world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": stack.hidden * 2,
+                    "d2h_bytes_per_step": 4, "tokens_per_s": args.steps / (ms_e2e * 1e-3),
+                    "what": "pinned input activation -> HBM, captured token graph, token id -> host, sync per step"},
+            "gpu_launches": launches_per_token * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "q4_gemv_kernel", "achieved": achieved, "peak": peak,
+                         "peak_source": peak_source, "unit": UNIT, "frac": achieved / peak if peak else None,
+                         "frac_of_8TBs": achieved / NOMINAL_HBM_GBS, "launches": prof["launches"],
+                         "avg_launch_us": prof["ms"] * 1e3 / max(1, prof["launches"]),
+                         "bytes_per_launch": prof["bytes"] / max(1, prof["launches"]), "traffic": None},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import q4_oracle as oracle
+
+            threads = os.cpu_count() or 1
+            v, sample, _ = cpu_sample(oracle, threads, args.cpu_seconds)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

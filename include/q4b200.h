@@ -1,0 +1,179 @@
+/*
+ * q4b200 -- C ABI of the B200 (sm_100a) affine-Q4 projection library.
+ *
+ * This is the boundary a host program binds in place of the reference's Metal runtime
+ * (Fuxx-1/qwen38-metal: src/metal.rs, the Q4 part of src/metal_runtime.rs, src/mps.rs).
+ * Each entry point names the reference interface it replaces; paths are relative to the
+ * reference repository root.
+ *
+ * Conventions
+ *   - every function returns a q4b_status; outputs are untouched on error; nothing aborts
+ *     and no exception crosses the boundary;
+ *   - q4b_last_error() gives the message of the calling thread's last failed call;
+ *   - host-pointer entry points are synchronous: results are in the caller's buffers on
+ *     return. They serialise on an internal lock, as the reference's pooled entry points do
+ *     (Mutex<Q4ActivationPool>, src/metal_runtime.rs:3627-3630), so one runtime may be
+ *     shared by several host threads;
+ *   - `_device` twins take device pointers and a cudaStream_t (passed as void*), enqueue
+ *     work and return without synchronising. They use the runtime's scratch buffers: calls
+ *     on one runtime must be ordered on the device (one stream, or events). Scratch grows on
+ *     first use of a larger shape, so run a shape once before capturing it in a CUDA graph;
+ *   - weights are uploaded byte for byte (no expansion, no repacking, file offsets kept), so
+ *     a tensor that is misaligned in its safetensors shard is misaligned in HBM; the kernels
+ *     take any byte alignment.
+ *
+ * Data format (MLX affine Q4, group 64): weights U32 [N][K/8], eight 4-bit values per
+ * little-endian word, value i at bits [4i,4i+4); scales and biases BF16 [N][K/64];
+ * w = scale*q + bias (src/native.rs:5417-5471, shaders/qwen38.metal:815-817).
+ */
+#ifndef Q4B200_H
+#define Q4B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Mirrors MetalRuntimeError, src/metal_runtime.rs:9218-9257, plus CUDA-side codes. */
+typedef enum q4b_status {
+    Q4B_OK = 0,
+    Q4B_NO_DEVICE = 1,              /* NoDevice */
+    Q4B_EMPTY_BUFFER = 2,           /* EmptyBuffer */
+    Q4B_POOL_POISONED = 3,          /* ActivationPoolPoisoned */
+    Q4B_EMPTY_DIMENSION = 4,        /* EmptyDimension */
+    Q4B_INPUT_NOT_GROUPED = 5,      /* InputNotGrouped{input_elements, group_size} */
+    Q4B_WRONG_LENGTH = 6,           /* WrongLength{name, actual, expected} */
+    Q4B_MISSING_SHARD = 7,          /* MissingMappedShard(index) */
+    Q4B_INVALID_BUFFER_OFFSET = 8,  /* InvalidBufferOffset */
+    Q4B_TENSOR_OUT_OF_RANGE = 9,    /* MappedTensorOutOfRange */
+    Q4B_DIMENSION_OVERFLOW = 10,    /* DimensionOverflow(name) */
+    Q4B_COMMAND_FAILED = 11,        /* CommandFailed: a kernel or copy reported an error */
+    Q4B_CUDA_ERROR = 12,            /* Library/Function/Pipeline analogue: CUDA call failed */
+    Q4B_INVALID_ARGUMENT = 13,      /* null pointer, unknown dtype, bad handle */
+    Q4B_UNSUPPORTED = 14            /* shape outside what this build handles */
+} q4b_status;
+
+typedef enum q4b_dtype {
+    Q4B_F32 = 0,  /* the reference's activation type (device const float*, shaders/qwen38.metal:214) */
+    Q4B_BF16 = 1  /* benchmarked activation type */
+} q4b_dtype;
+
+typedef struct q4b_runtime q4b_runtime; /* replaces MetalRuntime, src/metal_runtime.rs:79-153 */
+
+/*
+ * One projection: three (shard, byte offset) pairs and the row count.
+ * Replaces MappedQ4AffineJob, src/metal_runtime.rs:155-192. `aligned` is the caller's hint
+ * (weights 4-byte, scales/biases 2-byte aligned in the host mapping, src/native.rs:355-369);
+ * the library derives the load path from device addresses and ignores the hint.
+ */
+typedef struct q4b_job {
+    uint32_t weight_shard;
+    uint32_t scale_shard;
+    uint32_t bias_shard;
+    int32_t aligned;
+    uint64_t weight_offset;
+    uint64_t scale_offset;
+    uint64_t bias_offset;
+    uint64_t output_rows;
+} q4b_job;
+
+/* ---- runtime ---- */
+
+/* MetalRuntime::new, src/metal_runtime.rs:642-927. Options are latched from the environment
+ * once, here (the reference reads QWEN38_* variables, :916-925): Q4B_FORCE_VARIANT. */
+int q4b_runtime_create(int device_ordinal, q4b_runtime **out);
+void q4b_runtime_destroy(q4b_runtime *rt);
+/* Display impl of MetalRuntimeError, src/metal_runtime.rs:9259-9324 */
+const char *q4b_last_error(void);
+const char *q4b_status_name(int status);
+int q4b_device_info(q4b_runtime *rt, int *sm_count, uint64_t *total_bytes, char *name, uint32_t name_len);
+
+/* ---- weight shards ---- */
+
+/* MetalRuntime::map_weight_store, src/metal_runtime.rs:955-982: one device allocation per
+ * shard, bytes copied verbatim. An empty shard is Q4B_EMPTY_BUFFER (:964-966). */
+int q4b_shard_upload(q4b_runtime *rt, const void *host_bytes, uint64_t bytes, uint32_t *shard_id);
+/* Uninitialised device shard (for tensors generated in place). */
+int q4b_shard_alloc(q4b_runtime *rt, uint64_t bytes, uint32_t *shard_id);
+/* Copy into an existing shard (partial uploads, row slices). */
+int q4b_shard_write(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, const void *host_bytes, uint64_t bytes);
+int q4b_shard_read(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, void *host_bytes, uint64_t bytes);
+/* MappedWeightBuffers::shard_count, src/metal_runtime.rs:624-626 */
+int q4b_shard_count(q4b_runtime *rt, uint32_t *count);
+int q4b_shard_info(q4b_runtime *rt, uint32_t shard_id, void **device_ptr, uint64_t *bytes);
+/* MappedWeightBuffers::offset_is_aligned, src/metal_runtime.rs:628-638, on the device address.
+ * *aligned is 0 or 1. */
+int q4b_offset_is_aligned(q4b_runtime *rt, uint32_t shard_id, uint64_t byte_offset, uint64_t alignment,
+                          int *aligned);
+
+/* ---- projections, host buffers (synchronous) ---- */
+
+/* q4_affine_matvec_mapped_batch, src/metal_runtime.rs:3599-3678: several projections over one
+ * activation of k elements; outputs[i] receives jobs[i].output_rows floats. */
+int q4b_matvec_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t k, const q4b_job *jobs,
+                     uint32_t n_jobs, float *const *outputs);
+/* q4_affine_matmul_mapped_batch, src/metal_runtime.rs:3683-3792: x is [m][k] row-major;
+ * outputs[i] is [m][jobs[i].output_rows] row-major. */
+int q4b_matmul_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *jobs,
+                     uint32_t n_jobs, float *const *outputs);
+/* q4_affine_argmax_mapped_batch, src/metal_runtime.rs:3797-3891: tokens[m]; ties -> lowest index. */
+int q4b_argmax_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *job,
+                     uint32_t *tokens);
+/* q4_affine_mlp_mapped_batch, src/metal_runtime.rs:4479-4689: down(silu(gate x) * (up x));
+ * gate and up have equal rows, down's input width is that row count; out is [m][down rows]. */
+int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *gate,
+                  const q4b_job *up, const q4b_job *down, float *out);
+/* encode_q4_affine_matmul_add, src/metal_runtime.rs:5644-5798: outputs[i] += projection
+ * (residual form); outputs hold the residual on entry. */
+int q4b_matmul_add_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *jobs,
+                         uint32_t n_jobs, float *const *outputs);
+/* dequantized_row, src/native.rs:4944-4987 (embedding lookup): one row as fp32, on the device. */
+int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t k, uint64_t row, float *out);
+
+/* ---- device-resident twins (asynchronous, encode_q4_affine_* analogues,
+ *      src/metal_runtime.rs:5476-6832) ---- */
+
+#define Q4B_FLAG_ACCUMULATE 1u /* out += projection */
+
+int q4b_matmul_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
+                            const q4b_job *jobs, uint32_t n_jobs, float *const *outputs_dev, uint32_t flags,
+                            void *stream);
+/* tokens_dev[m] (u32) and, if not null, values_dev[m] (the winning logits); token ids are
+ * offset by index_base (row-sharded vocabularies). */
+int q4b_argmax_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
+                            const q4b_job *job, uint32_t index_base, uint32_t *tokens_dev, float *values_dev,
+                            void *stream);
+/* h = silu(gate)*up over `count` elements; either output may be null. */
+int q4b_swiglu_device(q4b_runtime *rt, const float *gate_dev, const float *up_dev, uint64_t count,
+                      float *out_f32_dev, uint16_t *out_bf16_dev, void *stream);
+/* out = bf16(in / sqrt(mean(in^2) + eps)) per row of n elements (synthetic stack glue). */
+int q4b_rms_unit_bf16_device(q4b_runtime *rt, const float *in_dev, uint32_t rows, uint32_t n, float eps,
+                             uint16_t *out_bf16_dev, void *stream);
+
+/* ---- seeded synthetic tensors, generated in HBM (benchmark inputs) ---- */
+
+int q4b_synth_q4_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, float sigma, uint64_t row0,
+                        uint64_t rows, uint64_t k, const q4b_job *destination);
+int q4b_synth_bf16_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, uint64_t count, uint16_t *out_dev,
+                          void *stream);
+
+/* ---- introspection ---- */
+
+/* Name of the kernel variant the dispatcher would pick (tracing aid, cf. QWEN38_PAIR_TRACE). */
+int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, uint64_t k, const q4b_job *jobs,
+                          uint32_t n_jobs, char *text, uint32_t text_len);
+/* Per-kernel timing (the reference's QWEN38_BATCH_TIMING, src/metal_runtime.rs:2188-2245, uses
+ * GPUStartTime/GPUEndTime; here a CUDA event pair is recorded around every projection-kernel launch,
+ * on the stream it is launched on). q4b_profile_end synchronises, returns the number of timed
+ * launches, the sum of their durations and the algorithmic bytes they moved (packed weights, scales,
+ * biases, prepared activations, outputs), and stops recording. Not for use during graph capture. */
+int q4b_profile_begin(q4b_runtime *rt);
+int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes);
+/* Kernels launched by this runtime since creation (the benchmark's launch count). */
+int q4b_launch_count(q4b_runtime *rt, uint64_t *launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,99 @@
+"""ctypes prototypes of include/q4b200.h. The library is required: there is no fallback."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+Q4B_F32, Q4B_BF16 = 0, 1
+FLAG_ACCUMULATE = 1
+
+STATUS_NAMES = {
+    0: "Ok", 1: "NoDevice", 2: "EmptyBuffer", 3: "ActivationPoolPoisoned", 4: "EmptyDimension",
+    5: "InputNotGrouped", 6: "WrongLength", 7: "MissingMappedShard", 8: "InvalidBufferOffset",
+    9: "MappedTensorOutOfRange", 10: "DimensionOverflow", 11: "CommandFailed", 12: "CudaError",
+    13: "InvalidArgument", 14: "Unsupported",
+}
+
+
+class Job(C.Structure):
+    """q4b_job: MappedQ4AffineJob of the reference (src/metal_runtime.rs:155-192)."""
+
+    _fields_ = [
+        ("weight_shard", C.c_uint32), ("scale_shard", C.c_uint32), ("bias_shard", C.c_uint32),
+        ("aligned", C.c_int32),
+        ("weight_offset", C.c_uint64), ("scale_offset", C.c_uint64), ("bias_offset", C.c_uint64),
+        ("output_rows", C.c_uint64),
+    ]
+
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.LIB_PATH
+
+
+def load() -> C.CDLL:
+    """Load lib/libq4b200.so, or raise: the package has no other compute path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: build it with `python -m qwen38_metal_b200.build` "
+            "(the package has no CPU or PyTorch fallback)")
+    lib = C.CDLL(path)
+    vp, u32, u64, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int
+    P = C.POINTER
+    sig = {
+        "q4b_runtime_create": [i32, P(vp)],
+        "q4b_device_info": [vp, P(i32), P(u64), C.c_char_p, u32],
+        "q4b_shard_upload": [vp, vp, u64, P(u32)],
+        "q4b_shard_alloc": [vp, u64, P(u32)],
+        "q4b_shard_write": [vp, u32, u64, vp, u64],
+        "q4b_shard_read": [vp, u32, u64, vp, u64],
+        "q4b_shard_count": [vp, P(u32)],
+        "q4b_shard_info": [vp, u32, P(vp), P(u64)],
+        "q4b_offset_is_aligned": [vp, u32, u64, u64, P(i32)],
+        "q4b_matvec_batch": [vp, vp, i32, u64, P(Job), u32, P(vp)],
+        "q4b_matmul_batch": [vp, vp, i32, u64, u64, P(Job), u32, P(vp)],
+        "q4b_matmul_add_batch": [vp, vp, i32, u64, u64, P(Job), u32, P(vp)],
+        "q4b_argmax_batch": [vp, vp, i32, u64, u64, P(Job), vp],
+        "q4b_mlp_batch": [vp, vp, i32, u64, u64, P(Job), P(Job), P(Job), vp],
+        "q4b_dequantize_row": [vp, P(Job), u64, u64, vp],
+        "q4b_matmul_batch_device": [vp, vp, i32, u64, u64, P(Job), u32, P(vp), u32, vp],
+        "q4b_argmax_batch_device": [vp, vp, i32, u64, u64, P(Job), u32, vp, vp, vp],
+        "q4b_swiglu_device": [vp, vp, vp, u64, vp, vp, vp],
+        "q4b_rms_unit_bf16_device": [vp, vp, u32, u32, C.c_float, vp, vp],
+        "q4b_synth_q4_device": [vp, u64, u64, C.c_float, u64, u64, u64, P(Job)],
+        "q4b_synth_bf16_device": [vp, u64, u64, u64, vp, vp],
+        "q4b_describe_dispatch": [vp, i32, u64, u64, P(Job), u32, C.c_char_p, u32],
+        "q4b_launch_count": [vp, P(u64)],
+        "q4b_profile_begin": [vp],
+        "q4b_profile_end": [vp, P(u64), P(C.c_double), P(u64)],
+    }
+    for name, argtypes in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = C.c_int
+    lib.q4b_runtime_destroy.argtypes = [vp]
+    lib.q4b_runtime_destroy.restype = None
+    lib.q4b_last_error.argtypes = []
+    lib.q4b_last_error.restype = C.c_char_p
+    lib.q4b_status_name.argtypes = [i32]
+    lib.q4b_status_name.restype = C.c_char_p
+    _lib = lib
+    return lib
+
+
+EXPORTS = [
+    "q4b_runtime_create", "q4b_runtime_destroy", "q4b_last_error", "q4b_status_name", "q4b_device_info",
+    "q4b_shard_upload", "q4b_shard_alloc", "q4b_shard_write", "q4b_shard_read", "q4b_shard_count",
+    "q4b_shard_info", "q4b_offset_is_aligned", "q4b_matvec_batch", "q4b_matmul_batch", "q4b_argmax_batch",
+    "q4b_mlp_batch", "q4b_matmul_add_batch", "q4b_dequantize_row", "q4b_matmul_batch_device",
+    "q4b_argmax_batch_device", "q4b_swiglu_device", "q4b_rms_unit_bf16_device", "q4b_synth_q4_device",
+    "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end",
+]

@@ -1,0 +1,45 @@
+// Work decomposition of the streaming (decode) projection kernel, shared by device and host
+// code so the index arithmetic can be unit-tested on a CPU.
+//
+// A launch covers `tiles` row tiles (16 output rows each, over all jobs of the launch) times
+// `cpt` K-chunks per tile (a chunk is 128 inputs = two affine groups = 64 packed bytes per
+// row). The tiles*cpt units are numbered tile-major and cut into `workers` contiguous,
+// near-equal ranges, one per warp. A tile whose units fall into more than one range is
+// summed through per-warp partial slots by the last warp to arrive, in worker order.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define Q4_HD __host__ __device__ __forceinline__
+#else
+#define Q4_HD inline
+#endif
+
+struct Q4Split {
+    uint64_t units;    // tiles * cpt
+    uint32_t cpt;      // chunks per tile
+    uint32_t workers;  // warps in the grid
+};
+
+// first unit of worker w (w may equal workers: one past the last unit)
+Q4_HD uint64_t q4_split_begin(const Q4Split &s, uint32_t w) {
+    return (s.units * (uint64_t)w) / s.workers;
+}
+
+// the worker whose range holds unit u
+Q4_HD uint32_t q4_split_owner(const Q4Split &s, uint64_t u) {
+    return (uint32_t)((((u + 1) * (uint64_t)s.workers) - 1) / s.units);
+}
+
+// workers contributing to tile t: [first, last]
+Q4_HD void q4_split_contributors(const Q4Split &s, uint32_t tile, uint32_t *first, uint32_t *last) {
+    uint64_t u0 = (uint64_t)tile * s.cpt;
+    *first = q4_split_owner(s, u0);
+    *last = q4_split_owner(s, u0 + s.cpt - 1);
+}
+
+// partial slot worker w uses for tile t: slot 0 when t is the tile its range starts in, else 1
+Q4_HD uint32_t q4_split_slot(const Q4Split &s, uint32_t w, uint32_t tile) {
+    uint32_t head_tile = (uint32_t)(q4_split_begin(s, w) / s.cpt);
+    return 2u * w + (tile == head_tile ? 0u : 1u);
+}

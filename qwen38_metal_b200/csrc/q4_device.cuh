@@ -1,0 +1,81 @@
+// Device helpers shared by the affine-Q4 kernels (sm_100a).
+//
+// Format (MLX affine, group 64): a weight row is K/8 little-endian u32 words, eight 4-bit
+// values per word with value i at bits [4i,4i+4) (k = 8*word + i); one bf16 scale and one bf16
+// bias per 64 consecutive k; w = scale*q + bias. Mirrors shaders/qwen38.metal:18-115 of the
+// reference (bf16 conversion, nibble order, byte-wise loads for unaligned tensors).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q4 {
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits) { return __uint_as_float(bits << 16); }
+
+// round-to-nearest-even without a NaN case: shaders/qwen38.metal:22-26
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float v) {
+    uint32_t bits = __float_as_uint(v);
+    return (bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16;
+}
+
+// Streaming 128-bit load: read-only path, no L1 allocation (weights are touched once).
+__device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// 16 bytes from an arbitrarily aligned address: two aligned 128-bit loads of the enclosing
+// window and a funnel shift (the byte-addressed twin of the aligned load; the reference's
+// qwen38_load_u32, shaders/qwen38.metal:105-110, reads byte by byte instead).
+// `mis` = address & 15, uniform over the warp. Reads up to 16 bytes past p+16 when mis != 0;
+// shard allocations are padded for that.
+__device__ __forceinline__ uint4 ldg_stream_v4_unaligned(const uint8_t *p, uint32_t mis) {
+    const uint8_t *base = p - mis;
+    uint4 lo = ldg_stream_v4(base);
+    if (mis == 0) return lo;
+    uint4 hi = ldg_stream_v4(base + 16);
+    uint32_t w0 = lo.x, w1 = lo.y, w2 = lo.z, w3 = lo.w, w4 = hi.x, w5 = hi.y, w6 = hi.z, w7 = hi.w;
+    if (mis & 4) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
+    if (mis & 8) { w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = w6; }
+    uint32_t sh = (mis & 3u) * 8u;
+    uint4 out;
+    out.x = __funnelshift_r(w0, w1, sh);
+    out.y = __funnelshift_r(w1, w2, sh);
+    out.z = __funnelshift_r(w2, w3, sh);
+    out.w = __funnelshift_r(w3, w4, sh);
+    return out;
+}
+
+// one bf16 parameter (scale or bias) at any byte alignment, as raw bits
+__device__ __forceinline__ uint32_t ldg_bf16_bits(const uint8_t *p) {
+    if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) {
+        return (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(p));
+    }
+    return (uint32_t)__ldg(p) | ((uint32_t)__ldg(p + 1) << 8);
+}
+
+// Two nibbles of a packed word -> exact bf16x2 (lo half: bits [0,4) of v, hi half: bits [16,20)).
+// 0x4300|q is the bf16 number 128+q (ulp 1 in [128,256)); subtracting 128 is exact.
+__device__ __forceinline__ uint32_t nib2_to_bf16x2(uint32_t v) {
+    uint32_t biased = (v & 0x000f000fu) | 0x43004300u;
+    uint32_t out;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(out) : "r"(biased), "r"(0x43004300u));
+    return out;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float silu(float v) { return v * (1.0f / (1.0f + __expf(-v))); }
+
+}  // namespace q4

@@ -1,0 +1,65 @@
+// Kernel-side parameter blocks and launcher prototypes shared between the .cu files and the
+// host runtime (runtime.cpp). Plain C structs: no CUDA types beyond cudaStream_t/cudaError_t.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q4 {
+
+constexpr int kMaxJobs = 12;
+
+// One projection of a grouped launch (the device image of a MappedQ4AffineJob,
+// src/metal_runtime.rs:155-192 of the reference, with shard ids resolved to pointers).
+struct GemvJob {
+    const uint8_t *w;      // packed weights, [n][k/8] u32, any byte alignment
+    const uint8_t *s;      // scales, [n][k/64] bf16
+    const uint8_t *b;      // biases, [n][k/64] bf16
+    float *out;            // [m][out_stride] fp32
+    uint32_t n;            // output rows
+    uint32_t out_stride;   // elements between activation rows of `out`
+    uint32_t tile_begin;   // first 16-row tile of this job in the launch
+    uint32_t w_misalign;   // (uintptr_t)w & 15
+};
+
+struct GemvParams {
+    GemvJob jobs[kMaxJobs];
+    uint32_t n_jobs;
+    const uint16_t *xp;    // prepared activation columns, [v_cols][k] bf16 in fragment order
+    const float *xsum;     // [k/64][vpad] per-group column sums
+    uint32_t v_cols;       // activation columns in use (m_rows, or 3*m_rows for fp32 input)
+    uint32_t vpad;         // 4 * column tiles
+    uint32_t m_rows;       // activation rows
+    uint32_t x_is_f32;     // columns are hi/mid/lo splits of fp32 rows
+    uint32_t accumulate;   // out += projection (residual form) instead of out = projection
+    uint32_t k;            // input elements
+    uint32_t groups;       // k / 64
+    uint32_t cpt;          // K-chunks (128 inputs) per tile = ceil(groups / 2)
+    uint32_t workers;      // warps in the grid
+    uint64_t units;        // tiles * cpt
+    float *partials;       // [workers][2][column tiles][32][4] fp32 scratch for split tiles
+    unsigned int *counters;  // [workers], zero between launches
+};
+
+}  // namespace q4
+
+extern "C" {
+cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t k, uint32_t vpad, uint16_t *xp,
+                          float *xsum, cudaStream_t stream);
+int q4k_gemv_warps_per_cta(void);
+cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int aligned, uint32_t ctas, cudaStream_t stream);
+uint32_t q4k_gemv_occupancy(int column_tiles, int aligned);  // resident CTAs per SM, 0 on error
+
+cudaError_t q4k_swiglu(const float *gate, const float *up, uint64_t count, float *out_f32, uint16_t *out_bf16,
+                       cudaStream_t stream);
+cudaError_t q4k_f32_to_bf16(const float *in, uint64_t count, uint16_t *out, cudaStream_t stream);
+uint32_t q4k_argmax_parts(uint32_t n);
+cudaError_t q4k_argmax_rows(const float *logits, uint32_t m, uint32_t n, uint32_t index_base, float *pv, uint32_t *pi,
+                            uint32_t *tokens, float *values, cudaStream_t stream);
+cudaError_t q4k_rms_unit_bf16(const float *in, uint32_t rows, uint32_t n, float eps, uint16_t *out, cudaStream_t stream);
+cudaError_t q4k_dequantize_row(const uint8_t *w, const uint8_t *s, const uint8_t *b, uint32_t k, uint32_t row, float *out,
+                               cudaStream_t stream);
+
+cudaError_t q4k_synth_q4(uint64_t seed, uint64_t tensor, float sigma, uint64_t row0, uint64_t rows, uint32_t k,
+                         uint8_t *w, uint8_t *s, uint8_t *b, cudaStream_t stream);
+cudaError_t q4k_synth_bf16(uint64_t seed, uint64_t tensor, uint64_t count, uint16_t *out, cudaStream_t stream);
+}

@@ -1,0 +1,777 @@
+// Host runtime behind the C ABI (include/q4b200.h): shard table, validation, scratch pools,
+// kernel selection and launch. It is the CUDA counterpart of the Q4 part of the reference's
+// MetalRuntime (src/metal_runtime.rs:79-207, 929-982, 3523-4756, 5476-6922, 8831-9057).
+// There is no CPU fallback: without a CUDA device every entry point fails with Q4B_NO_DEVICE.
+#include "../../include/q4b200.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "q4_kernels.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return status;
+}
+
+int fail_cuda(cudaError_t e, const char *what) {
+    return fail(Q4B_CUDA_ERROR, "CUDA call failed in %s: %s", what, cudaGetErrorString(e));
+}
+
+#define Q4B_CUDA(call, what)                          \
+    do {                                              \
+        cudaError_t e__ = (call);                     \
+        if (e__ != cudaSuccess) return fail_cuda(e__, what); \
+    } while (0)
+
+// Grow-only scratch buffer, power-of-two capacity: ensure_private_buffer /
+// shared_reusable_buffer of the reference (src/metal_runtime.rs:8993-9057).
+struct Pool {
+    void *ptr = nullptr;
+    size_t capacity = 0;
+    cudaError_t ensure(size_t bytes) {
+        if (bytes <= capacity) return cudaSuccess;
+        size_t want = 256;
+        while (want < bytes) want <<= 1;
+        void *fresh = nullptr;
+        cudaError_t e = cudaMalloc(&fresh, want);
+        if (e != cudaSuccess) return e;
+        if (ptr) cudaFree(ptr);
+        ptr = fresh;
+        capacity = want;
+        return cudaSuccess;
+    }
+    void release() {
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        capacity = 0;
+    }
+};
+
+struct Shard {
+    uint8_t *ptr = nullptr;
+    uint64_t bytes = 0;
+};
+
+constexpr uint64_t kShardTailPad = 64;  // the unaligned window load may read 16 bytes past a tensor
+
+struct Resolved {
+    const uint8_t *w, *s, *b;
+    uint32_t n;
+};
+
+}  // namespace
+
+struct q4b_runtime {
+    int device = 0;
+    int sm_count = 0;
+    uint64_t total_bytes = 0;
+    char name[128] = {0};
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    std::vector<Shard> shards;
+    uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident CTAs per SM
+    uint32_t max_workers = 0;
+    Pool x_in, xp, xsum, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
+    Pool outs[q4::kMaxJobs];
+    uint64_t launches = 0;
+    std::string force_variant;
+    // per-kernel timing window (q4b_profile_begin/end)
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;  // start/stop pairs
+    size_t prof_used = 0;
+    uint64_t prof_bytes = 0;
+};
+
+extern "C" uint32_t q4k_gemv_occupancy(int column_tiles, int aligned);
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int device) {
+        cudaGetDevice(&prev);
+        if (prev != device) cudaSetDevice(device);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+int check_rt(q4b_runtime *rt) {
+    if (!rt) return fail(Q4B_INVALID_ARGUMENT, "runtime handle is null");
+    return Q4B_OK;
+}
+
+// validate_mapped_q4_affine_shape, src/metal_runtime.rs:8854-8898, on shard ids
+int resolve_job(q4b_runtime *rt, const q4b_job &job, uint64_t k, Resolved *out) {
+    if (k == 0 || job.output_rows == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    if (k % 64 != 0)
+        return fail(Q4B_INPUT_NOT_GROUPED, "input dimension %llu is not divisible by affine group size 64",
+                    (unsigned long long)k);
+    const uint32_t ids[3] = {job.weight_shard, job.scale_shard, job.bias_shard};
+    for (uint32_t id : ids) {
+        if (id >= rt->shards.size() || rt->shards[id].ptr == nullptr)
+            return fail(Q4B_MISSING_SHARD, "mapped safetensors shard %u is absent", id);
+    }
+    const Shard &ws = rt->shards[job.weight_shard], &ss = rt->shards[job.scale_shard], &bs = rt->shards[job.bias_shard];
+    if (job.weight_offset > ws.bytes || job.scale_offset > ss.bytes || job.bias_offset > bs.bytes)
+        return fail(Q4B_INVALID_BUFFER_OFFSET, "mapped tensor offset is outside its shard");
+    if (job.output_rows > 0xffffffffull) return fail(Q4B_DIMENSION_OVERFLOW, "output rows exceeds runtime limits");
+    if (k / 8 > 0xffffffffull) return fail(Q4B_DIMENSION_OVERFLOW, "words per row exceeds runtime limits");
+    const uint64_t words = k / 8, groups = k / 64;
+    if (job.output_rows > UINT64_MAX / 4 / words) return fail(Q4B_DIMENSION_OVERFLOW, "packed weight count exceeds runtime limits");
+    const uint64_t weight_bytes = job.output_rows * words * 4;
+    const uint64_t affine_bytes = job.output_rows * groups * 2;
+    if (weight_bytes > ws.bytes - job.weight_offset || affine_bytes > ss.bytes - job.scale_offset ||
+        affine_bytes > bs.bytes - job.bias_offset)
+        return fail(Q4B_TENSOR_OUT_OF_RANGE, "mapped tensor range exceeds its safetensors shard");
+    out->w = ws.ptr + job.weight_offset;
+    out->s = ss.ptr + job.scale_offset;
+    out->b = bs.ptr + job.bias_offset;
+    out->n = (uint32_t)job.output_rows;
+    return Q4B_OK;
+}
+
+int resolve_jobs(q4b_runtime *rt, const q4b_job *jobs, uint32_t n_jobs, uint64_t m, uint64_t k,
+                 std::vector<Resolved> *out) {
+    if (!jobs || n_jobs == 0 || m == 0 || k == 0)
+        return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    if (m > 0xffffffffull) return fail(Q4B_DIMENSION_OVERFLOW, "batch size exceeds runtime limits");
+    out->resize(n_jobs);
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        int st = resolve_job(rt, jobs[i], k, &(*out)[i]);
+        if (st != Q4B_OK) return st;
+    }
+    return Q4B_OK;
+}
+
+bool job_is_aligned(const Resolved &r) {
+    return ((uintptr_t)r.w & 15u) == 0 && ((uintptr_t)r.s & 1u) == 0 && ((uintptr_t)r.b & 1u) == 0;
+}
+
+// One streaming launch: up to kMaxJobs projections, up to 8 bf16 (2 fp32) activation rows.
+int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m, uint32_t k, const Resolved *jobs,
+                     uint32_t n_jobs, float *const *outs, const uint32_t *out_strides, uint32_t flags,
+                     cudaStream_t stream) {
+    const bool f32 = x_dtype == Q4B_F32;
+    const uint32_t v_cols = m * (f32 ? 3u : 1u);
+    const int nt = v_cols <= 4 ? 1 : 2;
+    const uint32_t vpad = 4u * nt;
+    const uint32_t groups = k / 64;
+    Q4B_CUDA(rt->xp.ensure((size_t)v_cols * k * 2), "activation scratch");
+    Q4B_CUDA(rt->xsum.ensure((size_t)groups * vpad * 4), "activation sum scratch");
+    Q4B_CUDA(q4k_prepare_x(x_dev, f32 ? 1 : 0, m, k, vpad, (uint16_t *)rt->xp.ptr, (float *)rt->xsum.ptr, stream),
+             "q4_prepare_x launch");
+    rt->launches++;
+
+    q4::GemvParams p;
+    memset(&p, 0, sizeof p);
+    bool aligned = true;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        q4::GemvJob &j = p.jobs[i];
+        j.w = jobs[i].w;
+        j.s = jobs[i].s;
+        j.b = jobs[i].b;
+        j.out = outs[i];
+        j.n = jobs[i].n;
+        j.out_stride = out_strides ? out_strides[i] : jobs[i].n;
+        j.tile_begin = tiles;
+        j.w_misalign = (uint32_t)((uintptr_t)jobs[i].w & 15u);
+        tiles += (jobs[i].n + 15u) / 16u;
+        aligned = aligned && job_is_aligned(jobs[i]);
+    }
+    p.n_jobs = n_jobs;
+    p.xp = (const uint16_t *)rt->xp.ptr;
+    p.xsum = (const float *)rt->xsum.ptr;
+    p.v_cols = v_cols;
+    p.vpad = vpad;
+    p.m_rows = m;
+    p.x_is_f32 = f32 ? 1u : 0u;
+    p.accumulate = (flags & Q4B_FLAG_ACCUMULATE) ? 1u : 0u;
+    p.k = k;
+    p.groups = groups;
+    p.cpt = (groups + 1u) / 2u;
+    p.units = (uint64_t)tiles * p.cpt;
+    const uint32_t per_sm = rt->gemv_ctas[nt][aligned ? 1 : 0];
+    uint32_t ctas = (uint32_t)rt->sm_count * per_sm;
+    const uint32_t wpc = (uint32_t)q4k_gemv_warps_per_cta();
+    // never more warps than units: every worker then owns at least one unit, which the split-tile
+    // arrival count relies on; surplus warps of the last CTA exit at once
+    uint64_t workers = (uint64_t)ctas * wpc;
+    if (workers > p.units) workers = p.units;
+    p.workers = (uint32_t)workers;
+    ctas = (p.workers + wpc - 1) / wpc;
+    p.partials = (float *)rt->partials.ptr;
+    p.counters = (unsigned int *)rt->counters.ptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    if (rt->profiling) {
+        if (rt->prof_used + 2 > rt->prof_events.size()) {
+            for (int i = 0; i < 2; ++i) {
+                cudaEvent_t ev;
+                Q4B_CUDA(cudaEventCreate(&ev), "cudaEventCreate");
+                rt->prof_events.push_back(ev);
+            }
+        }
+        ev_start = rt->prof_events[rt->prof_used];
+        ev_stop = rt->prof_events[rt->prof_used + 1];
+        Q4B_CUDA(cudaEventRecord(ev_start, stream), "cudaEventRecord");
+    }
+    Q4B_CUDA(q4k_gemv(&p, nt, aligned ? 1 : 0, ctas, stream), "q4_gemv launch");
+    rt->launches++;
+    if (rt->profiling) {
+        Q4B_CUDA(cudaEventRecord(ev_stop, stream), "cudaEventRecord");
+        rt->prof_used += 2;
+        uint64_t bytes = (uint64_t)v_cols * k * 2 + (uint64_t)groups * vpad * 4;
+        for (uint32_t i = 0; i < n_jobs; ++i)
+            bytes += (uint64_t)jobs[i].n * (k / 2 + (uint64_t)groups * 4) + (uint64_t)m * jobs[i].n * 4;
+        rt->prof_bytes += bytes;
+    }
+    return Q4B_OK;
+}
+
+// Any m, any number of jobs: cut into launches the streaming kernel accepts.
+int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
+                   const std::vector<Resolved> &jobs, float *const *outs, uint32_t flags, cudaStream_t stream) {
+    const uint32_t rows_per_launch = x_dtype == Q4B_F32 ? 2u : 8u;
+    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
+    for (uint64_t m0 = 0; m0 < m; m0 += rows_per_launch) {
+        const uint32_t mb = (uint32_t)((m - m0) < rows_per_launch ? (m - m0) : rows_per_launch);
+        const uint8_t *xb = (const uint8_t *)x_dev + m0 * k * esize;
+        for (size_t j0 = 0; j0 < jobs.size(); j0 += q4::kMaxJobs) {
+            const uint32_t nj = (uint32_t)((jobs.size() - j0) < (size_t)q4::kMaxJobs ? (jobs.size() - j0) : (size_t)q4::kMaxJobs);
+            float *o[q4::kMaxJobs];
+            for (uint32_t i = 0; i < nj; ++i) o[i] = outs[j0 + i] + m0 * jobs[j0 + i].n;
+            int st = launch_streaming(rt, xb, x_dtype, mb, (uint32_t)k, &jobs[j0], nj, o, nullptr, flags, stream);
+            if (st != Q4B_OK) return st;
+        }
+    }
+    return Q4B_OK;
+}
+
+int check_dtype(int x_dtype) {
+    if (x_dtype != Q4B_F32 && x_dtype != Q4B_BF16) return fail(Q4B_INVALID_ARGUMENT, "unknown activation dtype %d", x_dtype);
+    return Q4B_OK;
+}
+
+int finish(q4b_runtime *rt, cudaStream_t stream) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(Q4B_COMMAND_FAILED, "CUDA command failed: %s", cudaGetErrorString(e));
+    (void)rt;
+    return Q4B_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// runtime
+// ------------------------------------------------------------------------------------------
+
+extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
+    if (!out) return fail(Q4B_INVALID_ARGUMENT, "output handle pointer is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(Q4B_NO_DEVICE, "no CUDA device is available");
+    }
+    if (device_ordinal < 0 || device_ordinal >= count)
+        return fail(Q4B_NO_DEVICE, "CUDA device %d is not available (%d visible)", device_ordinal, count);
+    DeviceGuard guard(device_ordinal);
+    cudaDeviceProp prop;
+    Q4B_CUDA(cudaGetDeviceProperties(&prop, device_ordinal), "cudaGetDeviceProperties");
+    if (prop.major != 10)
+        return fail(Q4B_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device_ordinal,
+                    prop.major, prop.minor);
+    q4b_runtime *rt = new (std::nothrow) q4b_runtime();
+    if (!rt) return fail(Q4B_CUDA_ERROR, "out of host memory");
+    rt->device = device_ordinal;
+    rt->sm_count = prop.multiProcessorCount;
+    rt->total_bytes = prop.totalGlobalMem;
+    snprintf(rt->name, sizeof rt->name, "%s", prop.name);
+    if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
+    e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete rt;
+        return fail_cuda(e, "cudaStreamCreate");
+    }
+    uint32_t max_ctas = 1;
+    for (int nt = 1; nt <= 2; ++nt)
+        for (int al = 0; al < 2; ++al) {
+            uint32_t occ = q4k_gemv_occupancy(nt, al);
+            if (occ == 0) {
+                cudaStreamDestroy(rt->stream);
+                delete rt;
+                return fail(Q4B_CUDA_ERROR, "streaming kernel cannot be resident on this device (sm_100a image missing?)");
+            }
+            rt->gemv_ctas[nt][al] = occ;
+            max_ctas = occ > max_ctas ? occ : max_ctas;
+        }
+    rt->max_workers = (uint32_t)rt->sm_count * max_ctas * (uint32_t)q4k_gemv_warps_per_cta();
+    // split-tile scratch: [workers][2 slots][2 column tiles][32 lanes][4 floats] and one counter per worker
+    e = rt->partials.ensure((size_t)rt->max_workers * 2 * 2 * 32 * 16);
+    if (e == cudaSuccess) e = rt->counters.ensure((size_t)rt->max_workers * 4);
+    if (e == cudaSuccess) e = cudaMemset(rt->counters.ptr, 0, rt->counters.capacity);
+    if (e != cudaSuccess) {
+        q4b_runtime_destroy(rt);
+        return fail_cuda(e, "scratch allocation");
+    }
+    *out = rt;
+    return Q4B_OK;
+}
+
+extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
+    if (!rt) return;
+    DeviceGuard guard(rt->device);
+    cudaDeviceSynchronize();
+    for (Shard &s : rt->shards)
+        if (s.ptr) cudaFree(s.ptr);
+    Pool *pools[] = {&rt->x_in, &rt->xp, &rt->xsum, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
+                     &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
+    for (Pool *p : pools) p->release();
+    for (Pool &p : rt->outs) p.release();
+    for (cudaEvent_t ev : rt->prof_events) cudaEventDestroy(ev);
+    if (rt->stream) cudaStreamDestroy(rt->stream);
+    delete rt;
+}
+
+extern "C" const char *q4b_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" const char *q4b_status_name(int status) {
+    switch (status) {
+        case Q4B_OK: return "Ok";
+        case Q4B_NO_DEVICE: return "NoDevice";
+        case Q4B_EMPTY_BUFFER: return "EmptyBuffer";
+        case Q4B_POOL_POISONED: return "ActivationPoolPoisoned";
+        case Q4B_EMPTY_DIMENSION: return "EmptyDimension";
+        case Q4B_INPUT_NOT_GROUPED: return "InputNotGrouped";
+        case Q4B_WRONG_LENGTH: return "WrongLength";
+        case Q4B_MISSING_SHARD: return "MissingMappedShard";
+        case Q4B_INVALID_BUFFER_OFFSET: return "InvalidBufferOffset";
+        case Q4B_TENSOR_OUT_OF_RANGE: return "MappedTensorOutOfRange";
+        case Q4B_DIMENSION_OVERFLOW: return "DimensionOverflow";
+        case Q4B_COMMAND_FAILED: return "CommandFailed";
+        case Q4B_CUDA_ERROR: return "CudaError";
+        case Q4B_INVALID_ARGUMENT: return "InvalidArgument";
+        case Q4B_UNSUPPORTED: return "Unsupported";
+        default: return "Unknown";
+    }
+}
+
+extern "C" int q4b_device_info(q4b_runtime *rt, int *sm_count, uint64_t *total_bytes, char *name, uint32_t name_len) {
+    if (int st = check_rt(rt)) return st;
+    if (sm_count) *sm_count = rt->sm_count;
+    if (total_bytes) *total_bytes = rt->total_bytes;
+    if (name && name_len) snprintf(name, name_len, "%s", rt->name);
+    return Q4B_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// shards
+// ------------------------------------------------------------------------------------------
+
+static int shard_new(q4b_runtime *rt, uint64_t bytes, uint32_t *shard_id) {
+    if (int st = check_rt(rt)) return st;
+    if (!shard_id) return fail(Q4B_INVALID_ARGUMENT, "shard id pointer is null");
+    if (bytes == 0) return fail(Q4B_EMPTY_BUFFER, "CUDA buffers cannot be empty");
+    void *p = nullptr;
+    Q4B_CUDA(cudaMalloc(&p, bytes + kShardTailPad), "shard allocation");
+    Q4B_CUDA(cudaMemset((uint8_t *)p + bytes, 0, kShardTailPad), "shard tail clear");
+    Shard s;
+    s.ptr = (uint8_t *)p;
+    s.bytes = bytes;
+    rt->shards.push_back(s);
+    *shard_id = (uint32_t)(rt->shards.size() - 1);
+    return Q4B_OK;
+}
+
+extern "C" int q4b_shard_upload(q4b_runtime *rt, const void *host_bytes, uint64_t bytes, uint32_t *shard_id) {
+    if (int st = check_rt(rt)) return st;
+    if (!host_bytes && bytes) return fail(Q4B_INVALID_ARGUMENT, "host pointer is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    uint32_t id = 0;
+    if (int st = shard_new(rt, bytes, &id)) return st;
+    cudaError_t e = cudaMemcpy(rt->shards[id].ptr, host_bytes, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(rt->shards[id].ptr);
+        rt->shards.pop_back();
+        return fail_cuda(e, "shard upload");
+    }
+    *shard_id = id;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_shard_alloc(q4b_runtime *rt, uint64_t bytes, uint32_t *shard_id) {
+    if (int st = check_rt(rt)) return st;
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    return shard_new(rt, bytes, shard_id);
+}
+
+static int shard_range(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, uint64_t bytes) {
+    if (shard_id >= rt->shards.size() || !rt->shards[shard_id].ptr)
+        return fail(Q4B_MISSING_SHARD, "mapped safetensors shard %u is absent", shard_id);
+    if (offset > rt->shards[shard_id].bytes) return fail(Q4B_INVALID_BUFFER_OFFSET, "mapped tensor offset is outside its shard");
+    if (bytes > rt->shards[shard_id].bytes - offset)
+        return fail(Q4B_TENSOR_OUT_OF_RANGE, "mapped tensor range exceeds its safetensors shard");
+    return Q4B_OK;
+}
+
+extern "C" int q4b_shard_write(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, const void *host_bytes,
+                               uint64_t bytes) {
+    if (int st = check_rt(rt)) return st;
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    if (int st = shard_range(rt, shard_id, offset, bytes)) return st;
+    if (bytes == 0) return Q4B_OK;
+    if (!host_bytes) return fail(Q4B_INVALID_ARGUMENT, "host pointer is null");
+    Q4B_CUDA(cudaMemcpy(rt->shards[shard_id].ptr + offset, host_bytes, bytes, cudaMemcpyHostToDevice), "shard write");
+    return Q4B_OK;
+}
+
+extern "C" int q4b_shard_read(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, void *host_bytes, uint64_t bytes) {
+    if (int st = check_rt(rt)) return st;
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    if (int st = shard_range(rt, shard_id, offset, bytes)) return st;
+    if (bytes == 0) return Q4B_OK;
+    if (!host_bytes) return fail(Q4B_INVALID_ARGUMENT, "host pointer is null");
+    Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
+    Q4B_CUDA(cudaMemcpy(host_bytes, rt->shards[shard_id].ptr + offset, bytes, cudaMemcpyDeviceToHost), "shard read");
+    return Q4B_OK;
+}
+
+extern "C" int q4b_shard_count(q4b_runtime *rt, uint32_t *count) {
+    if (int st = check_rt(rt)) return st;
+    if (!count) return fail(Q4B_INVALID_ARGUMENT, "count pointer is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    *count = (uint32_t)rt->shards.size();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_shard_info(q4b_runtime *rt, uint32_t shard_id, void **device_ptr, uint64_t *bytes) {
+    if (int st = check_rt(rt)) return st;
+    std::lock_guard<std::mutex> lock(rt->mu);
+    if (int st = shard_range(rt, shard_id, 0, 0)) return st;
+    if (device_ptr) *device_ptr = rt->shards[shard_id].ptr;
+    if (bytes) *bytes = rt->shards[shard_id].bytes;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_offset_is_aligned(q4b_runtime *rt, uint32_t shard_id, uint64_t byte_offset, uint64_t alignment,
+                                     int *aligned) {
+    if (int st = check_rt(rt)) return st;
+    if (!aligned || alignment == 0) return fail(Q4B_INVALID_ARGUMENT, "alignment must be positive and the result pointer non-null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    if (int st = shard_range(rt, shard_id, 0, 0)) return st;
+    *aligned = (((uintptr_t)rt->shards[shard_id].ptr + byte_offset) % alignment) == 0 ? 1 : 0;
+    return Q4B_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// device-resident entry points
+// ------------------------------------------------------------------------------------------
+
+extern "C" int q4b_matmul_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
+                                       const q4b_job *jobs, uint32_t n_jobs, float *const *outputs_dev,
+                                       uint32_t flags, void *stream) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!x_dev || !outputs_dev) return fail(Q4B_INVALID_ARGUMENT, "activation or output pointer is null");
+    if ((uintptr_t)x_dev & 15u) return fail(Q4B_INVALID_ARGUMENT, "device activations must be 16-byte aligned");
+    DeviceGuard guard(rt->device);
+    std::vector<Resolved> resolved;
+    if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
+    for (uint32_t i = 0; i < n_jobs; ++i)
+        if (!outputs_dev[i]) return fail(Q4B_INVALID_ARGUMENT, "output pointer %u is null", i);
+    return enqueue_matmul(rt, x_dev, x_dtype, m, k, resolved, outputs_dev, flags, (cudaStream_t)stream);
+}
+
+extern "C" int q4b_argmax_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
+                                       const q4b_job *job, uint32_t index_base, uint32_t *tokens_dev,
+                                       float *values_dev, void *stream) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!x_dev || !tokens_dev || !job) return fail(Q4B_INVALID_ARGUMENT, "activation, job or token pointer is null");
+    DeviceGuard guard(rt->device);
+    std::vector<Resolved> resolved;
+    if (int st = resolve_jobs(rt, job, 1, m, k, &resolved)) return st;
+    const uint32_t n = resolved[0].n;
+    const uint32_t parts = q4k_argmax_parts(n);
+    Q4B_CUDA(rt->logits.ensure((size_t)m * n * 4), "logit scratch");
+    Q4B_CUDA(rt->amax_v.ensure((size_t)m * parts * 4), "argmax scratch");
+    Q4B_CUDA(rt->amax_i.ensure((size_t)m * parts * 4), "argmax scratch");
+    float *logits = (float *)rt->logits.ptr;
+    if (int st = enqueue_matmul(rt, x_dev, x_dtype, m, k, resolved, &logits, 0, (cudaStream_t)stream)) return st;
+    Q4B_CUDA(q4k_argmax_rows(logits, (uint32_t)m, n, index_base, (float *)rt->amax_v.ptr, (uint32_t *)rt->amax_i.ptr,
+                             tokens_dev, values_dev, (cudaStream_t)stream),
+             "argmax launch");
+    rt->launches += 2;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_swiglu_device(q4b_runtime *rt, const float *gate_dev, const float *up_dev, uint64_t count,
+                                 float *out_f32_dev, uint16_t *out_bf16_dev, void *stream) {
+    if (int st = check_rt(rt)) return st;
+    if (!gate_dev || !up_dev || (!out_f32_dev && !out_bf16_dev)) return fail(Q4B_INVALID_ARGUMENT, "swiglu pointer is null");
+    if (count == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    DeviceGuard guard(rt->device);
+    Q4B_CUDA(q4k_swiglu(gate_dev, up_dev, count, out_f32_dev, out_bf16_dev, (cudaStream_t)stream), "swiglu launch");
+    rt->launches++;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_rms_unit_bf16_device(q4b_runtime *rt, const float *in_dev, uint32_t rows, uint32_t n, float eps,
+                                        uint16_t *out_bf16_dev, void *stream) {
+    if (int st = check_rt(rt)) return st;
+    if (!in_dev || !out_bf16_dev) return fail(Q4B_INVALID_ARGUMENT, "rms pointer is null");
+    if (rows == 0 || n == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    DeviceGuard guard(rt->device);
+    Q4B_CUDA(q4k_rms_unit_bf16(in_dev, rows, n, eps, out_bf16_dev, (cudaStream_t)stream), "rms launch");
+    rt->launches++;
+    return Q4B_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// host-buffer entry points
+// ------------------------------------------------------------------------------------------
+
+static int host_matmul(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *jobs,
+                       uint32_t n_jobs, float *const *outputs, uint32_t flags) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!x || !outputs) return fail(Q4B_INVALID_ARGUMENT, "activation or output pointer is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    std::vector<Resolved> resolved;
+    if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
+    for (uint32_t i = 0; i < n_jobs; ++i)
+        if (!outputs[i]) return fail(Q4B_INVALID_ARGUMENT, "output pointer %u is null", i);
+    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
+    Q4B_CUDA(rt->x_in.ensure((size_t)m * k * esize), "activation buffer");
+    // one device buffer holds every job's [m][n] output, 256-byte aligned slices
+    std::vector<size_t> offs(n_jobs);
+    size_t total = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        offs[i] = total;
+        total += (((size_t)m * resolved[i].n * 4) + 255) & ~(size_t)255;
+    }
+    Q4B_CUDA(rt->outs[0].ensure(total), "output buffer");
+    cudaStream_t s = rt->stream;
+    Q4B_CUDA(cudaMemcpyAsync(rt->x_in.ptr, x, (size_t)m * k * esize, cudaMemcpyHostToDevice, s), "activation upload");
+    std::vector<float *> outs_dev(n_jobs);
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        outs_dev[i] = (float *)((uint8_t *)rt->outs[0].ptr + offs[i]);
+        if (flags & Q4B_FLAG_ACCUMULATE)
+            Q4B_CUDA(cudaMemcpyAsync(outs_dev[i], outputs[i], (size_t)m * resolved[i].n * 4, cudaMemcpyHostToDevice, s),
+                     "residual upload");
+    }
+    if (int st = enqueue_matmul(rt, rt->x_in.ptr, x_dtype, m, k, resolved, outs_dev.data(), flags, s)) {
+        cudaStreamSynchronize(s);
+        return st;
+    }
+    // results land in a private copy first so that caller buffers stay untouched on failure
+    for (uint32_t i = 0; i < n_jobs; ++i)
+        Q4B_CUDA(cudaMemcpyAsync(outputs[i], outs_dev[i], (size_t)m * resolved[i].n * 4, cudaMemcpyDeviceToHost, s),
+                 "result download");
+    return finish(rt, s);
+}
+
+extern "C" int q4b_matvec_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t k, const q4b_job *jobs,
+                                uint32_t n_jobs, float *const *outputs) {
+    return host_matmul(rt, x, x_dtype, 1, k, jobs, n_jobs, outputs, 0);
+}
+
+extern "C" int q4b_matmul_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k,
+                                const q4b_job *jobs, uint32_t n_jobs, float *const *outputs) {
+    return host_matmul(rt, x, x_dtype, m, k, jobs, n_jobs, outputs, 0);
+}
+
+extern "C" int q4b_matmul_add_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k,
+                                    const q4b_job *jobs, uint32_t n_jobs, float *const *outputs) {
+    return host_matmul(rt, x, x_dtype, m, k, jobs, n_jobs, outputs, Q4B_FLAG_ACCUMULATE);
+}
+
+extern "C" int q4b_argmax_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k,
+                                const q4b_job *job, uint32_t *tokens) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!x || !tokens || !job) return fail(Q4B_INVALID_ARGUMENT, "activation, job or token pointer is null");
+    if (m == 0 || k == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
+    Q4B_CUDA(rt->x_in.ensure((size_t)m * k * esize), "activation buffer");
+    Q4B_CUDA(rt->tokens.ensure((size_t)m * 4), "token buffer");
+    cudaStream_t s = rt->stream;
+    Q4B_CUDA(cudaMemcpyAsync(rt->x_in.ptr, x, (size_t)m * k * esize, cudaMemcpyHostToDevice, s), "activation upload");
+    if (int st = q4b_argmax_batch_device(rt, rt->x_in.ptr, x_dtype, m, k, job, 0, (uint32_t *)rt->tokens.ptr, nullptr, s)) {
+        cudaStreamSynchronize(s);
+        return st;
+    }
+    std::vector<uint32_t> staged(m);
+    Q4B_CUDA(cudaMemcpyAsync(staged.data(), rt->tokens.ptr, (size_t)m * 4, cudaMemcpyDeviceToHost, s), "token download");
+    if (int st = finish(rt, s)) return st;
+    memcpy(tokens, staged.data(), (size_t)m * 4);
+    return Q4B_OK;
+}
+
+extern "C" int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *gate,
+                             const q4b_job *up, const q4b_job *down, float *out) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!x || !out || !gate || !up || !down) return fail(Q4B_INVALID_ARGUMENT, "activation, job or output pointer is null");
+    if (m == 0 || k == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    // gate and up must agree (src/metal_runtime.rs:4511-4517)
+    if (gate->output_rows != up->output_rows)
+        return fail(Q4B_WRONG_LENGTH, "up projection rows has %llu elements, expected %llu",
+                    (unsigned long long)up->output_rows, (unsigned long long)gate->output_rows);
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    const uint64_t inter = gate->output_rows;
+    std::vector<Resolved> gu, dn;
+    const q4b_job pair[2] = {*gate, *up};
+    if (int st = resolve_jobs(rt, pair, 2, m, k, &gu)) return st;
+    if (int st = resolve_jobs(rt, down, 1, m, inter, &dn)) return st;
+    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
+    Q4B_CUDA(rt->x_in.ensure((size_t)m * k * esize), "activation buffer");
+    Q4B_CUDA(rt->gate.ensure((size_t)m * inter * 4), "gate buffer");
+    Q4B_CUDA(rt->up.ensure((size_t)m * inter * 4), "up buffer");
+    Q4B_CUDA(rt->hidden.ensure((size_t)m * inter * 4), "hidden buffer");
+    Q4B_CUDA(rt->outs[0].ensure((size_t)m * dn[0].n * 4), "output buffer");
+    cudaStream_t s = rt->stream;
+    Q4B_CUDA(cudaMemcpyAsync(rt->x_in.ptr, x, (size_t)m * k * esize, cudaMemcpyHostToDevice, s), "activation upload");
+    float *gu_out[2] = {(float *)rt->gate.ptr, (float *)rt->up.ptr};
+    int st = enqueue_matmul(rt, rt->x_in.ptr, x_dtype, m, k, gu, gu_out, 0, s);
+    if (st == Q4B_OK) {
+        cudaError_t e = q4k_swiglu(gu_out[0], gu_out[1], m * inter, (float *)rt->hidden.ptr, nullptr, s);
+        rt->launches++;
+        if (e != cudaSuccess) st = fail_cuda(e, "swiglu launch");
+    }
+    float *dn_out = (float *)rt->outs[0].ptr;
+    // the intermediate stays fp32 (the decode chain of the reference, src/metal_runtime.rs:4616-4645)
+    if (st == Q4B_OK) st = enqueue_matmul(rt, rt->hidden.ptr, Q4B_F32, m, inter, dn, &dn_out, 0, s);
+    if (st != Q4B_OK) {
+        cudaStreamSynchronize(s);
+        return st;
+    }
+    Q4B_CUDA(cudaMemcpyAsync(out, dn_out, (size_t)m * dn[0].n * 4, cudaMemcpyDeviceToHost, s), "result download");
+    return finish(rt, s);
+}
+
+extern "C" int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t k, uint64_t row, float *out) {
+    if (int st = check_rt(rt)) return st;
+    if (!job || !out) return fail(Q4B_INVALID_ARGUMENT, "job or output pointer is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    Resolved r;
+    if (int st = resolve_job(rt, *job, k, &r)) return st;
+    if (row >= r.n) return fail(Q4B_WRONG_LENGTH, "row has %llu elements, expected %u", (unsigned long long)row, r.n);
+    Q4B_CUDA(rt->outs[0].ensure((size_t)k * 4), "output buffer");
+    cudaStream_t s = rt->stream;
+    Q4B_CUDA(q4k_dequantize_row(r.w, r.s, r.b, (uint32_t)k, (uint32_t)row, (float *)rt->outs[0].ptr, s), "dequantize launch");
+    rt->launches++;
+    Q4B_CUDA(cudaMemcpyAsync(out, rt->outs[0].ptr, (size_t)k * 4, cudaMemcpyDeviceToHost, s), "result download");
+    return finish(rt, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// synthetic tensors, introspection
+// ------------------------------------------------------------------------------------------
+
+extern "C" int q4b_synth_q4_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, float sigma, uint64_t row0,
+                                   uint64_t rows, uint64_t k, const q4b_job *destination) {
+    if (int st = check_rt(rt)) return st;
+    if (!destination) return fail(Q4B_INVALID_ARGUMENT, "destination job is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    Resolved r;
+    q4b_job job = *destination;
+    job.output_rows = rows;
+    if (int st = resolve_job(rt, job, k, &r)) return st;
+    Q4B_CUDA(q4k_synth_q4(seed, tensor, sigma, row0, rows, (uint32_t)k, (uint8_t *)r.w, (uint8_t *)r.s, (uint8_t *)r.b,
+                          rt->stream),
+             "synthetic weight launch");
+    return finish(rt, rt->stream);
+}
+
+extern "C" int q4b_synth_bf16_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, uint64_t count,
+                                     uint16_t *out_dev, void *stream) {
+    if (int st = check_rt(rt)) return st;
+    if (!out_dev) return fail(Q4B_INVALID_ARGUMENT, "output pointer is null");
+    DeviceGuard guard(rt->device);
+    Q4B_CUDA(q4k_synth_bf16(seed, tensor, count, out_dev, (cudaStream_t)stream), "synthetic activation launch");
+    return Q4B_OK;
+}
+
+extern "C" int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, uint64_t k, const q4b_job *jobs,
+                                     uint32_t n_jobs, char *text, uint32_t text_len) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!text || text_len == 0) return fail(Q4B_INVALID_ARGUMENT, "text buffer is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    std::vector<Resolved> resolved;
+    if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
+    bool aligned = true;
+    for (const Resolved &r : resolved) aligned = aligned && job_is_aligned(r);
+    const uint32_t rows = x_dtype == Q4B_F32 ? 2u : 8u;
+    const uint32_t mb = (uint32_t)(m < rows ? m : rows);
+    const uint32_t v = mb * (x_dtype == Q4B_F32 ? 3u : 1u);
+    snprintf(text, text_len, "stream_mma nt=%d %s launches=%llu", v <= 4 ? 1 : 2, aligned ? "aligned16" : "byte_addressed",
+             (unsigned long long)(((m + rows - 1) / rows) * ((n_jobs + q4::kMaxJobs - 1) / q4::kMaxJobs)));
+    return Q4B_OK;
+}
+
+extern "C" int q4b_profile_begin(q4b_runtime *rt) {
+    if (int st = check_rt(rt)) return st;
+    rt->profiling = true;
+    rt->prof_used = 0;
+    rt->prof_bytes = 0;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes) {
+    if (int st = check_rt(rt)) return st;
+    DeviceGuard guard(rt->device);
+    rt->profiling = false;
+    double total = 0.0;
+    for (size_t i = 0; i + 1 < rt->prof_used; i += 2) {
+        Q4B_CUDA(cudaEventSynchronize(rt->prof_events[i + 1]), "cudaEventSynchronize");
+        float ms = 0.f;
+        Q4B_CUDA(cudaEventElapsedTime(&ms, rt->prof_events[i], rt->prof_events[i + 1]), "cudaEventElapsedTime");
+        total += ms;
+    }
+    if (launches) *launches = rt->prof_used / 2;
+    if (total_ms) *total_ms = total;
+    if (bytes) *bytes = rt->prof_bytes;
+    rt->prof_used = 0;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_launch_count(q4b_runtime *rt, uint64_t *launches) {
+    if (int st = check_rt(rt)) return st;
+    if (!launches) return fail(Q4B_INVALID_ARGUMENT, "launch count pointer is null");
+    *launches = rt->launches;
+    return Q4B_OK;
+}

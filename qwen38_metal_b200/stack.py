@@ -1,0 +1,141 @@
+"""Synthetic decode stack: the projection half of the reference's GPU-resident decode graph.
+
+The reference encodes a whole token as one command buffer (`decode_layers`,
+src/metal_runtime.rs:2022-2081; per layer `encode_decode_linear_layer` :3301-3520 and
+`encode_decode_full_layer` :1567-2020): RMS-norm, three or four projections sharing one activation,
+attention/DeltaNet, output projection, RMS-norm, gate/up, SwiGLU, down. Attention and DeltaNet are
+not projections and are left out; what remains per layer is
+
+    a (bf16, hidden) -> [q,k,v | qkv,z,b,a | gate,up]  one grouped launch, one activation read
+    h = bf16(silu(gate) * up)                          (qwen38_swiglu_rows)
+    d = down(h)                                        fp32
+    a' = bf16(d / rms(d))                              weightless RMS-norm keeps |a| near 1
+
+and after the last layer lm_head -> argmax. Weights are generated in HBM from a seed
+(`CudaRuntime.synth_q4`); every other projection starts two bytes off a 16-byte boundary, which is
+how tensors sit in real safetensors shards. With `world > 1` each rank holds rows
+[floor(r*N/W), floor((r+1)*N/W)) of every projection; the caller gathers `h`, `d` and the argmax
+candidates between ranks (`gather` callbacks), all other work is local.
+
+torch is used for device buffers, streams and CUDA-graph capture only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import capi
+from .runtime import CudaRuntime, MappedQ4AffineJob
+
+HIDDEN = 5120
+INTER = 17408
+VOCAB = 248320
+# Q/K/V of a full-attention layer and the four DeltaNet input projections, then MLP gate and up
+LAYER_ROWS = (6144, 1024, 1024, 6144, 2048, 2048, 48, INTER, INTER)
+GATE, UP = 7, 8
+
+
+def shard_rows(n: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows [begin, end) of an n-row projection owned by `rank` (row sharding; may be empty)."""
+    return (n * rank) // world, (n * (rank + 1)) // world
+
+
+def weight_bytes(n: int, k: int) -> int:
+    """Packed weights + bf16 scales + bf16 biases of an [n][k] projection: 0.5625 bytes per weight."""
+    return n * (k // 2) + 2 * n * (k // 64) * 2
+
+
+def token_bytes(layers: int = 64, hidden: int = HIDDEN, inter: int = INTER, vocab: int = VOCAB,
+                layer_rows=LAYER_ROWS) -> int:
+    per_layer = sum(weight_bytes(n, hidden) for n in layer_rows) + weight_bytes(hidden, inter)
+    return layers * per_layer + weight_bytes(vocab, hidden)
+
+
+@dataclass
+class Projection:
+    job: MappedQ4AffineJob | None  # None when this rank owns no rows
+    rows: int                      # rows held here
+    row0: int                      # first global row held here
+    total_rows: int
+
+
+class SyntheticStack:
+    def __init__(self, rt: CudaRuntime, layers: int = 64, hidden: int = HIDDEN, inter: int = INTER,
+                 vocab: int = VOCAB, layer_rows=LAYER_ROWS, seed: int = 20260, rank: int = 0, world: int = 1,
+                 misalign: int = 2, device: int = 0):
+        self.rt, self.layers, self.hidden, self.inter, self.vocab = rt, layers, hidden, inter, vocab
+        self.layer_rows, self.seed, self.rank, self.world = tuple(layer_rows), seed, rank, world
+        self.device = torch.device("cuda", device)
+        self.gate_i, self.up_i = len(layer_rows) - 2, len(layer_rows) - 1
+        self.bytes_local = 0
+        tensor = 0
+        self.proj: list[list[Projection]] = []
+        self.down: list[Projection] = []
+        for _ in range(layers):
+            row = []
+            for i, n in enumerate(self.layer_rows):
+                row.append(self._make(tensor, n, hidden, misalign if i % 2 else 0))
+                tensor += 1
+            self.proj.append(row)
+            self.down.append(self._make(tensor, hidden, inter, misalign))
+            tensor += 1
+        self.lm_head = self._make(tensor, vocab, hidden, 0)
+        self.x0_tensor = tensor + 1
+        f32, bf16 = torch.float32, torch.bfloat16
+        dev = self.device
+        # activations (replicated on every rank) and per-rank output slices
+        self.x = torch.zeros(hidden, dtype=bf16, device=dev)
+        self.outs = [torch.zeros(max(p.total_rows, 1), dtype=f32, device=dev) for p in self.proj[0]]
+        self.h = torch.zeros(inter, dtype=bf16, device=dev)
+        self.d = torch.zeros(hidden, dtype=f32, device=dev)
+        self.token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.best = torch.zeros(1, dtype=f32, device=dev)
+        self.checksum = torch.zeros(len(self.layer_rows) - 2, dtype=f32, device=dev)
+
+    def _make(self, tensor: int, n: int, k: int, offset: int) -> Projection:
+        r0, r1 = shard_rows(n, self.rank, self.world)
+        rows = r1 - r0
+        if rows == 0:
+            return Projection(None, 0, r0, n)
+        groups = k // 64
+        wb = self.rt.alloc_shard(rows * (k // 2) + offset)
+        sb = self.rt.alloc_shard(rows * groups * 2 + offset)
+        bb = self.rt.alloc_shard(rows * groups * 2 + offset)
+        job = MappedQ4AffineJob(wb, offset, sb, offset, bb, offset, rows, offset % 4 == 0)
+        self.rt.synth_q4(self.seed, tensor, 0.02, r0, rows, k, job)
+        self.bytes_local += weight_bytes(rows, k)
+        return Projection(job, rows, r0, n)
+
+    def reset_input(self, stream: int = 0) -> None:
+        self.rt.synth_bf16(self.seed, self.x0_tensor, self.hidden, self.x.data_ptr(), stream)
+
+    def _grouped(self, x_ptr: int, k: int, projs, outs, stream: int) -> None:
+        jobs, ptrs = [], []
+        for p, o in zip(projs, outs):
+            if p.job is not None:
+                jobs.append(p.job)
+                ptrs.append(o.data_ptr() + 4 * p.row0)
+        if jobs:
+            self.rt.matmul_batch_device(x_ptr, capi.Q4B_BF16, 1, k, jobs, ptrs, 0, stream)
+
+    def decode_token(self, stream: int = 0, gather=None) -> None:
+        """Enqueue one token on `stream` (a raw cudaStream_t). `gather(tensor, proj)` makes a row-sharded
+        output whole on every rank; it is None on one GPU."""
+        rt = self.rt
+        for layer in range(self.layers):
+            projs = self.proj[layer]
+            self._grouped(self.x.data_ptr(), self.hidden, projs, self.outs, stream)
+            gate, up = self.outs[self.gate_i], self.outs[self.up_i]
+            if gather is not None:
+                gather(gate, projs[self.gate_i])
+                gather(up, projs[self.up_i])
+            rt.swiglu_device(gate.data_ptr(), up.data_ptr(), self.inter, 0, self.h.data_ptr(), stream)
+            self._grouped(self.h.data_ptr(), self.inter, [self.down[layer]], [self.d], stream)
+            if gather is not None:
+                gather(self.d, self.down[layer])
+            rt.rms_unit_bf16_device(self.d.data_ptr(), 1, self.hidden, 1e-6, self.x.data_ptr(), stream)
+        p = self.lm_head
+        if p.job is not None:
+            rt.argmax_batch_device(self.x.data_ptr(), capi.Q4B_BF16, 1, self.hidden, p.job, p.row0,
+                                   self.token.data_ptr(), self.best.data_ptr(), stream)

@@ -1,0 +1,10 @@
+// Host build of the device work-split arithmetic (qwen38_metal_b200/csrc/q4_decomp.h) for CPU tests.
+#include "../qwen38_metal_b200/csrc/q4_decomp.h"
+extern "C" {
+uint64_t shim_begin(uint64_t units, uint32_t cpt, uint32_t workers, uint32_t w) { return q4_split_begin(Q4Split{units, cpt, workers}, w); }
+uint32_t shim_owner(uint64_t units, uint32_t cpt, uint32_t workers, uint64_t u) { return q4_split_owner(Q4Split{units, cpt, workers}, u); }
+void shim_contributors(uint64_t units, uint32_t cpt, uint32_t workers, uint32_t tile, uint32_t *first, uint32_t *last) {
+    q4_split_contributors(Q4Split{units, cpt, workers}, tile, first, last);
+}
+uint32_t shim_slot(uint64_t units, uint32_t cpt, uint32_t workers, uint32_t w, uint32_t tile) { return q4_split_slot(Q4Split{units, cpt, workers}, w, tile); }
+}

@@ -1,0 +1,125 @@
+"""The reference's own Q4 tests (src/metal_runtime.rs `mod tests`), run through the C ABI on the GPU.
+
+Same fixtures, same entry points, same alignment cases; the check is the reference's absolute tolerance
+against exactly evaluated outputs (tests/golden/) plus this build's bar: relative L2 <= 1e-5 against the
+CPU oracle's kernel-form arithmetic for fp32 outputs."""
+import numpy as np
+import pytest
+
+import ref_cases as rc
+from helpers import golden_rows, upload_matrix
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_STREAM = 1e-5  # fp32 outputs of the streaming (decode / short batch) family
+
+
+def run_case(rt, case, batch, offset):
+    x = rc.case_input(case, batch)
+    jobs, tensors = [], []
+    for m in case.matrices:
+        q, packed, scales, biases = rc.matrix_tensors(m, case.k)
+        jobs.append(upload_matrix(rt, packed, scales, biases, offset))
+        tensors.append((packed, scales, biases))
+    if batch == 1:
+        outs = [o.reshape(1, -1) for o in rt.q4_affine_matvec_mapped_batch(x.reshape(-1), jobs)]
+    else:
+        outs = rt.q4_affine_matmul_mapped_batch(x.reshape(-1), batch, jobs)
+    return x, outs, tensors
+
+
+@pytest.mark.parametrize("case", [c for c in rc.CASES if c.kind == "matmul"], ids=lambda c: c.name)
+def test_projection_fixtures(case, runtime, oracle, golden):
+    for batch in case.batches:
+        for offset in case.offsets:
+            x, outs, tensors = run_case(runtime, case, batch, offset)
+            for mi, (out, (packed, scales, biases)) in enumerate(zip(outs, tensors)):
+                expected = golden_rows(case, golden[case.name], batch, mi)
+                assert out.shape == expected.shape
+                assert np.max(np.abs(out - expected)) < min(case.tol, 1e-3), (case.name, batch, offset)
+                ref = oracle.matmul_factored_f32(x, packed, scales, biases, packed.shape[0])
+                assert oracle.rel_l2(out, ref) <= REL_L2_STREAM
+
+
+def test_matvec_convenience_entry(runtime, golden):
+    """q4_affine_matvec_matches_cpu_reference, src/metal_runtime.rs:9332-9367: slices in, vector out."""
+    case = rc.CASES[0]
+    q, packed, scales, biases = rc.matrix_tensors(case.matrices[0], case.k)
+    out = runtime.q4_affine_matvec(rc.case_input(case, 1).reshape(-1), packed, scales, biases, 5)
+    assert np.max(np.abs(out - golden_rows(case, golden[case.name], 1)[0])) < 1e-3
+
+
+def test_residual_fixture(runtime, golden):
+    """batch2_rows2_residual_matches_cpu_reference, src/metal_runtime.rs:9903-10052: dst += projection on a
+    non-zero residual, aligned and behind a one-byte prefix, odd row count."""
+    case = next(c for c in rc.CASES if c.kind == "residual")
+    m = case.matrices[0]
+    q, packed, scales, biases = rc.matrix_tensors(m, case.k)
+    base, step = case.extra["initial"]
+    init = (np.float32(base) + np.arange(2 * m.rows, dtype=np.float32) * np.float32(step)).reshape(2, m.rows)
+    for offset in case.offsets:
+        job = upload_matrix(runtime, packed, scales, biases, offset)
+        out = runtime.q4_affine_matmul_add_mapped_batch(rc.case_input(case, 2).reshape(-1), 2, [job], [init])[0]
+        assert np.max(np.abs(out - golden_rows(case, golden[case.name], 2))) < 1e-3
+
+
+def test_argmax_fixture_is_exact(runtime, golden):
+    """q4_argmax_batch_matches_cpu_reference, src/metal_runtime.rs:10453-10500: exact tokens, ties -> lowest."""
+    case = next(c for c in rc.CASES if c.kind == "argmax")
+    q, packed, scales, biases = rc.matrix_tensors(case.matrices[0], case.k)
+    job = upload_matrix(runtime, packed, scales, biases)
+    tokens = runtime.q4_affine_argmax_mapped_batch(rc.case_input(case, 3).reshape(-1), 3, job)
+    assert tokens.tolist() == golden[case.name]["tokens"]["3"]
+
+
+def test_mlp_fixture(runtime, oracle, golden):
+    """fused_q4_mlp_batch_matches_cpu_reference, src/metal_runtime.rs:10726-10910: prefill batch and the
+    single-row decode chain."""
+    case = next(c for c in rc.CASES if c.kind == "mlp")
+    trips = [rc.matrix_tensors(m, 64)[1:] for m in case.matrices]
+    gate, up, down = (upload_matrix(runtime, *t) for t in trips)
+    for batch in case.batches:
+        x = rc.case_input(case, batch)
+        out = runtime.q4_affine_mlp_mapped_batch(x.reshape(-1), batch, gate, up, down)
+        expected = golden_rows(case, golden[case.name], batch)
+        tol = case.extra["decode_tol"] if batch == 1 else case.tol
+        assert np.max(np.abs(out - expected)) < tol
+        assert oracle.rel_l2(out, oracle.mlp(x, *trips, 64, 64, form=0)) < 2e-3
+
+
+def test_incomplete_group_is_rejected(runtime):
+    """q4_affine_matvec_rejects_incomplete_group, src/metal_runtime.rs:11805-11809."""
+    from qwen38_metal_b200.runtime import Q4RuntimeError
+
+    with pytest.raises(Q4RuntimeError) as err:
+        runtime.q4_affine_matvec(np.zeros(63, np.float32), np.zeros(1, np.uint32), np.zeros(1, np.uint16),
+                                 np.zeros(1, np.uint16), 1)
+    assert err.value.kind == "InputNotGrouped"
+
+
+def test_validation_errors_mirror_the_reference(runtime):
+    """validate_mapped_q4_affine_shape, src/metal_runtime.rs:8854-8898."""
+    from qwen38_metal_b200.runtime import DeviceBuffer, MappedQ4AffineJob, Q4RuntimeError
+
+    q, packed, scales, biases = rc.matrix_tensors(rc.CASES[0].matrices[0], 128)
+    job = upload_matrix(runtime, packed, scales, biases)
+    x = np.zeros(128, np.float32)
+    cases = [
+        ([], x, "EmptyDimension"),
+        ([MappedQ4AffineJob(job.weights, 0, job.scales, 0, job.biases, 0, 0)], x, "EmptyDimension"),
+        ([job], np.zeros(96, np.float32), "InputNotGrouped"),
+        ([MappedQ4AffineJob(job.weights, job.weights.length + 1, job.scales, 0, job.biases, 0, 5)], x, "InvalidBufferOffset"),
+        ([MappedQ4AffineJob(job.weights, 4, job.scales, 0, job.biases, 0, 5)], x, "MappedTensorOutOfRange"),
+        ([MappedQ4AffineJob(job.weights, 0, job.scales, 0, job.biases, 0, 6)], x, "MappedTensorOutOfRange"),
+        ([MappedQ4AffineJob(DeviceBuffer(10_000, 8), 0, job.scales, 0, job.biases, 0, 5)], x, "MissingMappedShard"),
+    ]
+    for jobs, xin, kind in cases:
+        with pytest.raises(Q4RuntimeError) as err:
+            runtime.q4_affine_matvec_mapped_batch(xin, jobs)
+        assert err.value.kind == kind, (kind, str(err.value))
+    with pytest.raises(Q4RuntimeError) as err:
+        runtime.buffer_from_slice(np.zeros(0, np.uint8))
+    assert err.value.kind == "EmptyBuffer"
+    # the runtime is still usable after every rejected call
+    out = runtime.q4_affine_matvec_mapped_batch(rc.case_input(rc.CASES[0], 1).reshape(-1), [job])[0]
+    assert np.isfinite(out).all()

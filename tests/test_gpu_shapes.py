@@ -1,0 +1,172 @@
+"""Parity at the benchmark's shapes and at the edges the reference does not test: every byte alignment,
+every short batch width, odd group counts, N = 1, N = 48, fp32 and bf16 activations, the grouped launch,
+and the bit-exactness of the in-HBM generator against the CPU one."""
+import numpy as np
+import pytest
+
+import ref_cases as rc
+from helpers import upload_in_one_shard, upload_matrix
+
+pytestmark = pytest.mark.gpu
+
+SEED = 20260
+
+
+def synth(oracle, tensor, n, k):
+    return oracle.synth_q4(SEED, tensor, n, k)
+
+
+def x_bf16(oracle, tensor, m, k):
+    bits = oracle.synth_bf16(SEED, 1000 + tensor, m * k)
+    return bits, oracle.bf16_to_f32(bits).reshape(m, k)
+
+
+def test_config0_single_matvec_5120(runtime, oracle):
+    """M=1, K=N=5120, bf16 activation: relative L2 <= 1e-5 against the scalar oracle."""
+    trip = synth(oracle, 1, 5120, 5120)
+    bits, xf = x_bf16(oracle, 1, 1, 5120)
+    job = upload_matrix(runtime, *trip)
+    out = runtime.q4_affine_matvec_mapped_batch(bits, [job])[0]
+    ref = oracle.matmul_factored_f32(xf, *trip, 5120, threads=8)[0]
+    assert oracle.rel_l2(out, ref) <= 1e-5
+    truth = oracle.matmul_f64(xf[:, :], trip[0][:256], trip[1][:256], trip[2][:256], 256)[0]
+    assert oracle.rel_l2(out[:256], truth) <= 1e-5
+    # the fp32 entry (the reference's activation type) gives the same numbers for bf16-valued input
+    out32 = runtime.q4_affine_matvec_mapped_batch(xf.reshape(-1), [job])[0]
+    assert oracle.rel_l2(out32, ref) <= 1e-5
+
+
+@pytest.mark.parametrize("offset", [0, 1, 2, 3, 4, 6, 8, 12, 15, 16])
+def test_every_byte_alignment(runtime, oracle, offset):
+    n, k = 53, 640
+    trip = synth(oracle, 10 + offset, n, k)
+    bits, xf = x_bf16(oracle, 2, 2, k)
+    job = upload_matrix(runtime, *trip, offset=offset)
+    out = runtime.q4_affine_matmul_mapped_batch(bits, 2, [job])[0]
+    assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 1e-5
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 7, 8, 9, 16, 17])
+def test_short_batch_widths_bf16(runtime, oracle, m):
+    n, k = 200, 1024
+    trip = synth(oracle, 30, n, k)
+    bits, xf = x_bf16(oracle, 3, m, k)
+    job = upload_matrix(runtime, *trip)
+    out = runtime.q4_affine_matmul_mapped_batch(bits, m, [job])[0]
+    assert out.shape == (m, n)
+    assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 1e-5
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5])
+def test_fp32_activations_lose_nothing(runtime, oracle, m):
+    """fp32 input is split into three bf16 terms on the device; full-mantissa values must survive."""
+    n, k = 77, 512
+    trip = synth(oracle, 31, n, k)
+    rng = np.random.default_rng(5 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32) * np.float32(1.2345678)
+    job = upload_matrix(runtime, *trip)
+    out = runtime.q4_affine_matmul_mapped_batch(x.reshape(-1), m, [job])[0]
+    assert oracle.rel_l2(out, oracle.matmul_factored_f32(x, *trip, n)) <= 1e-5
+    assert oracle.rel_l2(out, oracle.matmul_f64(x, *trip, n)) <= 1e-5
+
+
+@pytest.mark.parametrize("n,k", [(1, 64), (5, 192), (16, 64), (17, 320), (48, 5120), (1000, 128)])
+def test_edge_shapes(runtime, oracle, n, k):
+    trip = synth(oracle, 40 + n, n, k)
+    bits, xf = x_bf16(oracle, 4, 1, k)
+    job = upload_matrix(runtime, *trip)
+    out = runtime.q4_affine_matvec_mapped_batch(bits, [job])[0]
+    assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)[0]) <= 1e-5
+
+
+def test_config1_grouped_decode_shapes(runtime, oracle):
+    """The grouped launches of one decode layer at reduced row counts (same K, same grouping, same mix of
+    aligned and 2-byte-misaligned tensors); full row counts are covered by the property test below."""
+    k = 5120
+    bits, xf = x_bf16(oracle, 5, 1, k)
+    for gi, rows in enumerate([(96, 32, 16), (96, 64, 32, 48), (272, 272)]):
+        trips = [synth(oracle, 100 + 10 * gi + i, n, k) for i, n in enumerate(rows)]
+        jobs = []
+        for i, t in enumerate(trips):  # every other projection starts 2 bytes off
+            jobs.append(upload_matrix(runtime, *t, offset=2 if i % 2 else 0))
+        outs = runtime.q4_affine_matvec_mapped_batch(bits, jobs)
+        for out, t, n in zip(outs, trips, rows):
+            assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *t, n)[0]) <= 1e-5
+    # down projection: K = 17408
+    trip = synth(oracle, 140, 80, 17408)
+    bits, xf = x_bf16(oracle, 6, 1, 17408)
+    out = runtime.q4_affine_matvec_mapped_batch(bits, [upload_matrix(runtime, *trip, offset=2)])[0]
+    assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, 80)[0]) <= 1e-5
+
+
+def test_tensors_of_one_projection_in_one_shard_with_file_offsets(runtime, oracle):
+    """Safetensors layout: weight, scales and biases of several projections packed back to back in one
+    shard whose data region starts at an odd offset (src/model.rs:165-169)."""
+    k = 256
+    trips = [synth(oracle, 150 + i, n, k) for i, n in enumerate((33, 7, 20))]
+    for start in (0, 8 + 1237, 8 + 1238):
+        jobs = upload_in_one_shard(runtime, trips, start)
+        bits, xf = x_bf16(oracle, 7, 3, k)
+        outs = runtime.q4_affine_matmul_mapped_batch(bits, 3, jobs)
+        for out, t in zip(outs, trips):
+            assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *t, t[0].shape[0])) <= 1e-5
+
+
+def test_generator_in_hbm_equals_cpu_generator(runtime, oracle):
+    from qwen38_metal_b200.runtime import MappedQ4AffineJob
+
+    n, k = 40, 320
+    for offset in (0, 2):
+        wb = runtime.alloc_shard(n * k // 2 + 16)
+        sb = runtime.alloc_shard(n * (k // 64) * 2 + 16)
+        bb = runtime.alloc_shard(n * (k // 64) * 2 + 16)
+        job = MappedQ4AffineJob(wb, offset, sb, offset, bb, offset, n, offset == 0)
+        runtime.synth_q4(SEED, 77, 0.02, 0, n, k, job)
+        w, s, b = oracle.synth_q4(SEED, 77, n, k)
+        assert np.array_equal(runtime.read_shard(wb, offset, n * k // 2), w.view(np.uint8).reshape(-1))
+        assert np.array_equal(runtime.read_shard(sb, offset, n * (k // 64) * 2), s.view(np.uint8).reshape(-1))
+        assert np.array_equal(runtime.read_shard(bb, offset, n * (k // 64) * 2), b.view(np.uint8).reshape(-1))
+    # a row slice generated on its own equals the same rows of the whole tensor (row sharding)
+    wb2 = runtime.alloc_shard(10 * k // 2)
+    sb2 = runtime.alloc_shard(10 * (k // 64) * 2)
+    bb2 = runtime.alloc_shard(10 * (k // 64) * 2)
+    runtime.synth_q4(SEED, 77, 0.02, 30, 10, k, MappedQ4AffineJob(wb2, 0, sb2, 0, bb2, 0, 10))
+    assert np.array_equal(runtime.read_shard(wb2, 0, 10 * k // 2), w[30:].view(np.uint8).reshape(-1))
+
+
+def test_full_size_layer_set_by_linearity(runtime, oracle):
+    """Full row counts of one decode layer (N = 6144/1024/1024, 6144/2048/2048/48, 17408 x2) generated in
+    HBM: y(x1 + x2) == y(x1) + y(x2) for bf16 inputs whose sum is exact, sampled rows equal the oracle,
+    and rerunning is bit-reproducible."""
+    from qwen38_metal_b200.runtime import MappedQ4AffineJob
+
+    k = 5120
+    rows = [6144, 1024, 1024, 6144, 2048, 2048, 48, 17408, 17408]
+    jobs = []
+    for i, n in enumerate(rows):
+        off = 2 if i % 2 else 0
+        wb = runtime.alloc_shard(n * k // 2 + off)
+        sb = runtime.alloc_shard(n * (k // 64) * 2 + off)
+        bb = runtime.alloc_shard(n * (k // 64) * 2 + off)
+        job = MappedQ4AffineJob(wb, off, sb, off, bb, off, n, off == 0)
+        runtime.synth_q4(SEED, 200 + i, 0.02, 0, n, k, job)
+        jobs.append(job)
+    rng = np.random.default_rng(3)
+    x1 = (rng.integers(-64, 64, size=k) / 32.0).astype(np.float32)  # 8-bit values: exact in bf16, sums too
+    x2 = (rng.integers(-64, 64, size=k) / 32.0).astype(np.float32)
+    b1, b2, b12 = (oracle.f32_to_bf16(v) for v in (x1, x2, x1 + x2))
+    y1 = runtime.q4_affine_matvec_mapped_batch(b1, jobs)
+    y2 = runtime.q4_affine_matvec_mapped_batch(b2, jobs)
+    y12 = runtime.q4_affine_matvec_mapped_batch(b12, jobs)
+    again = runtime.q4_affine_matvec_mapped_batch(b12, jobs)
+    for a, b, c, d, n in zip(y1, y2, y12, again, rows):
+        assert a.shape == (n,)
+        assert oracle.rel_l2(a + b, c) <= 1e-5
+        assert np.array_equal(c, d)
+    # sampled rows against the oracle: regenerate those rows on the CPU
+    for i in (0, 6, 8):
+        n = rows[i]
+        for r0 in (0, n - 16):
+            w, s, b = oracle.synth_q4(SEED, 200 + i, 16, k, row0=r0)
+            ref = oracle.matmul_factored_f32(x1, w, s, b, 16)[0]
+            assert oracle.rel_l2(y1[i][r0:r0 + 16], ref) <= 1e-5
