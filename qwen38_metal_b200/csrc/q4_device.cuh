@@ -22,9 +22,48 @@ __device__ __forceinline__ uint32_t float_to_bf16_bits(float v) {
 // Streaming 128-bit load: read-only path, no L1 allocation (weights are touched once).
 __device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
+    return v;
+}
+
+// Predicated loads: nothing is fetched and zeros are returned when `pred` is false. Written as
+// predicated instructions so a warp whose lanes disagree does not branch.
+__device__ __forceinline__ uint4 ldg_stream_v4_pred(const void *p, bool pred) {
+    uint4 v;
+    asm("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+        "@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p), "r"((uint32_t)pred));
+    return v;
+}
+
+// cached variant for data that every warp re-reads (prepared activations)
+__device__ __forceinline__ uint4 ldg_v4_pred(const void *p, bool pred) {
+    uint4 v;
+    asm("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+        "@q ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p), "r"((uint32_t)pred));
+    return v;
+}
+
+__device__ __forceinline__ float2 ldg_f2_pred(const float *p, bool pred) {
+    float2 v;
+    asm("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %3, 0;\n\tmov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\t"
+        "@q ld.global.nc.v2.f32 {%0,%1}, [%2];\n\t}"
+        : "=f"(v.x), "=f"(v.y)
+        : "l"(p), "r"((uint32_t)pred));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ldg_u16_pred(const void *p, bool pred) {
+    uint32_t v;
+    asm("{\n\t.reg .pred q;\n\t.reg .b16 h;\n\tsetp.ne.b32 q, %2, 0;\n\tmov.b16 h, 0;\n\t"
+        "@q ld.global.nc.u16 h, [%1];\n\tcvt.u32.u16 %0, h;\n\t}"
+        : "=r"(v)
+        : "l"(p), "r"((uint32_t)pred));
     return v;
 }
 
@@ -58,18 +97,38 @@ __device__ __forceinline__ uint32_t ldg_bf16_bits(const uint8_t *p) {
     return (uint32_t)__ldg(p) | ((uint32_t)__ldg(p + 1) << 8);
 }
 
+// Constants of the nibble conversion, held in registers the compiler cannot see through so that
+// mask-and-or stays one three-input logic instruction (with two immediates it becomes two).
+struct Magic {
+    uint32_t mask;   // 0x000f000f
+    uint32_t bias;   // 0x43004300: bf16 128.0 in both halves
+};
+
+__device__ __forceinline__ Magic make_magic() {
+    Magic m;
+    asm volatile("mov.b32 %0, 0x000f000f;\n\tmov.b32 %1, 0x43004300;" : "=r"(m.mask), "=r"(m.bias));
+    return m;
+}
+
 // Two nibbles of a packed word -> exact bf16x2 (lo half: bits [0,4) of v, hi half: bits [16,20)).
 // 0x4300|q is the bf16 number 128+q (ulp 1 in [128,256)); subtracting 128 is exact.
-__device__ __forceinline__ uint32_t nib2_to_bf16x2(uint32_t v) {
-    uint32_t biased = (v & 0x000f000fu) | 0x43004300u;
-    uint32_t out;
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(out) : "r"(biased), "r"(0x43004300u));
+__device__ __forceinline__ uint32_t nib2_to_bf16x2(uint32_t v, const Magic &m) {
+    uint32_t biased, out;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(v), "r"(m.mask), "r"(m.bias));  // (v & mask) | bias
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(out) : "r"(biased), "r"(m.bias));
     return out;
+}
+
+// Load into registers that keep their old contents when `pred` is false (no zero fill).
+__device__ __forceinline__ void ldg_v4_keep(uint4 &v, const void *p, bool pred) {
+    asm("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t@q ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "l"(p), "r"((uint32_t)pred));
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])

@@ -14,7 +14,7 @@
 // columns, so the fp32 entry points lose nothing.
 //
 // Data movement: each lane streams 16 bytes of two weight rows per K-chunk (128 inputs) with
-// 128-bit no-allocate loads, double-buffered across chunks; the four lanes of a quad cover 64
+// 128-bit no-allocate loads, several chunks in flight per lane; the four lanes of a quad cover 64
 // contiguous bytes of a row. A quad's lanes 0,1 hold affine group A of the chunk and lanes 2,3
 // group B; the activation fragment puts group A's x in MMA columns 0..3 and group B's in 4..7
 // (zero elsewhere), so one MMA yields both groups' sums separately and each lane scales the
@@ -30,7 +30,6 @@
 namespace q4 {
 
 constexpr int kWarpsPerCta = 8;
-constexpr int kBatchChunks = 2;  // K-chunks fetched per lane per pipeline step
 
 // ---------------------------------------------------------------------------------------------
 // Activation preparation: one pass over x that produces what every warp of the projection
@@ -112,145 +111,97 @@ __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const void *__restric
 // The projection kernel.
 // ---------------------------------------------------------------------------------------------
 
+// K-chunks in flight per lane (each: 2 x 16 B of weights + 4 bf16 parameters); two column tiles leave
+// fewer registers for buffers
+template <int NT>
+struct Depth {
+    static constexpr int value = NT == 1 ? 4 : 2;
+};
+
 struct ChunkRegs {
     uint4 wa, wb;       // 16 bytes of tile rows g and g+8
     uint32_t sa, ba;    // scale/bias bits for row g, this lane's group
     uint32_t sb, bb;    // same for row g+8
 };
 
-struct Batch {
-    ChunkRegs c[kBatchChunks];
-    uint32_t tile;      // global tile index
-    uint32_t chunk0;    // first chunk of the batch inside the tile
-    uint32_t nchunks;   // 0 = empty batch
-    uint32_t seg_last;  // batch ends this warp's run of chunks inside the tile
+// Per-lane cursors of one tile segment. They point at the chunk the next refill will fetch for
+// buffer 0; buffer i adds an immediate offset.
+struct LaneView {
+    const uint8_t *wa, *wb;  // this lane's 16 bytes in rows g and g+8
+    const uint8_t *sa, *sb;  // scale of this lane's group (rows g, g+8)
+    const uint8_t *ba, *bb;  // bias likewise
+    uint32_t mis;            // weight address & 15 (byte-addressed path)
 };
 
-template <int NT, bool ALIGNED>
-struct Streamer {
-    const GemvParams &p;
-    const uint32_t lane, g, t;
-    // load cursor
-    uint64_t u, u_end;
-    explicit __device__ Streamer(const GemvParams &params, uint32_t lane_id, uint64_t u0, uint64_t u1)
-        : p(params), lane(lane_id), g(lane_id >> 2), t(lane_id & 3u), u(u0), u_end(u1) {}
-
-    __device__ __forceinline__ uint32_t find_job(uint32_t tile) const {
-        uint32_t j = 0;
-#pragma unroll 1
-        while (j + 1 < p.n_jobs && tile >= p.jobs[j + 1].tile_begin) ++j;
-        return j;
+// Loads never need masking: a chunk past the lane's last group (odd group count) reads the start of
+// the next row, or the padding behind the shard, and is cancelled by zeroed parameters when consumed.
+template <bool ALIGNED>
+__device__ __forceinline__ void load_chunk(ChunkRegs &c, const LaneView &v, int ahead) {
+    const uint32_t woff = (uint32_t)ahead * 64u, poff = (uint32_t)ahead * 4u;
+    if (ALIGNED) {
+        c.wa = ldg_stream_v4(v.wa + woff);
+        c.wb = ldg_stream_v4(v.wb + woff);
+        c.sa = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.sa + poff));
+        c.sb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.sb + poff));
+        c.ba = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.ba + poff));
+        c.bb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.bb + poff));
+    } else {
+        c.wa = ldg_stream_v4_unaligned(v.wa + woff, v.mis);
+        c.wb = ldg_stream_v4_unaligned(v.wb + woff, v.mis);
+        c.sa = ldg_bf16_bits(v.sa + poff);
+        c.sb = ldg_bf16_bits(v.sb + poff);
+        c.ba = ldg_bf16_bits(v.ba + poff);
+        c.bb = ldg_bf16_bits(v.bb + poff);
     }
+}
 
-    // Issue the loads of the next batch (up to kBatchChunks chunks of one tile).
-    __device__ __forceinline__ void fetch(Batch &b) {
-        b.nchunks = 0;
-        if (u >= u_end) return;
-        const uint32_t cpt = p.cpt;
-        uint32_t tile = (uint32_t)(u / cpt);
-        uint32_t chunk0 = (uint32_t)(u - (uint64_t)tile * cpt);
-        uint64_t left = u_end - u;
-        uint32_t in_tile = cpt - chunk0;
-        uint32_t seg_left = left < in_tile ? (uint32_t)left : in_tile;  // chunks left in this segment
-        uint32_t n = seg_left < (uint32_t)kBatchChunks ? seg_left : (uint32_t)kBatchChunks;
-        b.tile = tile;
-        b.chunk0 = chunk0;
-        b.nchunks = n;
-        b.seg_last = (n == seg_left);
-        const uint32_t j = find_job(tile);
-        const GemvJob &job = p.jobs[j];
-        uint32_t row_a = (tile - job.tile_begin) * 16u + g;
-        uint32_t row_b = row_a + 8u;
-        row_a = row_a < job.n ? row_a : job.n - 1u;  // clamp: rows past N read a valid row, never stored
-        row_b = row_b < job.n ? row_b : job.n - 1u;
-        const uint64_t row_bytes = (uint64_t)p.k >> 1;
-        const uint8_t *wa = job.w + (uint64_t)row_a * row_bytes;
-        const uint8_t *wb = job.w + (uint64_t)row_b * row_bytes;
-        const uint64_t pa = (uint64_t)row_a * p.groups, pb = (uint64_t)row_b * p.groups;
-#pragma unroll
-        for (int i = 0; i < kBatchChunks; ++i) {
-            ChunkRegs &c = b.c[i];
-            uint32_t chunk = chunk0 + i;
-            uint32_t group = chunk * 2u + (t >> 1);
-            bool live = ((uint32_t)i < n) && (group < p.groups);
-            if (live) {
-                uint32_t off = chunk * 64u + t * 16u;
-                if (ALIGNED) {
-                    c.wa = ldg_stream_v4(wa + off);
-                    c.wb = ldg_stream_v4(wb + off);
-                    c.sa = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(job.s) + pa + group);
-                    c.sb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(job.s) + pb + group);
-                    c.ba = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(job.b) + pa + group);
-                    c.bb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(job.b) + pb + group);
-                } else {
-                    c.wa = ldg_stream_v4_unaligned(wa + off, job.w_misalign);
-                    c.wb = ldg_stream_v4_unaligned(wb + off, job.w_misalign);
-                    c.sa = ldg_bf16_bits(job.s + 2 * (pa + group));
-                    c.sb = ldg_bf16_bits(job.s + 2 * (pb + group));
-                    c.ba = ldg_bf16_bits(job.b + 2 * (pa + group));
-                    c.bb = ldg_bf16_bits(job.b + 2 * (pb + group));
-                }
-            } else {
-                c.wa = make_uint4(0, 0, 0, 0);
-                c.wb = make_uint4(0, 0, 0, 0);
-                c.sa = c.sb = c.ba = c.bb = 0;
-            }
-        }
-        u += n;
-    }
-};
-
-// one chunk: 8 MMAs per column tile, then the affine step for this lane's group
+// One chunk: 8 MMAs per column tile, then the affine step for the group this lane streamed.
+//   xf    activation fragment registers; lanes that supply zeros never load and keep their zeros
+//   xsrc  this lane's fragment of the chunk for column tile 0 (column tiles are 4*x_col_stride apart)
+//   xs    per-group column sums of the chunk for this lane's group and column pair
+//   live  the lane's group exists in this chunk (false only in the last chunk of an odd group count)
 template <int NT>
-__device__ __forceinline__ void consume_chunk(const GemvParams &p, const ChunkRegs &c, uint32_t chunk, uint32_t g,
-                                              uint32_t t, float (&acc)[NT][4]) {
+__device__ __forceinline__ void consume_chunk(const ChunkRegs &c, bool live, uint4 (&xf)[NT][4], const uint16_t *xsrc,
+                                              uint32_t x_mask, uint32_t x_col_stride, const float *xs,
+                                              const Magic &mg, float (&acc)[NT][4]) {
     const uint32_t wa[4] = {c.wa.x, c.wa.y, c.wa.z, c.wa.w};
     const uint32_t wb[4] = {c.wb.x, c.wb.y, c.wb.z, c.wb.w};
-    const uint32_t group = chunk * 2u + (t >> 1);
-    const bool group_ok = group < p.groups;
-    const float sa = bf16_bits_to_float(c.sa), sb = bf16_bits_to_float(c.sb);
-    const float ba = bf16_bits_to_float(c.ba), bb = bf16_bits_to_float(c.bb);
-    // this lane supplies activation column (g & 3) of a column tile, for the group it streams:
-    // columns 0..3 carry group A (lanes t<2), columns 4..7 group B (lanes t>=2), zero elsewhere
-    const bool x_lane = ((g < 4u) == (t < 2u));
+    const float sa = live ? bf16_bits_to_float(c.sa) : 0.f, sb = live ? bf16_bits_to_float(c.sb) : 0.f;
+    const float ba = live ? bf16_bits_to_float(c.ba) : 0.f, bb = live ? bf16_bits_to_float(c.bb) : 0.f;
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-        const uint32_t v = 4u * j + (g & 3u);
-        uint4 xf[4];
-        if (x_lane && v < p.v_cols && group_ok) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(p.xp + (uint64_t)v * p.k + chunk * 128u + t * 32u);
-            xf[0] = __ldg(src);
-            xf[1] = __ldg(src + 1);
-            xf[2] = __ldg(src + 2);
-            xf[3] = __ldg(src + 3);
-        } else {
-            xf[0] = xf[1] = xf[2] = xf[3] = make_uint4(0, 0, 0, 0);
-        }
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4 *src = reinterpret_cast<const uint4 *>(xsrc + (size_t)(4 * j) * x_col_stride);
+        const bool has_x = (x_mask >> j) & 1u;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const uint32_t xr[4] = {xf[w].x, xf[w].y, xf[w].z, xf[w].w};
+        for (int w = 0; w < 4; ++w) ldg_v4_keep(xf[j][w], src + w, has_x);
+    }
+    float d[NT][4];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t a0 = nib2_to_bf16x2(wa[w] >> (8 * h));
-                uint32_t a2 = nib2_to_bf16x2(wa[w] >> (8 * h + 4));
-                uint32_t a1 = nib2_to_bf16x2(wb[w] >> (8 * h));
-                uint32_t a3 = nib2_to_bf16x2(wb[w] >> (8 * h + 4));
-                mma_bf16_16816(d, a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
+    for (int j = 0; j < NT; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t a0 = nib2_to_bf16x2(wa[w] >> (8 * h), mg);
+            const uint32_t a2 = nib2_to_bf16x2(wa[w] >> (8 * h + 4), mg);
+            const uint32_t a1 = nib2_to_bf16x2(wb[w] >> (8 * h), mg);
+            const uint32_t a3 = nib2_to_bf16x2(wb[w] >> (8 * h + 4), mg);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const uint32_t xr[4] = {xf[j][w].x, xf[j][w].y, xf[j][w].z, xf[j][w].w};
+                mma_bf16_16816(d[j], a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
             }
         }
-        // d[0],d[1]: row g, columns 2t,2t+1; d[2],d[3]: row g+8. Columns map to activation
-        // columns v0 = 4j + 2(t&1), v0+1 for the group this lane streamed.
-        float xs0 = 0.f, xs1 = 0.f;
-        if (group_ok) {
-            const float2 xs = __ldg(reinterpret_cast<const float2 *>(p.xsum + (uint64_t)group * p.vpad + 4u * j + 2u * (t & 1u)));
-            xs0 = xs.x;
-            xs1 = xs.y;
-        }
-        acc[j][0] += d[0] * sa + xs0 * ba;
-        acc[j][1] += d[1] * sa + xs1 * ba;
-        acc[j][2] += d[2] * sb + xs0 * bb;
-        acc[j][3] += d[3] * sb + xs1 * bb;
+    }
+    // d[.][0],d[.][1]: row g, MMA columns 2t,2t+1; d[.][2],d[.][3]: row g+8. Those columns are activation
+    // columns 4j + 2(t&1), +1 of the group this lane streamed.
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const float2 s2 = __ldg(reinterpret_cast<const float2 *>(xs + 4 * j));
+        acc[j][0] = fmaf(d[j][0], sa, fmaf(s2.x, ba, acc[j][0]));
+        acc[j][1] = fmaf(d[j][1], sa, fmaf(s2.y, ba, acc[j][1]));
+        acc[j][2] = fmaf(d[j][2], sb, fmaf(s2.x, bb, acc[j][2]));
+        acc[j][3] = fmaf(d[j][3], sb, fmaf(s2.y, bb, acc[j][3]));
     }
 }
 
@@ -313,72 +264,125 @@ __device__ __forceinline__ void store_tile(const GemvParams &p, uint32_t tile, f
 }
 
 template <int NT, bool ALIGNED>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) q4_gemv_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 2) q4_gemv_kernel(const __grid_constant__ GemvParams p) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t worker = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (worker >= p.workers) return;
     const Q4Split split{p.units, p.cpt, p.workers};
-    const uint64_t u0 = q4_split_begin(split, worker), u1 = q4_split_begin(split, worker + 1);
-    if (u0 >= u1) return;
-
-    Streamer<NT, ALIGNED> stream(p, lane, u0, u1);
-    Batch cur, nxt;
-    stream.fetch(cur);
-    float acc[NT][4];
+    uint64_t u = q4_split_begin(split, worker);
+    const uint64_t u1 = q4_split_begin(split, worker + 1);
+    const uint32_t cpt = p.cpt, groups = p.groups;
+    // this lane supplies activation column (g & 3) of each column tile, for the group it streams:
+    // MMA columns 0..3 carry group A (lanes t<2), columns 4..7 group B (lanes t>=2), zero elsewhere
+    const bool x_lane = ((g < 4u) == (t < 2u));
+    const uint32_t v_first = g & 3u;
+    uint32_t x_mask = 0;  // bit j: this lane loads a fragment for column tile j
 #pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    uint32_t seg_chunk0 = cur.chunk0;  // first chunk of the running segment
-
-    while (cur.nchunks != 0) {
-        stream.fetch(nxt);  // loads for the next step are in flight while this one is consumed
+    for (int j = 0; j < NT; ++j) x_mask |= (x_lane && (v_first + 4u * j < p.v_cols)) ? (1u << j) : 0u;
+    const uint16_t *xfrag0 = p.xp + (size_t)v_first * p.k + t * 32u;
+    const float *xs0 = p.xsum + (size_t)(t >> 1) * p.vpad + 2u * (t & 1u);
+    // chunks whose group exists for this lane: group = 2*chunk + (t>>1) < groups
+    const uint32_t lane_chunks = (groups + 1u - (t >> 1)) >> 1;
+    const Magic mg = make_magic();
+    uint4 xf[NT][4];
 #pragma unroll
-        for (int i = 0; i < kBatchChunks; ++i) {
-            if ((uint32_t)i < cur.nchunks) consume_chunk<NT>(p, cur.c[i], cur.chunk0 + i, g, t, acc);
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) xf[j][w] = make_uint4(0, 0, 0, 0);
+
+    uint32_t tile = (uint32_t)(u / cpt);
+    uint32_t c0 = (uint32_t)(u - (uint64_t)tile * cpt);
+    uint32_t job_index = 0;
+    while (u < u1) {
+        const uint64_t left = u1 - u;
+        const uint32_t c1 = (left < (uint64_t)(cpt - c0)) ? c0 + (uint32_t)left : cpt;
+        while (job_index + 1 < p.n_jobs && tile >= p.jobs[job_index + 1].tile_begin) ++job_index;
+        const GemvJob &job = p.jobs[job_index];
+        LaneView v;
+        {
+            uint32_t row_a = (tile - job.tile_begin) * 16u + g;
+            uint32_t row_b = row_a + 8u;
+            row_a = row_a < job.n ? row_a : job.n - 1u;  // rows past N read a valid row and are never stored
+            row_b = row_b < job.n ? row_b : job.n - 1u;
+            const uint64_t row_bytes = (uint64_t)p.k >> 1;
+            v.wa = job.w + (uint64_t)row_a * row_bytes + t * 16u + c0 * 64u;
+            v.wb = job.w + (uint64_t)row_b * row_bytes + t * 16u + c0 * 64u;
+            const uint64_t pa = ((uint64_t)row_a * groups + (t >> 1)) * 2u + c0 * 4u;
+            const uint64_t pb = ((uint64_t)row_b * groups + (t >> 1)) * 2u + c0 * 4u;
+            v.sa = job.s + pa;
+            v.sb = job.s + pb;
+            v.ba = job.b + pa;
+            v.bb = job.b + pb;
+            v.mis = job.w_misalign;
         }
-        if (cur.seg_last) {
-            const uint32_t tile = cur.tile;
-            const uint32_t seg_end = cur.chunk0 + cur.nchunks;
-            const bool whole = (seg_chunk0 == 0) && (seg_end == p.cpt);
-            uint32_t job_index = stream.find_job(tile);
-            if (whole) {
-                store_tile<NT>(p, tile, acc, g, t, job_index);
-            } else {
-                // split tile: park the lane accumulators, count in, last arrival sums in worker order
-                uint32_t first, last;
-                q4_split_contributors(split, tile, &first, &last);
-                float4 *slot = reinterpret_cast<float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, worker, tile) * NT) * 32u;
+        const uint16_t *xsrc = xfrag0 + c0 * 128u;
+        const float *xs = xs0 + (size_t)c0 * 2u * p.vpad;
+        const uint32_t xs_step = 2u * p.vpad;
+        float acc[NT][4];
 #pragma unroll
-                for (int j = 0; j < NT; ++j) slot[j * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-                __threadfence();
-                __syncwarp();
-                uint32_t arrived = 0;
-                if (lane == 0) arrived = atomicAdd(p.counters + first, 1u);
-                arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                if (arrived == last - first) {
-                    __threadfence();
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+        // kDepth chunks in flight: a buffer is consumed, then refilled with the chunk kDepth ahead
+        constexpr int kDepth = Depth<NT>::value;
+        ChunkRegs buf[kDepth];
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-                    for (uint32_t w = first; w <= last; ++w) {
-                        const float4 *src = reinterpret_cast<const float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, w, tile) * NT) * 32u;
+        for (int i = 0; i < kDepth; ++i)
+            if (c0 + i < c1) load_chunk<ALIGNED>(buf[i], v, i);
+        for (uint32_t c = c0; c < c1; c += kDepth) {
 #pragma unroll
-                        for (int j = 0; j < NT; ++j) {
-                            float4 v = __ldcg(src + j * 32 + lane);
-                            acc[j][0] += v.x;
-                            acc[j][1] += v.y;
-                            acc[j][2] += v.z;
-                            acc[j][3] += v.w;
-                        }
-                    }
-                    store_tile<NT>(p, tile, acc, g, t, job_index);
-                    if (lane == 0) p.counters[first] = 0;  // ready for the next launch
+            for (int i = 0; i < kDepth; ++i) {
+                if (c + i < c1) {
+                    consume_chunk<NT>(buf[i], c + i < lane_chunks, xf, xsrc + i * 128, x_mask, p.k, xs + i * xs_step, mg, acc);
+                    if (c + i + kDepth < c1) load_chunk<ALIGNED>(buf[i], v, i + kDepth);
                 }
             }
-#pragma unroll
-            for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-            seg_chunk0 = nxt.chunk0;
+            v.wa += kDepth * 64;
+            v.wb += kDepth * 64;
+            v.sa += kDepth * 4;
+            v.sb += kDepth * 4;
+            v.ba += kDepth * 4;
+            v.bb += kDepth * 4;
+            xsrc += kDepth * 128;
+            xs += kDepth * xs_step;
         }
-        cur = nxt;
+
+        if (c0 == 0 && c1 == cpt) {
+            store_tile<NT>(p, tile, acc, g, t, job_index);
+        } else {
+            // split tile: park the lane accumulators, count in, last arrival sums in worker order
+            uint32_t first, last;
+            q4_split_contributors(split, tile, &first, &last);
+            float4 *slot = reinterpret_cast<float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, worker, tile) * NT) * 32u;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) slot[j * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+            __threadfence();
+            __syncwarp();
+            uint32_t arrived = 0;
+            if (lane == 0) arrived = atomicAdd(p.counters + first, 1u);
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            if (arrived == last - first) {
+                __threadfence();
+#pragma unroll
+                for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+                for (uint32_t w = first; w <= last; ++w) {
+                    const float4 *src = reinterpret_cast<const float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, w, tile) * NT) * 32u;
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        float4 pv = __ldcg(src + j * 32 + lane);
+                        acc[j][0] += pv.x;
+                        acc[j][1] += pv.y;
+                        acc[j][2] += pv.z;
+                        acc[j][3] += pv.w;
+                    }
+                }
+                store_tile<NT>(p, tile, acc, g, t, job_index);
+                if (lane == 0) p.counters[first] = 0;  // ready for the next launch
+            }
+        }
+        u += c1 - c0;
+        ++tile;
+        c0 = 0;
     }
 }
 

@@ -70,7 +70,7 @@ struct Shard {
     uint64_t bytes = 0;
 };
 
-constexpr uint64_t kShardTailPad = 64;  // the unaligned window load may read 16 bytes past a tensor
+constexpr uint64_t kShardTailPad = 1024;  // prefetch and the unaligned window load may read a little past a tensor
 
 struct Resolved {
     const uint8_t *w, *s, *b;
@@ -177,8 +177,8 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
     const int nt = v_cols <= 4 ? 1 : 2;
     const uint32_t vpad = 4u * nt;
     const uint32_t groups = k / 64;
-    Q4B_CUDA(rt->xp.ensure((size_t)v_cols * k * 2), "activation scratch");
-    Q4B_CUDA(rt->xsum.ensure((size_t)groups * vpad * 4), "activation sum scratch");
+    Q4B_CUDA(rt->xp.ensure((size_t)v_cols * k * 2 + 1024), "activation scratch");  // + over-read slack
+    Q4B_CUDA(rt->xsum.ensure((size_t)groups * vpad * 4 + 1024), "activation sum scratch");
     Q4B_CUDA(q4k_prepare_x(x_dev, f32 ? 1 : 0, m, k, vpad, (uint16_t *)rt->xp.ptr, (float *)rt->xsum.ptr, stream),
              "q4_prepare_x launch");
     rt->launches++;
