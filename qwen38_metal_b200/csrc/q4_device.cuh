@@ -67,6 +67,41 @@ __device__ __forceinline__ uint32_t ldg_u16_pred(const void *p, bool pred) {
     return v;
 }
 
+// Asynchronous 16-byte global -> shared copy (L2 only: the data is streamed once), its group fence and
+// wait, and the matching shared load.
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_16_pred(uint32_t smem_addr, const void *gmem, bool pred) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q cp.async.cg.shared.global [%0], [%1], 16;\n\t}" ::"r"(smem_addr),
+                 "l"(gmem), "r"((uint32_t)pred)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr) : "memory");
+    return v;
+}
+
+// 16 bytes starting `mis` (0..15) bytes into the 32-byte window {lo, hi}
+__device__ __forceinline__ uint4 realign_16(uint4 lo, uint4 hi, uint32_t mis) {
+    uint32_t w0 = lo.x, w1 = lo.y, w2 = lo.z, w3 = lo.w, w4 = hi.x, w5 = hi.y, w6 = hi.z, w7 = hi.w;
+    if (mis & 4) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
+    if (mis & 8) { w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = w6; }
+    const uint32_t sh = (mis & 3u) * 8u;
+    uint4 out;
+    out.x = __funnelshift_r(w0, w1, sh);
+    out.y = __funnelshift_r(w1, w2, sh);
+    out.z = __funnelshift_r(w2, w3, sh);
+    out.w = __funnelshift_r(w3, w4, sh);
+    return out;
+}
+
 // 16 bytes from an arbitrarily aligned address: two aligned 128-bit loads of the enclosing
 // window and a funnel shift (the byte-addressed twin of the aligned load; the reference's
 // qwen38_load_u32, shaders/qwen38.metal:105-110, reads byte by byte instead).
@@ -100,22 +135,34 @@ __device__ __forceinline__ uint32_t ldg_bf16_bits(const uint8_t *p) {
 // Constants of the nibble conversion, held in registers the compiler cannot see through so that
 // mask-and-or stays one three-input logic instruction (with two immediates it becomes two).
 struct Magic {
-    uint32_t mask;   // 0x000f000f
-    uint32_t bias;   // 0x43004300: bf16 128.0 in both halves
+    uint32_t mask_lo;  // 0x000f000f: nibbles at bits [0,4) of each half
+    uint32_t mask_hi;  // 0x00f000f0: nibbles at bits [4,8) of each half
+    uint32_t k1024;    // 0x64006400: fp16 1024.0 in both halves
+    uint32_t sixteenth;  // 0x2c002c00: fp16 1/16
+    uint32_t neg64;    // 0xd400d400: fp16 -64.0
 };
 
 __device__ __forceinline__ Magic make_magic() {
     Magic m;
-    asm volatile("mov.b32 %0, 0x000f000f;\n\tmov.b32 %1, 0x43004300;" : "=r"(m.mask), "=r"(m.bias));
+    asm volatile("mov.b32 %0, 0x000f000f;\n\tmov.b32 %1, 0x00f000f0;\n\tmov.b32 %2, 0x64006400;\n\t"
+                 "mov.b32 %3, 0x2c002c00;\n\tmov.b32 %4, 0xd400d400;"
+                 : "=r"(m.mask_lo), "=r"(m.mask_hi), "=r"(m.k1024), "=r"(m.sixteenth), "=r"(m.neg64));
     return m;
 }
 
-// Two nibbles of a packed word -> exact bf16x2 (lo half: bits [0,4) of v, hi half: bits [16,20)).
-// 0x4300|q is the bf16 number 128+q (ulp 1 in [128,256)); subtracting 128 is exact.
-__device__ __forceinline__ uint32_t nib2_to_bf16x2(uint32_t v, const Magic &m) {
+// Two nibbles of a packed word -> exact fp16x2. 0x6400|q is the fp16 number 1024+q (ulp 1 in
+// [1024,2048)); a nibble four bits higher reads as 1024+16q. Both corrections are exact.
+//   lo: nibbles at bits [0,4) and [16,20)      hi: nibbles at bits [4,8) and [20,24)
+__device__ __forceinline__ uint32_t nib_lo_to_f16x2(uint32_t v, const Magic &m) {
     uint32_t biased, out;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(v), "r"(m.mask), "r"(m.bias));  // (v & mask) | bias
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(out) : "r"(biased), "r"(m.bias));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(v), "r"(m.mask_lo), "r"(m.k1024));  // (v & mask) | 1024
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(out) : "r"(biased), "r"(m.k1024));
+    return out;
+}
+__device__ __forceinline__ uint32_t nib_hi_to_f16x2(uint32_t v, const Magic &m) {
+    uint32_t biased, out;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(v), "r"(m.mask_hi), "r"(m.k1024));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out) : "r"(biased), "r"(m.sixteenth), "r"(m.neg64));  // (1024+16q)/16 - 64
     return out;
 }
 
@@ -126,10 +173,10 @@ __device__ __forceinline__ void ldg_v4_keep(uint4 &v, const void *p, bool pred) 
         : "l"(p), "r"((uint32_t)pred));
 }
 
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
     asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));

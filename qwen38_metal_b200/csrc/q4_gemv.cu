@@ -8,102 +8,134 @@
 //
 // Arithmetic is the reference's factored form (shaders/qwen38.metal:224-241):
 //     y[n] = sum_g ( scale[n,g] * sum_{k in g} x[k]*q[n,k]  +  bias[n,g] * sum_{k in g} x[k] )
-// The inner sums run on the warp-level tensor-core MMA (m16n8k16, bf16 x bf16 -> fp32): q is
-// 0..15 and x is bf16, so every product is exact and only fp32 accumulation rounds. fp32
-// activations are split into three bf16 terms (hi+mid+lo == x exactly) that ride in three MMA
-// columns, so the fp32 entry points lose nothing.
+// The inner sums run on the warp-level tensor-core MMA (m16n8k16, f16 x f16 -> fp32). q is 0..15 and
+// the activation is held as fp16 after an exact power-of-two row scaling (undone in fp32 at the end),
+// so every product is exact and only fp32 accumulation rounds: a bf16 activation fits fp16 exactly
+// within 2^28 of the row maximum, and an fp32 activation is split into three fp16 terms
+// (hi+mid+lo == x) that ride in three MMA columns.
 //
 // Data movement: each lane streams 16 bytes of two weight rows per K-chunk (128 inputs) with
-// 128-bit no-allocate loads, several chunks in flight per lane; the four lanes of a quad cover 64
+// asynchronous global->shared copies issued eight chunks ahead; the four lanes of a quad cover 64
 // contiguous bytes of a row. A quad's lanes 0,1 hold affine group A of the chunk and lanes 2,3
 // group B; the activation fragment puts group A's x in MMA columns 0..3 and group B's in 4..7
 // (zero elsewhere), so one MMA yields both groups' sums separately and each lane scales the
 // sums of the group it loaded.
 //
-// Work is cut into near-equal contiguous unit ranges per warp (q4_decomp.h); tiles split
-// between warps are combined, in worker order, by the last warp to arrive (no spinning).
+// Work is cut into near-equal contiguous unit ranges, one per warp (q4_decomp.h); a warp is a whole
+// thread block, so all its bookkeeping is uniform. Tiles split between warps are combined, in worker
+// order, by the last warp to arrive (no spinning).
 #include "q4_kernels.h"
+
+#include <cuda_fp16.h>
 
 #include "q4_decomp.h"
 #include "q4_device.cuh"
 
 namespace q4 {
 
-constexpr int kWarpsPerCta = 8;
-
 // ---------------------------------------------------------------------------------------------
-// Activation preparation: one pass over x that produces what every warp of the projection
-// kernel needs -- bf16 columns in MMA fragment order and per-group sums.
-//   xp  : [V][K] bf16; inside each block of 8 inputs the order is k0,k4,k1,k5,k2,k6,k3,k7
-//         (lo/hi halves of the registers nib2_to_bf16x2 produces).
-//   xsum: [K/64][vpad] fp32, sum of the column's values over the group; zero for v >= V.
+// Activation preparation: one block per activation row.
+//   xp     : [V][kp] fp16, kp = K rounded up to 128 with zero fill; inside each block of 8 inputs the
+//            order is k0,k4,k1,k5,k2,k6,k3,k7 (the pairing the nibble extraction produces)
+//   xsum   : [kp/64][vpad] fp32, sum of the column's fp16 values over the group; zero where v >= V or
+//            the group is padding
+//   row_inv: [M] fp32, 2^-e of the row: x' = x * 2^e puts the row maximum in [2^14, 2^15)
 // V = M for bf16 input; V = 3M for fp32 input (column 3m+p is part p of row m).
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) q4_prepare_x_kernel(const void *__restrict__ x, int x_is_f32, uint32_t m_rows,
-                                                          uint32_t k, uint32_t vpad, uint16_t *__restrict__ xp,
-                                                          float *__restrict__ xsum) {
-    const uint32_t blocks_per_row = k / 8;
-    const uint32_t groups = k / 64;
+__global__ void __launch_bounds__(256) q4_prepare_x_kernel(const void *__restrict__ x, int x_is_f32, uint32_t k,
+                                                          uint32_t kp, uint32_t vpad, uint16_t *__restrict__ xp,
+                                                          float *__restrict__ xsum, float *__restrict__ row_inv) {
+    __shared__ uint32_t warp_max[8];
+    const uint32_t row = blockIdx.x;
+    const uint32_t blocks = k / 8, blocks_p = kp / 8;
     const uint32_t parts = x_is_f32 ? 3u : 1u;
-    // one thread per 8-input block; the 8 threads of a group are consecutive lanes
-    uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    uint64_t total = (uint64_t)m_rows * blocks_per_row;
-    bool active = idx < total;
-    uint32_t row = active ? (uint32_t)(idx / blocks_per_row) : 0;
-    uint32_t blk = active ? (uint32_t)(idx % blocks_per_row) : 0;
-    float v[8];
-    if (active) {
+    const uint32_t v_cols = gridDim.x * parts;
+    const float *xf = static_cast<const float *>(x) + (uint64_t)row * k;
+    const uint16_t *xb = static_cast<const uint16_t *>(x) + (uint64_t)row * k;
+
+    // pass 1: largest magnitude of the row (as fp32 bits; order-preserving for non-negative values)
+    uint32_t amax = 0;
+    for (uint32_t b = threadIdx.x; b < blocks; b += 256) {
         if (x_is_f32) {
-            const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(x) + (uint64_t)row * k + blk * 8);
-            float4 a = src[0], b = src[1];
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            const float4 *src = reinterpret_cast<const float4 *>(xf + b * 8);
+            float4 lo = src[0], hi = src[1];
+            const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = max(amax, __float_as_uint(v[i]) & 0x7fffffffu);
         } else {
-            uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + (uint64_t)row * k + blk * 8);
-            uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+            uint4 raw = *reinterpret_cast<const uint4 *>(xb + b * 8);
+            const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                v[2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
-                v[2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
+                amax = max(amax, (r[i] << 16) & 0x7fffffffu);
+                amax = max(amax, r[i] & 0x7fff0000u);
             }
         }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.f;
     }
-    for (uint32_t p = 0; p < parts; ++p) {
-        uint32_t bits[8];
-        float part_sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            bits[i] = float_to_bf16_bits(v[i]);
-            float taken = bf16_bits_to_float(bits[i]);
-            part_sum += taken;
-            v[i] -= taken;  // exact: the remainder has at most 16 significant bits
+    for (int off = 16; off > 0; off >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((threadIdx.x & 31u) == 0) warp_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = max(amax, warp_max[i]);
+    int e = 14 - ((int)((amax >> 23) & 0xffu) - 127);  // floor(log2(max)) = exponent field - 127
+    e = amax == 0 ? 0 : max(-100, min(100, e));
+    const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
+    if (threadIdx.x == 0) row_inv[row] = __uint_as_float((uint32_t)(127 - e) << 23);
+
+    // pass 2: scaled fp16 parts in fragment order, group sums
+    for (uint32_t b = threadIdx.x; b < blocks_p; b += 256) {
+        float v[8];
+        if (b < blocks) {
+            if (x_is_f32) {
+                const float4 *src = reinterpret_cast<const float4 *>(xf + b * 8);
+                float4 lo = src[0], hi = src[1];
+                v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            } else {
+                uint4 raw = *reinterpret_cast<const uint4 *>(xb + b * 8);
+                const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    v[2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
+                    v[2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= scale;  // exact: a power of two
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
         }
-        // sum over the 8 consecutive lanes that share a group
-        part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 1);
-        part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 2);
-        part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 4);
-        if (active) {
-            uint32_t col = row * parts + p;
+        for (uint32_t p = 0; p < parts; ++p) {
+            uint32_t bits[8];
+            float part_sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half h = __float2half_rn(v[i]);
+                bits[i] = (uint32_t)__half_as_ushort(h);
+                const float taken = __half2float(h);
+                part_sum += taken;
+                v[i] -= taken;  // exact: the remainder has fewer significant bits than fp32 holds
+            }
+            // the 8 consecutive lanes of a group add up (a row has a whole number of groups)
+            part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 1);
+            part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 2);
+            part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 4);
+            const uint32_t col = row * parts + p;
             uint4 out;
             out.x = bits[0] | (bits[4] << 16);
             out.y = bits[1] | (bits[5] << 16);
             out.z = bits[2] | (bits[6] << 16);
             out.w = bits[3] | (bits[7] << 16);
-            *reinterpret_cast<uint4 *>(xp + (uint64_t)col * k + blk * 8) = out;
-            if ((threadIdx.x & 7u) == 0) xsum[(uint64_t)(blk / 8) * vpad + col] = part_sum;
+            *reinterpret_cast<uint4 *>(xp + (uint64_t)col * kp + b * 8) = out;
+            if ((threadIdx.x & 7u) == 0) xsum[(uint64_t)(b / 8) * vpad + col] = part_sum;
         }
     }
-    // zero the padding columns of xsum (columns V..vpad-1)
-    uint32_t vcols = m_rows * parts;
-    if (vcols < vpad) {
-        uint64_t pad_total = (uint64_t)groups * (vpad - vcols);
-        for (uint64_t i = idx; i < pad_total; i += (uint64_t)gridDim.x * blockDim.x) {
-            uint32_t g = (uint32_t)(i / (vpad - vcols));
-            uint32_t c = vcols + (uint32_t)(i % (vpad - vcols));
-            xsum[(uint64_t)g * vpad + c] = 0.f;
-        }
+    // zero the unused columns of xsum (columns V..vpad-1); block 0 does it for every group
+    if (row == 0 && v_cols < vpad) {
+        const uint32_t pad = vpad - v_cols, groups_p = kp / 64;
+        for (uint32_t i = threadIdx.x; i < groups_p * pad; i += 256) xsum[(uint64_t)(i / pad) * vpad + v_cols + i % pad] = 0.f;
     }
 }
 
@@ -111,63 +143,68 @@ __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const void *__restric
 // The projection kernel.
 // ---------------------------------------------------------------------------------------------
 
-// K-chunks in flight per lane (each: 2 x 16 B of weights + 4 bf16 parameters); two column tiles leave
-// fewer registers for buffers
-template <int NT>
-struct Depth {
-    static constexpr int value = NT == 1 ? 4 : 2;
+// Weight bytes travel global -> shared with per-lane 16-byte async copies (cp.async), kStages chunks
+// ahead of their use, so the number of bytes in flight does not depend on registers. Each warp owns a
+// private ring; a lane reads back what it (or, in the byte-addressed variant, its quad) copied.
+constexpr int kStages = 8;
+// bytes per stage: aligned variant 2 row halves x 32 lanes x 16 B; byte-addressed variant
+// 2 row halves x 8 quads x 5 windows x 16 B (the aligned windows enclosing 64 misaligned bytes)
+constexpr int kStageBytesAligned = 2 * 32 * 16;
+constexpr int kStageBytesWindowed = 2 * 8 * 5 * 16;
+
+struct ParamRegs {
+    uint32_t sa, ba;  // scale/bias bits for row g, this lane's group
+    uint32_t sb, bb;  // same for row g+8
 };
 
-struct ChunkRegs {
-    uint4 wa, wb;       // 16 bytes of tile rows g and g+8
-    uint32_t sa, ba;    // scale/bias bits for row g, this lane's group
-    uint32_t sb, bb;    // same for row g+8
-};
-
-// Per-lane cursors of one tile segment. They point at the chunk the next refill will fetch for
-// buffer 0; buffer i adds an immediate offset.
-struct LaneView {
-    const uint8_t *wa, *wb;  // this lane's 16 bytes in rows g and g+8
-    const uint8_t *sa, *sb;  // scale of this lane's group (rows g, g+8)
-    const uint8_t *ba, *bb;  // bias likewise
-    uint32_t mis;            // weight address & 15 (byte-addressed path)
-};
-
-// Loads never need masking: a chunk past the lane's last group (odd group count) reads the start of
-// the next row, or the padding behind the shard, and is cancelled by zeroed parameters when consumed.
 template <bool ALIGNED>
-__device__ __forceinline__ void load_chunk(ChunkRegs &c, const LaneView &v, int ahead) {
-    const uint32_t woff = (uint32_t)ahead * 64u, poff = (uint32_t)ahead * 4u;
+__device__ __forceinline__ void issue_weights(uint32_t stage_addr, const uint8_t *wa, const uint8_t *wb, uint32_t lane,
+                                              uint32_t t, bool pred) {
     if (ALIGNED) {
-        c.wa = ldg_stream_v4(v.wa + woff);
-        c.wb = ldg_stream_v4(v.wb + woff);
-        c.sa = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.sa + poff));
-        c.sb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.sb + poff));
-        c.ba = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.ba + poff));
-        c.bb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(v.bb + poff));
+        cp_async_16_pred(stage_addr + lane * 16u, wa, pred);
+        cp_async_16_pred(stage_addr + 512u + lane * 16u, wb, pred);
     } else {
-        c.wa = ldg_stream_v4_unaligned(v.wa + woff, v.mis);
-        c.wb = ldg_stream_v4_unaligned(v.wb + woff, v.mis);
-        c.sa = ldg_bf16_bits(v.sa + poff);
-        c.sb = ldg_bf16_bits(v.sb + poff);
-        c.ba = ldg_bf16_bits(v.ba + poff);
-        c.bb = ldg_bf16_bits(v.bb + poff);
+        // quad q = lane>>2 owns 80 bytes per row half: windows 0..3 from its four lanes, window 4 from lane 3
+        const uint32_t a = stage_addr + (lane >> 2) * 80u + t * 16u, b = a + 640u;
+        cp_async_16_pred(a, wa, pred);
+        cp_async_16_pred(b, wb, pred);
+        cp_async_16_pred(a + 16u, wa + 16, pred && t == 3u);
+        cp_async_16_pred(b + 16u, wb + 16, pred && t == 3u);
     }
 }
 
-// One chunk: 8 MMAs per column tile, then the affine step for the group this lane streamed.
-//   xf    activation fragment registers; lanes that supply zeros never load and keep their zeros
-//   xsrc  this lane's fragment of the chunk for column tile 0 (column tiles are 4*x_col_stride apart)
-//   xs    per-group column sums of the chunk for this lane's group and column pair
-//   live  the lane's group exists in this chunk (false only in the last chunk of an odd group count)
+template <bool ALIGNED>
+__device__ __forceinline__ void read_weights(uint32_t stage_addr, uint32_t lane, uint32_t t, uint32_t mis, uint4 &wa,
+                                             uint4 &wb) {
+    if (ALIGNED) {
+        wa = lds_v4(stage_addr + lane * 16u);
+        wb = lds_v4(stage_addr + 512u + lane * 16u);
+    } else {
+        const uint32_t a = stage_addr + (lane >> 2) * 80u + t * 16u;
+        wa = realign_16(lds_v4(a), lds_v4(a + 16u), mis);
+        wb = realign_16(lds_v4(a + 640u), lds_v4(a + 656u), mis);
+    }
+}
+
+template <bool ALIGNED>
+__device__ __forceinline__ void load_params(ParamRegs &c, const uint8_t *sa, const uint8_t *sb, const uint8_t *ba,
+                                            const uint8_t *bb) {
+    if (ALIGNED) {
+        c.sa = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(sa));
+        c.sb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(sb));
+        c.ba = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(ba));
+        c.bb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(bb));
+    } else {
+        c.sa = ldg_bf16_bits(sa);
+        c.sb = ldg_bf16_bits(sb);
+        c.ba = ldg_bf16_bits(ba);
+        c.bb = ldg_bf16_bits(bb);
+    }
+}
+
+// activation fragment of one chunk; lanes that supply zeros never load and keep their zeros
 template <int NT>
-__device__ __forceinline__ void consume_chunk(const ChunkRegs &c, bool live, uint4 (&xf)[NT][4], const uint16_t *xsrc,
-                                              uint32_t x_mask, uint32_t x_col_stride, const float *xs,
-                                              const Magic &mg, float (&acc)[NT][4]) {
-    const uint32_t wa[4] = {c.wa.x, c.wa.y, c.wa.z, c.wa.w};
-    const uint32_t wb[4] = {c.wb.x, c.wb.y, c.wb.z, c.wb.w};
-    const float sa = live ? bf16_bits_to_float(c.sa) : 0.f, sb = live ? bf16_bits_to_float(c.sb) : 0.f;
-    const float ba = live ? bf16_bits_to_float(c.ba) : 0.f, bb = live ? bf16_bits_to_float(c.bb) : 0.f;
+__device__ __forceinline__ void load_x(uint4 (&xf)[NT][4], const uint16_t *xsrc, uint32_t x_mask, uint32_t x_col_stride) {
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const uint4 *src = reinterpret_cast<const uint4 *>(xsrc + (size_t)(4 * j) * x_col_stride);
@@ -175,6 +212,16 @@ __device__ __forceinline__ void consume_chunk(const ChunkRegs &c, bool live, uin
 #pragma unroll
         for (int w = 0; w < 4; ++w) ldg_v4_keep(xf[j][w], src + w, has_x);
     }
+}
+
+// One chunk: 8 MMAs per column tile, then the affine step for the group this lane streamed.
+//   xs  per-group column sums of the chunk for this lane's group and column pair
+template <int NT>
+__device__ __forceinline__ void consume_chunk(const uint4 &cwa, const uint4 &cwb, float sa, float sb, float ba, float bb,
+                                              const uint4 (&xf)[NT][4], const float *xs, const Magic &mg,
+                                              float (&acc)[NT][4]) {
+    const uint32_t wa[4] = {cwa.x, cwa.y, cwa.z, cwa.w};
+    const uint32_t wb[4] = {cwb.x, cwb.y, cwb.z, cwb.w};
     float d[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
@@ -182,14 +229,14 @@ __device__ __forceinline__ void consume_chunk(const ChunkRegs &c, bool live, uin
     for (int w = 0; w < 4; ++w) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t a0 = nib2_to_bf16x2(wa[w] >> (8 * h), mg);
-            const uint32_t a2 = nib2_to_bf16x2(wa[w] >> (8 * h + 4), mg);
-            const uint32_t a1 = nib2_to_bf16x2(wb[w] >> (8 * h), mg);
-            const uint32_t a3 = nib2_to_bf16x2(wb[w] >> (8 * h + 4), mg);
+            // nibble pairs (2h, 2h+4) and (2h+1, 2h+5) of the word, rows g and g+8
+            const uint32_t va = h ? (wa[w] >> 8) : wa[w], vb = h ? (wb[w] >> 8) : wb[w];
+            const uint32_t a0 = nib_lo_to_f16x2(va, mg), a2 = nib_hi_to_f16x2(va, mg);
+            const uint32_t a1 = nib_lo_to_f16x2(vb, mg), a3 = nib_hi_to_f16x2(vb, mg);
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const uint32_t xr[4] = {xf[j][w].x, xf[j][w].y, xf[j][w].z, xf[j][w].w};
-                mma_bf16_16816(d[j], a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
+                mma_f16_16816(d[j], a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
             }
         }
     }
@@ -206,7 +253,7 @@ __device__ __forceinline__ void consume_chunk(const ChunkRegs &c, bool live, uin
 }
 
 // Final step for one tile: fold the two group halves (lanes t and t^2), gather the four
-// columns of each tile into every lane, recombine fp32 splits, store.
+// columns of each tile into every lane, recombine fp32 splits, undo the row scaling, store.
 template <int NT>
 __device__ __forceinline__ void store_tile(const GemvParams &p, uint32_t tile, float (&acc)[NT][4], uint32_t g,
                                            uint32_t t, uint32_t job_index) {
@@ -256,6 +303,7 @@ __device__ __forceinline__ void store_tile(const GemvParams &p, uint32_t tile, f
                     if (c == 3 * m + 1 || c == 3 * m + 2) y += col[c][half];
                 }
             }
+            y *= __ldg(p.row_inv + m);  // exact: a power of two
             float *dst = job.out + (uint64_t)m * job.out_stride + row;
             if (p.accumulate) y += *dst;  // residual form: dst += projection
             *dst = y;
@@ -263,12 +311,57 @@ __device__ __forceinline__ void store_tile(const GemvParams &p, uint32_t tile, f
     }
 }
 
-template <int NT, bool ALIGNED>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, 2) q4_gemv_kernel(const __grid_constant__ GemvParams p) {
-    const uint32_t lane = threadIdx.x & 31u;
+// A whole tile is stored at once; a tile split between warps is parked in the warp's partial slot and
+// summed, in worker order, by the last warp to arrive.
+template <int NT>
+__device__ __forceinline__ void finish_tile(const GemvParams &p, const Q4Split &split, uint32_t worker, uint32_t tile,
+                                            bool whole, float (&acc)[NT][4], uint32_t lane, uint32_t g, uint32_t t,
+                                            uint32_t job_index) {
+    if (whole) {
+        store_tile<NT>(p, tile, acc, g, t, job_index);
+        return;
+    }
+    uint32_t first, last;
+    q4_split_contributors(split, tile, &first, &last);
+    float4 *slot = reinterpret_cast<float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, worker, tile) * NT) * 32u;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) slot[j * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    __threadfence();
+    __syncwarp();
+    uint32_t arrived = 0;
+    if (lane == 0) arrived = atomicAdd(p.counters + first, 1u);
+    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+    if (arrived == last - first) {
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        for (uint32_t w = first; w <= last; ++w) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, w, tile) * NT) * 32u;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float4 pv = __ldcg(src + j * 32 + lane);
+                acc[j][0] += pv.x;
+                acc[j][1] += pv.y;
+                acc[j][2] += pv.z;
+                acc[j][3] += pv.w;
+            }
+        }
+        store_tile<NT>(p, tile, acc, g, t, job_index);
+        if (lane == 0) p.counters[first] = 0;  // ready for the next launch
+    }
+}
+
+// General variant: any byte alignment of the three tensors, any group count. Weights come through
+// aligned 16-byte windows, parameters through plain loads; when the group count is odd, lanes 2,3 of a
+// quad have no group in the last chunk of a row and their parameters are zeroed.
+template <int NT>
+__global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_generic_kernel(const __grid_constant__ GemvParams p) {
+    constexpr bool ALIGNED = false;
+    const bool ODD = (p.groups & 1u) != 0;
+    extern __shared__ __align__(128) uint8_t ring_bytes[];
+    const uint32_t lane = threadIdx.x;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t worker = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-    if (worker >= p.workers) return;
+    const uint32_t worker = blockIdx.x;
     const Q4Split split{p.units, p.cpt, p.workers};
     uint64_t u = q4_split_begin(split, worker);
     const uint64_t u1 = q4_split_begin(split, worker + 1);
@@ -280,16 +373,164 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 2) q4_gemv_kernel(const __g
     uint32_t x_mask = 0;  // bit j: this lane loads a fragment for column tile j
 #pragma unroll
     for (int j = 0; j < NT; ++j) x_mask |= (x_lane && (v_first + 4u * j < p.v_cols)) ? (1u << j) : 0u;
-    const uint16_t *xfrag0 = p.xp + (size_t)v_first * p.k + t * 32u;
+    const uint16_t *xfrag0 = p.xp + (size_t)v_first * p.kp + t * 32u;
     const float *xs0 = p.xsum + (size_t)(t >> 1) * p.vpad + 2u * (t & 1u);
+    const uint32_t xs_step = 2u * p.vpad;
     // chunks whose group exists for this lane: group = 2*chunk + (t>>1) < groups
     const uint32_t lane_chunks = (groups + 1u - (t >> 1)) >> 1;
     const Magic mg = make_magic();
-    uint4 xf[NT][4];
+    constexpr uint32_t kStageBytes = ALIGNED ? kStageBytesAligned : kStageBytesWindowed;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_bytes);
+    uint4 xf[2][NT][4];  // activation fragments of the chunk in use and the next one
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
+    for (int b = 0; b < 2; ++b)
 #pragma unroll
-        for (int w = 0; w < 4; ++w) xf[j][w] = make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) xf[b][j][w] = make_uint4(0, 0, 0, 0);
+
+    uint32_t tile = (uint32_t)(u / cpt);
+    uint32_t c0 = (uint32_t)(u - (uint64_t)tile * cpt);
+    uint32_t job_index = 0;
+    while (u < u1) {
+        const uint64_t left = u1 - u;
+        const uint32_t c1 = (left < (uint64_t)(cpt - c0)) ? c0 + (uint32_t)left : cpt;
+        const uint32_t n = c1 - c0;  // chunks in this segment
+        while (job_index + 1 < p.n_jobs && tile >= p.jobs[job_index + 1].tile_begin) ++job_index;
+        const GemvJob &job = p.jobs[job_index];
+        const uint32_t mis = ALIGNED ? 0u : job.w_misalign;
+        // per-lane cursors at the segment's first chunk
+        const uint8_t *wa, *wb, *sa, *sb, *ba, *bb;
+        {
+            uint32_t row_a = (tile - job.tile_begin) * 16u + g;
+            uint32_t row_b = row_a + 8u;
+            row_a = row_a < job.n ? row_a : job.n - 1u;  // rows past N read a valid row and are never stored
+            row_b = row_b < job.n ? row_b : job.n - 1u;
+            const uint64_t row_bytes = (uint64_t)p.k >> 1;
+            wa = job.w + (uint64_t)row_a * row_bytes + t * 16u + c0 * 64u - mis;  // byte-addressed: the aligned window
+            wb = job.w + (uint64_t)row_b * row_bytes + t * 16u + c0 * 64u - mis;
+            const uint64_t pa = ((uint64_t)row_a * groups + (t >> 1)) * 2u + c0 * 4u;
+            const uint64_t pb = ((uint64_t)row_b * groups + (t >> 1)) * 2u + c0 * 4u;
+            sa = job.s + pa;
+            sb = job.s + pb;
+            ba = job.b + pa;
+            bb = job.b + pb;
+        }
+        const uint16_t *xsrc = xfrag0 + c0 * 128u;
+        const float *xs = xs0 + (size_t)c0 * xs_step;
+        const uint32_t live_n = lane_chunks > c0 ? lane_chunks - c0 : 0u;  // segment chunks with a group for this lane
+        float acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+        // prologue: weights of the first kStages chunks, parameters of the first two, activations of the first
+#pragma unroll
+        for (int i = 0; i < kStages; ++i) {
+            issue_weights<ALIGNED>(ring + i * kStageBytes, wa + i * 64, wb + i * 64, lane, t, (uint32_t)i < n);
+            if (i == 3 || i == 7) cp_async_commit();  // one group per half of the ring
+        }
+        ParamRegs prm[2];
+        load_params<ALIGNED>(prm[0], sa, sb, ba, bb);
+        load_params<ALIGNED>(prm[1], sa + 4, sb + 4, ba + 4, bb + 4);
+        if (ODD) {
+            if (0 >= live_n) prm[0].sa = prm[0].sb = prm[0].ba = prm[0].bb = 0;
+            if (1 >= live_n) prm[1].sa = prm[1].sb = prm[1].ba = prm[1].bb = 0;
+        }
+        load_x<NT>(xf[0], xsrc, x_mask, p.kp);
+
+        // Four chunks are consumed, then their four stages are refilled in one burst (chunks 8..11 ahead):
+        // the burst asks for 256 contiguous bytes of each row at once, which keeps DRAM pages open.
+        uint32_t half = 0;  // which half of the ring the next four chunks use
+        for (uint32_t ci = 0; ci < n; ci += 4) {
+            const uint32_t stage0 = ring + half * (4 * kStageBytes);
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                if (ci + s < n) {
+                    const int b = s & 1;
+                    // each half of the ring is one copy group; only the other half's group may still be pending
+                    if (s == 0) {
+                        cp_async_wait<1>();
+                        if (!ALIGNED) __syncwarp();  // a lane reads windows its quad neighbours copied
+                    }
+                    uint4 cwa, cwb;
+                    read_weights<ALIGNED>(stage0 + s * kStageBytes, lane, t, mis, cwa, cwb);
+                    load_x<NT>(xf[b ^ 1], xsrc + (s + 1) * 128, x_mask, p.kp);  // reads past the segment are harmless
+                    consume_chunk<NT>(cwa, cwb, bf16_bits_to_float(prm[b].sa), bf16_bits_to_float(prm[b].sb),
+                                      bf16_bits_to_float(prm[b].ba), bf16_bits_to_float(prm[b].bb), xf[b], xs + s * xs_step, mg, acc);
+                    load_params<ALIGNED>(prm[b], sa + (s + 2) * 4, sb + (s + 2) * 4, ba + (s + 2) * 4, bb + (s + 2) * 4);
+                    if (ODD) {
+                        if (ci + s + 2 >= live_n) prm[b].sa = prm[b].sb = prm[b].ba = prm[b].bb = 0;
+                    }
+                }
+            }
+            if (!ALIGNED) __syncwarp();  // everyone has read before the stages are refilled
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                issue_weights<ALIGNED>(stage0 + s * kStageBytes, wa + (s + kStages) * 64, wb + (s + kStages) * 64, lane, t,
+                                       ci + s + kStages < n);
+            cp_async_commit();
+            wa += 4 * 64;
+            wb += 4 * 64;
+            sa += 16;
+            sb += 16;
+            ba += 16;
+            bb += 16;
+            xsrc += 4 * 128;
+            xs += 4 * xs_step;
+            half ^= 1u;
+        }
+        cp_async_wait<0>();
+
+        finish_tile<NT>(p, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index);
+        u += n;
+        ++tile;
+        c0 = 0;
+    }
+}
+
+// Fast variant: weights, scales and biases start on 16-byte boundaries and the group count is a
+// multiple of 8 (K % 512 == 0), so parameters ride the same async path as the weights: per four chunks
+// one 16-byte copy per row and array (8 groups = 4 chunks), read back with one 128-bit shared load.
+// Shared memory per warp: 8 weight stages of 1 KB and 2 parameter stages of 512 B.
+constexpr int kFastRingBytes = kStages * kStageBytesAligned + 2 * 512;
+
+// bf16 parameter of chunk slot `w4` for this lane's group parity, as fp32: picks one half of the
+// 32-bit word and moves it to the top (sel = 0x1044 for the low half, 0x3244 for the high half)
+__device__ __forceinline__ float param_of(uint32_t word, uint32_t sel) {
+    return __uint_as_float(__byte_perm(word, 0u, sel));
+}
+
+template <int NT>
+__global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_fast_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(128) uint8_t ring_bytes[];
+    const uint32_t lane = threadIdx.x;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t worker = blockIdx.x;
+    const Q4Split split{p.units, p.cpt, p.workers};
+    uint64_t u = q4_split_begin(split, worker);
+    const uint64_t u1 = q4_split_begin(split, worker + 1);
+    const uint32_t cpt = p.cpt, groups = p.groups;
+    const bool x_lane = ((g < 4u) == (t < 2u));
+    const uint32_t v_first = g & 3u;
+    uint32_t x_mask = 0;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) x_mask |= (x_lane && (v_first + 4u * j < p.v_cols)) ? (1u << j) : 0u;
+    const uint16_t *xfrag0 = p.xp + (size_t)v_first * p.kp + t * 32u;
+    const float *xs0 = p.xsum + (size_t)(t >> 1) * p.vpad + 2u * (t & 1u);
+    const uint32_t xs_step = 2u * p.vpad;
+    const uint32_t half_sel = (t >> 1) ? 0x3244u : 0x1044u;
+    const Magic mg = make_magic();
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_bytes);
+    const uint32_t pring = ring + kStages * kStageBytesAligned;
+    // parameter copies: lane l moves 16 bytes of row (l & 15) of array (l >> 4: scales, biases)
+    const uint32_t prow = lane & 15u;
+    uint4 xf[2][NT][4];
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) xf[b][j][w] = make_uint4(0, 0, 0, 0);
 
     uint32_t tile = (uint32_t)(u / cpt);
     uint32_t c0 = (uint32_t)(u - (uint64_t)tile * cpt);
@@ -299,87 +540,84 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 2) q4_gemv_kernel(const __g
         const uint32_t c1 = (left < (uint64_t)(cpt - c0)) ? c0 + (uint32_t)left : cpt;
         while (job_index + 1 < p.n_jobs && tile >= p.jobs[job_index + 1].tile_begin) ++job_index;
         const GemvJob &job = p.jobs[job_index];
-        LaneView v;
+        const uint32_t cbase = c0 & ~3u;  // chunks are handled in aligned groups of four
+        // per-lane cursors at chunk cbase
+        const uint8_t *wa, *wb, *pp;
         {
-            uint32_t row_a = (tile - job.tile_begin) * 16u + g;
-            uint32_t row_b = row_a + 8u;
+            const uint32_t row0 = (tile - job.tile_begin) * 16u;
+            uint32_t row_a = row0 + g, row_b = row0 + g + 8u, row_p = row0 + prow;
             row_a = row_a < job.n ? row_a : job.n - 1u;  // rows past N read a valid row and are never stored
             row_b = row_b < job.n ? row_b : job.n - 1u;
+            row_p = row_p < job.n ? row_p : job.n - 1u;
             const uint64_t row_bytes = (uint64_t)p.k >> 1;
-            v.wa = job.w + (uint64_t)row_a * row_bytes + t * 16u + c0 * 64u;
-            v.wb = job.w + (uint64_t)row_b * row_bytes + t * 16u + c0 * 64u;
-            const uint64_t pa = ((uint64_t)row_a * groups + (t >> 1)) * 2u + c0 * 4u;
-            const uint64_t pb = ((uint64_t)row_b * groups + (t >> 1)) * 2u + c0 * 4u;
-            v.sa = job.s + pa;
-            v.sb = job.s + pb;
-            v.ba = job.b + pa;
-            v.bb = job.b + pb;
-            v.mis = job.w_misalign;
+            wa = job.w + (uint64_t)row_a * row_bytes + t * 16u + cbase * 64u;
+            wb = job.w + (uint64_t)row_b * row_bytes + t * 16u + cbase * 64u;
+            pp = ((lane >> 4) ? job.b : job.s) + ((uint64_t)row_p * groups) * 2u + cbase * 4u;
         }
-        const uint16_t *xsrc = xfrag0 + c0 * 128u;
-        const float *xs = xs0 + (size_t)c0 * 2u * p.vpad;
-        const uint32_t xs_step = 2u * p.vpad;
+        const uint16_t *xsrc = xfrag0 + cbase * 128u;
+        const float *xs = xs0 + (size_t)cbase * xs_step;
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
-        // kDepth chunks in flight: a buffer is consumed, then refilled with the chunk kDepth ahead
-        constexpr int kDepth = Depth<NT>::value;
-        ChunkRegs buf[kDepth];
+        // prologue: the first two groups of four chunks (weights of chunks in [c0,c1) only), first activations
 #pragma unroll
-        for (int i = 0; i < kDepth; ++i)
-            if (c0 + i < c1) load_chunk<ALIGNED>(buf[i], v, i);
-        for (uint32_t c = c0; c < c1; c += kDepth) {
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int i = 0; i < kDepth; ++i) {
-                if (c + i < c1) {
-                    consume_chunk<NT>(buf[i], c + i < lane_chunks, xf, xsrc + i * 128, x_mask, p.k, xs + i * xs_step, mg, acc);
-                    if (c + i + kDepth < c1) load_chunk<ALIGNED>(buf[i], v, i + kDepth);
-                }
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t c = cbase + 4 * h + s;
+                const uint32_t stage = ring + (4 * h + s) * kStageBytesAligned;
+                cp_async_16_pred(stage + lane * 16u, wa + (4 * h + s) * 64, c >= c0 && c < c1);
+                cp_async_16_pred(stage + 512u + lane * 16u, wb + (4 * h + s) * 64, c >= c0 && c < c1);
             }
-            v.wa += kDepth * 64;
-            v.wb += kDepth * 64;
-            v.sa += kDepth * 4;
-            v.sb += kDepth * 4;
-            v.ba += kDepth * 4;
-            v.bb += kDepth * 4;
-            xsrc += kDepth * 128;
-            xs += kDepth * xs_step;
+            cp_async_16_pred(pring + h * 512u + lane * 16u, pp + h * 16, cbase + 4 * h < c1);
+            cp_async_commit();
         }
+        if (c0 & 1u) load_x<NT>(xf[1], xsrc + (c0 - cbase) * 128u, x_mask, p.kp);
+        else load_x<NT>(xf[0], xsrc + (c0 - cbase) * 128u, x_mask, p.kp);
 
-        if (c0 == 0 && c1 == cpt) {
-            store_tile<NT>(p, tile, acc, g, t, job_index);
-        } else {
-            // split tile: park the lane accumulators, count in, last arrival sums in worker order
-            uint32_t first, last;
-            q4_split_contributors(split, tile, &first, &last);
-            float4 *slot = reinterpret_cast<float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, worker, tile) * NT) * 32u;
+        uint32_t half = 0;
+        for (uint32_t cg = cbase; cg < c1; cg += 4) {
+            const uint32_t stage0 = ring + half * (4 * kStageBytesAligned);
+            const uint32_t pstage = pring + half * 512u;
+            cp_async_wait<1>();  // this half's group has landed; the other half's may be pending
+            __syncwarp();        // parameters were copied by other lanes
+            const uint4 psa = lds_v4(pstage + g * 16u), psb = lds_v4(pstage + (g + 8u) * 16u);
+            const uint4 pba = lds_v4(pstage + 256u + g * 16u), pbb = lds_v4(pstage + 256u + (g + 8u) * 16u);
+            const uint32_t wsa[4] = {psa.x, psa.y, psa.z, psa.w}, wsb[4] = {psb.x, psb.y, psb.z, psb.w};
+            const uint32_t wba[4] = {pba.x, pba.y, pba.z, pba.w}, wbb[4] = {pbb.x, pbb.y, pbb.z, pbb.w};
 #pragma unroll
-            for (int j = 0; j < NT; ++j) slot[j * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-            __threadfence();
-            __syncwarp();
-            uint32_t arrived = 0;
-            if (lane == 0) arrived = atomicAdd(p.counters + first, 1u);
-            arrived = __shfl_sync(0xffffffffu, arrived, 0);
-            if (arrived == last - first) {
-                __threadfence();
-#pragma unroll
-                for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-                for (uint32_t w = first; w <= last; ++w) {
-                    const float4 *src = reinterpret_cast<const float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, w, tile) * NT) * 32u;
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        float4 pv = __ldcg(src + j * 32 + lane);
-                        acc[j][0] += pv.x;
-                        acc[j][1] += pv.y;
-                        acc[j][2] += pv.z;
-                        acc[j][3] += pv.w;
-                    }
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t c = cg + s;
+                if (c >= c0 && c < c1) {
+                    const int b = s & 1;
+                    const uint32_t stage = stage0 + s * kStageBytesAligned;
+                    const uint4 cwa = lds_v4(stage + lane * 16u), cwb = lds_v4(stage + 512u + lane * 16u);
+                    load_x<NT>(xf[b ^ 1], xsrc + (s + 1) * 128, x_mask, p.kp);  // reads past the segment are harmless
+                    consume_chunk<NT>(cwa, cwb, param_of(wsa[s], half_sel), param_of(wsb[s], half_sel),
+                                      param_of(wba[s], half_sel), param_of(wbb[s], half_sel), xf[b], xs + s * xs_step, mg, acc);
                 }
-                store_tile<NT>(p, tile, acc, g, t, job_index);
-                if (lane == 0) p.counters[first] = 0;  // ready for the next launch
             }
+            __syncwarp();  // every lane is done with this half before it is refilled
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t stage = stage0 + s * kStageBytesAligned;
+                const bool more = cg + 8 + s < c1;
+                cp_async_16_pred(stage + lane * 16u, wa + (8 + s) * 64, more);
+                cp_async_16_pred(stage + 512u + lane * 16u, wb + (8 + s) * 64, more);
+            }
+            cp_async_16_pred(pstage + lane * 16u, pp + 32, cg + 8 < c1);
+            cp_async_commit();
+            wa += 4 * 64;
+            wb += 4 * 64;
+            pp += 16;
+            xsrc += 4 * 128;
+            xs += 4 * xs_step;
+            half ^= 1u;
         }
+        cp_async_wait<0>();
+        __syncwarp();
+        finish_tile<NT>(p, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index);
         u += c1 - c0;
         ++tile;
         c0 = 0;
@@ -392,25 +630,21 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 2) q4_gemv_kernel(const __g
 // Host launchers
 // ---------------------------------------------------------------------------------------------
 
-extern "C" cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t k, uint32_t vpad,
-                                     uint16_t *xp, float *xsum, cudaStream_t stream) {
-    uint64_t total = (uint64_t)m_rows * (k / 8);
-    uint32_t blocks = (uint32_t)((total + 255) / 256);
-    q4::q4_prepare_x_kernel<<<blocks, 256, 0, stream>>>(x, x_is_f32, m_rows, k, vpad, xp, xsum);
+extern "C" cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t k, uint32_t kp, uint32_t vpad,
+                                     uint16_t *xp, float *xsum, float *row_inv, cudaStream_t stream) {
+    q4::q4_prepare_x_kernel<<<m_rows, 256, 0, stream>>>(x, x_is_f32, k, kp, vpad, xp, xsum, row_inv);
     return cudaGetLastError();
 }
 
-extern "C" int q4k_gemv_warps_per_cta(void) { return q4::kWarpsPerCta; }
+namespace {
 
-extern "C" uint32_t q4k_gemv_occupancy(int column_tiles, int aligned) {
-    using namespace q4;
+constexpr size_t kGenericRingBytes = (size_t)q4::kStages * q4::kStageBytesWindowed;
+
+template <int NT>
+uint32_t occupancy_of(bool fast) {
     int blocks = 0;
-    cudaError_t e = cudaErrorInvalidValue;
-    const int threads = kWarpsPerCta * 32;
-    if (column_tiles == 1 && aligned) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4_gemv_kernel<1, true>, threads, 0);
-    if (column_tiles == 1 && !aligned) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4_gemv_kernel<1, false>, threads, 0);
-    if (column_tiles == 2 && aligned) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4_gemv_kernel<2, true>, threads, 0);
-    if (column_tiles == 2 && !aligned) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4_gemv_kernel<2, false>, threads, 0);
+    cudaError_t e = fast ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4::q4_gemv_fast_kernel<NT>, 32, q4::kFastRingBytes)
+                         : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4::q4_gemv_generic_kernel<NT>, 32, kGenericRingBytes);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return 0;
@@ -418,16 +652,25 @@ extern "C" uint32_t q4k_gemv_occupancy(int column_tiles, int aligned) {
     return blocks > 0 ? (uint32_t)blocks : 0u;
 }
 
-extern "C" cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int aligned, uint32_t ctas,
-                                cudaStream_t stream) {
-    using namespace q4;
-    dim3 grid(ctas), block(kWarpsPerCta * 32);
+}  // namespace
+
+// resident warps (= blocks) per SM of a variant
+extern "C" uint32_t q4k_gemv_occupancy(int column_tiles, int fast) {
+    if (column_tiles == 1) return occupancy_of<1>(fast != 0);
+    if (column_tiles == 2) return occupancy_of<2>(fast != 0);
+    return 0;
+}
+
+// one warp per block: `workers` blocks. fast: every job of the launch meets the fast variant's
+// alignment and shape conditions.
+extern "C" cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int fast, cudaStream_t stream) {
+    const dim3 grid(params->workers), block(32);
     if (column_tiles == 1) {
-        if (aligned) q4_gemv_kernel<1, true><<<grid, block, 0, stream>>>(*params);
-        else q4_gemv_kernel<1, false><<<grid, block, 0, stream>>>(*params);
+        if (fast) q4::q4_gemv_fast_kernel<1><<<grid, block, q4::kFastRingBytes, stream>>>(*params);
+        else q4::q4_gemv_generic_kernel<1><<<grid, block, kGenericRingBytes, stream>>>(*params);
     } else if (column_tiles == 2) {
-        if (aligned) q4_gemv_kernel<2, true><<<grid, block, 0, stream>>>(*params);
-        else q4_gemv_kernel<2, false><<<grid, block, 0, stream>>>(*params);
+        if (fast) q4::q4_gemv_fast_kernel<2><<<grid, block, q4::kFastRingBytes, stream>>>(*params);
+        else q4::q4_gemv_generic_kernel<2><<<grid, block, kGenericRingBytes, stream>>>(*params);
     } else {
         return cudaErrorInvalidValue;
     }

@@ -24,17 +24,19 @@ struct GemvJob {
 struct GemvParams {
     GemvJob jobs[kMaxJobs];
     uint32_t n_jobs;
-    const uint16_t *xp;    // prepared activation columns, [v_cols][k] bf16 in fragment order
-    const float *xsum;     // [k/64][vpad] per-group column sums
+    const uint16_t *xp;    // prepared activation columns, [v_cols][kp] fp16 in fragment order, row-scaled
+    const float *xsum;     // [kp/64][vpad] per-group column sums
+    const float *row_inv;  // [m_rows] inverse of the power-of-two row scaling
     uint32_t v_cols;       // activation columns in use (m_rows, or 3*m_rows for fp32 input)
     uint32_t vpad;         // 4 * column tiles
     uint32_t m_rows;       // activation rows
     uint32_t x_is_f32;     // columns are hi/mid/lo splits of fp32 rows
     uint32_t accumulate;   // out += projection (residual form) instead of out = projection
     uint32_t k;            // input elements
+    uint32_t kp;           // k rounded up to 128 (row stride of xp)
     uint32_t groups;       // k / 64
     uint32_t cpt;          // K-chunks (128 inputs) per tile = ceil(groups / 2)
-    uint32_t workers;      // warps in the grid
+    uint32_t workers;      // warps (= blocks) in the grid
     uint64_t units;        // tiles * cpt
     float *partials;       // [workers][2][column tiles][32][4] fp32 scratch for split tiles
     unsigned int *counters;  // [workers], zero between launches
@@ -43,11 +45,10 @@ struct GemvParams {
 }  // namespace q4
 
 extern "C" {
-cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t k, uint32_t vpad, uint16_t *xp,
-                          float *xsum, cudaStream_t stream);
-int q4k_gemv_warps_per_cta(void);
-cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int aligned, uint32_t ctas, cudaStream_t stream);
-uint32_t q4k_gemv_occupancy(int column_tiles, int aligned);  // resident CTAs per SM, 0 on error
+cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t k, uint32_t kp, uint32_t vpad,
+                          uint16_t *xp, float *xsum, float *row_inv, cudaStream_t stream);
+cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int aligned, cudaStream_t stream);  // one warp per block
+uint32_t q4k_gemv_occupancy(int column_tiles, int aligned);  // resident warps per SM, 0 on error
 
 cudaError_t q4k_swiglu(const float *gate, const float *up, uint64_t count, float *out_f32, uint16_t *out_bf16,
                        cudaStream_t stream);

@@ -87,9 +87,9 @@ struct q4b_runtime {
     cudaStream_t stream = nullptr;
     std::mutex mu;
     std::vector<Shard> shards;
-    uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident CTAs per SM
+    uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident warps per SM
     uint32_t max_workers = 0;
-    Pool x_in, xp, xsum, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
+    Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
     Pool outs[q4::kMaxJobs];
     uint64_t launches = 0;
     std::string force_variant;
@@ -164,8 +164,9 @@ int resolve_jobs(q4b_runtime *rt, const q4b_job *jobs, uint32_t n_jobs, uint64_t
     return Q4B_OK;
 }
 
-bool job_is_aligned(const Resolved &r) {
-    return ((uintptr_t)r.w & 15u) == 0 && ((uintptr_t)r.s & 1u) == 0 && ((uintptr_t)r.b & 1u) == 0;
+// the fast kernel variant copies parameters in 16-byte pieces of 8 groups
+bool job_is_fast(const Resolved &r, uint32_t groups) {
+    return (((uintptr_t)r.w | (uintptr_t)r.s | (uintptr_t)r.b) & 15u) == 0 && groups % 8u == 0;
 }
 
 // One streaming launch: up to kMaxJobs projections, up to 8 bf16 (2 fp32) activation rows.
@@ -177,74 +178,78 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
     const int nt = v_cols <= 4 ? 1 : 2;
     const uint32_t vpad = 4u * nt;
     const uint32_t groups = k / 64;
-    Q4B_CUDA(rt->xp.ensure((size_t)v_cols * k * 2 + 1024), "activation scratch");  // + over-read slack
-    Q4B_CUDA(rt->xsum.ensure((size_t)groups * vpad * 4 + 1024), "activation sum scratch");
-    Q4B_CUDA(q4k_prepare_x(x_dev, f32 ? 1 : 0, m, k, vpad, (uint16_t *)rt->xp.ptr, (float *)rt->xsum.ptr, stream),
+    const uint32_t kp = (k + 127u) & ~127u;
+    Q4B_CUDA(rt->xp.ensure((size_t)v_cols * kp * 2 + 1024), "activation scratch");  // + over-read slack
+    Q4B_CUDA(rt->xsum.ensure((size_t)(kp / 64) * vpad * 4 + 1024), "activation sum scratch");
+    Q4B_CUDA(rt->row_inv.ensure(256), "row scale scratch");
+    Q4B_CUDA(q4k_prepare_x(x_dev, f32 ? 1 : 0, m, k, kp, vpad, (uint16_t *)rt->xp.ptr, (float *)rt->xsum.ptr,
+                           (float *)rt->row_inv.ptr, stream),
              "q4_prepare_x launch");
     rt->launches++;
 
-    q4::GemvParams p;
-    memset(&p, 0, sizeof p);
-    bool aligned = true;
-    uint32_t tiles = 0;
-    for (uint32_t i = 0; i < n_jobs; ++i) {
-        q4::GemvJob &j = p.jobs[i];
-        j.w = jobs[i].w;
-        j.s = jobs[i].s;
-        j.b = jobs[i].b;
-        j.out = outs[i];
-        j.n = jobs[i].n;
-        j.out_stride = out_strides ? out_strides[i] : jobs[i].n;
-        j.tile_begin = tiles;
-        j.w_misalign = (uint32_t)((uintptr_t)jobs[i].w & 15u);
-        tiles += (jobs[i].n + 15u) / 16u;
-        aligned = aligned && job_is_aligned(jobs[i]);
-    }
-    p.n_jobs = n_jobs;
-    p.xp = (const uint16_t *)rt->xp.ptr;
-    p.xsum = (const float *)rt->xsum.ptr;
-    p.v_cols = v_cols;
-    p.vpad = vpad;
-    p.m_rows = m;
-    p.x_is_f32 = f32 ? 1u : 0u;
-    p.accumulate = (flags & Q4B_FLAG_ACCUMULATE) ? 1u : 0u;
-    p.k = k;
-    p.groups = groups;
-    p.cpt = (groups + 1u) / 2u;
-    p.units = (uint64_t)tiles * p.cpt;
-    const uint32_t per_sm = rt->gemv_ctas[nt][aligned ? 1 : 0];
-    uint32_t ctas = (uint32_t)rt->sm_count * per_sm;
-    const uint32_t wpc = (uint32_t)q4k_gemv_warps_per_cta();
-    // never more warps than units: every worker then owns at least one unit, which the split-tile
-    // arrival count relies on; surplus warps of the last CTA exit at once
-    uint64_t workers = (uint64_t)ctas * wpc;
-    if (workers > p.units) workers = p.units;
-    p.workers = (uint32_t)workers;
-    ctas = (p.workers + wpc - 1) / wpc;
-    p.partials = (float *)rt->partials.ptr;
-    p.counters = (unsigned int *)rt->counters.ptr;
-    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
-    if (rt->profiling) {
-        if (rt->prof_used + 2 > rt->prof_events.size()) {
-            for (int i = 0; i < 2; ++i) {
-                cudaEvent_t ev;
-                Q4B_CUDA(cudaEventCreate(&ev), "cudaEventCreate");
-                rt->prof_events.push_back(ev);
-            }
+    // Jobs that meet the fast variant's conditions (all three tensors on 16-byte boundaries, K % 512 == 0)
+    // go in one launch, the rest in a second launch of the general (byte-addressed) variant.
+    for (int fast = 1; fast >= 0; --fast) {
+        q4::GemvParams p;
+        memset(&p, 0, sizeof p);
+        uint32_t tiles = 0, count = 0;
+        uint64_t prof_bytes = 0;
+        for (uint32_t i = 0; i < n_jobs; ++i) {
+            if ((job_is_fast(jobs[i], groups) ? 1 : 0) != fast) continue;
+            q4::GemvJob &j = p.jobs[count++];
+            j.w = jobs[i].w;
+            j.s = jobs[i].s;
+            j.b = jobs[i].b;
+            j.out = outs[i];
+            j.n = jobs[i].n;
+            j.out_stride = out_strides ? out_strides[i] : jobs[i].n;
+            j.tile_begin = tiles;
+            j.w_misalign = (uint32_t)((uintptr_t)jobs[i].w & 15u);
+            tiles += (jobs[i].n + 15u) / 16u;
+            prof_bytes += (uint64_t)jobs[i].n * (k / 2 + (uint64_t)groups * 4) + (uint64_t)m * jobs[i].n * 4;
         }
-        ev_start = rt->prof_events[rt->prof_used];
-        ev_stop = rt->prof_events[rt->prof_used + 1];
-        Q4B_CUDA(cudaEventRecord(ev_start, stream), "cudaEventRecord");
-    }
-    Q4B_CUDA(q4k_gemv(&p, nt, aligned ? 1 : 0, ctas, stream), "q4_gemv launch");
-    rt->launches++;
-    if (rt->profiling) {
-        Q4B_CUDA(cudaEventRecord(ev_stop, stream), "cudaEventRecord");
-        rt->prof_used += 2;
-        uint64_t bytes = (uint64_t)v_cols * k * 2 + (uint64_t)groups * vpad * 4;
-        for (uint32_t i = 0; i < n_jobs; ++i)
-            bytes += (uint64_t)jobs[i].n * (k / 2 + (uint64_t)groups * 4) + (uint64_t)m * jobs[i].n * 4;
-        rt->prof_bytes += bytes;
+        if (count == 0) continue;
+        p.n_jobs = count;
+        p.xp = (const uint16_t *)rt->xp.ptr;
+        p.xsum = (const float *)rt->xsum.ptr;
+        p.row_inv = (const float *)rt->row_inv.ptr;
+        p.kp = kp;
+        p.v_cols = v_cols;
+        p.vpad = vpad;
+        p.m_rows = m;
+        p.x_is_f32 = f32 ? 1u : 0u;
+        p.accumulate = (flags & Q4B_FLAG_ACCUMULATE) ? 1u : 0u;
+        p.k = k;
+        p.groups = groups;
+        p.cpt = (groups + 1u) / 2u;
+        p.units = (uint64_t)tiles * p.cpt;
+        // one warp per block, every SM filled to the variant's occupancy; never more warps than units, so
+        // every worker owns at least one unit (the split-tile arrival count relies on it)
+        uint64_t workers = (uint64_t)rt->sm_count * rt->gemv_ctas[nt][fast];
+        if (workers > p.units) workers = p.units;
+        p.workers = (uint32_t)workers;
+        p.partials = (float *)rt->partials.ptr;
+        p.counters = (unsigned int *)rt->counters.ptr;
+        cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+        if (rt->profiling) {
+            if (rt->prof_used + 2 > rt->prof_events.size()) {
+                for (int i = 0; i < 2; ++i) {
+                    cudaEvent_t ev;
+                    Q4B_CUDA(cudaEventCreate(&ev), "cudaEventCreate");
+                    rt->prof_events.push_back(ev);
+                }
+            }
+            ev_start = rt->prof_events[rt->prof_used];
+            ev_stop = rt->prof_events[rt->prof_used + 1];
+            Q4B_CUDA(cudaEventRecord(ev_start, stream), "cudaEventRecord");
+        }
+        Q4B_CUDA(q4k_gemv(&p, nt, fast, stream), "q4_gemv launch");
+        rt->launches++;
+        if (rt->profiling) {
+            Q4B_CUDA(cudaEventRecord(ev_stop, stream), "cudaEventRecord");
+            rt->prof_used += 2;
+            rt->prof_bytes += prof_bytes + (uint64_t)v_cols * kp * 2 + (uint64_t)(kp / 64) * vpad * 4;
+        }
     }
     return Q4B_OK;
 }
@@ -327,7 +332,7 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
             rt->gemv_ctas[nt][al] = occ;
             max_ctas = occ > max_ctas ? occ : max_ctas;
         }
-    rt->max_workers = (uint32_t)rt->sm_count * max_ctas * (uint32_t)q4k_gemv_warps_per_cta();
+    rt->max_workers = (uint32_t)rt->sm_count * max_ctas;
     // split-tile scratch: [workers][2 slots][2 column tiles][32 lanes][4 floats] and one counter per worker
     e = rt->partials.ensure((size_t)rt->max_workers * 2 * 2 * 32 * 16);
     if (e == cudaSuccess) e = rt->counters.ensure((size_t)rt->max_workers * 4);
@@ -346,7 +351,7 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
     cudaDeviceSynchronize();
     for (Shard &s : rt->shards)
         if (s.ptr) cudaFree(s.ptr);
-    Pool *pools[] = {&rt->x_in, &rt->xp, &rt->xsum, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
+    Pool *pools[] = {&rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
@@ -733,13 +738,13 @@ extern "C" int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, u
     std::lock_guard<std::mutex> lock(rt->mu);
     std::vector<Resolved> resolved;
     if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
-    bool aligned = true;
-    for (const Resolved &r : resolved) aligned = aligned && job_is_aligned(r);
+    uint32_t fast = 0;
+    for (const Resolved &r : resolved) fast += job_is_fast(r, (uint32_t)(k / 64)) ? 1u : 0u;
     const uint32_t rows = x_dtype == Q4B_F32 ? 2u : 8u;
     const uint32_t mb = (uint32_t)(m < rows ? m : rows);
     const uint32_t v = mb * (x_dtype == Q4B_F32 ? 3u : 1u);
-    snprintf(text, text_len, "stream_mma nt=%d %s launches=%llu", v <= 4 ? 1 : 2, aligned ? "aligned16" : "byte_addressed",
-             (unsigned long long)(((m + rows - 1) / rows) * ((n_jobs + q4::kMaxJobs - 1) / q4::kMaxJobs)));
+    snprintf(text, text_len, "stream_mma column_tiles=%d fast_jobs=%u byte_addressed_jobs=%u row_blocks=%llu", v <= 4 ? 1 : 2, fast,
+             n_jobs - fast, (unsigned long long)((m + rows - 1) / rows));
     return Q4B_OK;
 }
 
