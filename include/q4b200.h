@@ -170,6 +170,11 @@ int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, uint64_t k, 
  * biases, prepared activations, outputs), and stops recording. Not for use during graph capture. */
 int q4b_profile_begin(q4b_runtime *rt);
 int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes);
+/* Per-warp timeline of the last fast-variant projection launch (tracing aid): four device-clock stamps in
+ * nanoseconds per warp -- start, first weights landed, last chunk done, results stored.
+ * Not for use during graph capture. */
+int q4b_trace_enable(q4b_runtime *rt, int on);
+int q4b_trace_read(q4b_runtime *rt, uint64_t *stamps, uint32_t max_workers, uint32_t *workers);
 /* Kernels launched by this runtime since creation (the benchmark's launch count). */
 int q4b_launch_count(q4b_runtime *rt, uint64_t *launches);
 

@@ -222,9 +222,13 @@ __device__ __forceinline__ void consume_chunk(const uint4 &cwa, const uint4 &cwb
                                               float (&acc)[NT][4]) {
     const uint32_t wa[4] = {cwa.x, cwa.y, cwa.z, cwa.w};
     const uint32_t wb[4] = {cwb.x, cwb.y, cwb.z, cwb.w};
-    float d[NT][4];
+    // two independent accumulation chains (words 0,1 and words 2,3) halve the dependent MMA latency
+    float d[NT][4], e[NT][4];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
+    for (int j = 0; j < NT; ++j) {
+        d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
+        e[j][0] = e[j][1] = e[j][2] = e[j][3] = 0.f;
+    }
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
 #pragma unroll
@@ -236,9 +240,15 @@ __device__ __forceinline__ void consume_chunk(const uint4 &cwa, const uint4 &cwb
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const uint32_t xr[4] = {xf[j][w].x, xf[j][w].y, xf[j][w].z, xf[j][w].w};
-                mma_f16_16816(d[j], a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
+                if (w < 2) mma_f16_16816(d[j], a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
+                else mma_f16_16816(e[j], a0, a1, a2, a3, xr[2 * h], xr[2 * h + 1]);
             }
         }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[j][i] += e[j][i];
     }
     // d[.][0],d[.][1]: row g, MMA columns 2t,2t+1; d[.][2],d[.][3]: row g+8. Those columns are activation
     // columns 4j + 2(t&1), +1 of the group this lane streamed.
@@ -500,10 +510,18 @@ __device__ __forceinline__ float param_of(uint32_t word, uint32_t sel) {
     return __uint_as_float(__byte_perm(word, 0u, sel));
 }
 
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 template <int NT>
 __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_fast_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t ring_bytes[];
     const uint32_t lane = threadIdx.x;
+    if (p.trace && lane == 0) p.trace[blockIdx.x * 4 + 0] = global_ns();
+    bool first_data = true;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t worker = blockIdx.x;
     const Q4Split split{p.units, p.cpt, p.workers};
@@ -578,35 +596,64 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_fast_kernel(con
 
         uint32_t half = 0;
         for (uint32_t cg = cbase; cg < c1; cg += 4) {
-            const uint32_t stage0 = ring + half * (4 * kStageBytesAligned);
+            const uint32_t stage0 = ring + half * (4 * kStageBytesAligned) + lane * 16u;
             const uint32_t pstage = pring + half * 512u;
             cp_async_wait<1>();  // this half's group has landed; the other half's may be pending
             __syncwarp();        // parameters were copied by other lanes
+            if (p.trace && first_data) {
+                if (lane == 0) p.trace[blockIdx.x * 4 + 1] = global_ns();
+                first_data = false;
+            }
             const uint4 psa = lds_v4(pstage + g * 16u), psb = lds_v4(pstage + (g + 8u) * 16u);
             const uint4 pba = lds_v4(pstage + 256u + g * 16u), pbb = lds_v4(pstage + 256u + (g + 8u) * 16u);
             const uint32_t wsa[4] = {psa.x, psa.y, psa.z, psa.w}, wsb[4] = {psb.x, psb.y, psb.z, psb.w};
             const uint32_t wba[4] = {pba.x, pba.y, pba.z, pba.w}, wbb[4] = {pbb.x, pbb.y, pbb.z, pbb.w};
+            if (cg >= c0 && cg + 12 <= c1) {
+                // steady state: all four chunks and all four refills lie inside the segment
+                uint4 cwa = lds_v4(stage0), cwb = lds_v4(stage0 + 512u);
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint32_t c = cg + s;
-                if (c >= c0 && c < c1) {
+                for (int s = 0; s < 4; ++s) {
                     const int b = s & 1;
-                    const uint32_t stage = stage0 + s * kStageBytesAligned;
-                    const uint4 cwa = lds_v4(stage + lane * 16u), cwb = lds_v4(stage + 512u + lane * 16u);
-                    load_x<NT>(xf[b ^ 1], xsrc + (s + 1) * 128, x_mask, p.kp);  // reads past the segment are harmless
+                    uint4 nwa = cwa, nwb = cwb;
+                    if (s < 3) {  // next chunk's weights leave shared memory while this one is computed
+                        nwa = lds_v4(stage0 + (s + 1) * kStageBytesAligned);
+                        nwb = lds_v4(stage0 + (s + 1) * kStageBytesAligned + 512u);
+                    }
+                    load_x<NT>(xf[b ^ 1], xsrc + (s + 1) * 128, x_mask, p.kp);
                     consume_chunk<NT>(cwa, cwb, param_of(wsa[s], half_sel), param_of(wsb[s], half_sel),
                                       param_of(wba[s], half_sel), param_of(wbb[s], half_sel), xf[b], xs + s * xs_step, mg, acc);
+                    cwa = nwa;
+                    cwb = nwb;
                 }
-            }
-            __syncwarp();  // every lane is done with this half before it is refilled
+                __syncwarp();  // every lane is done with this half before it is refilled
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint32_t stage = stage0 + s * kStageBytesAligned;
-                const bool more = cg + 8 + s < c1;
-                cp_async_16_pred(stage + lane * 16u, wa + (8 + s) * 64, more);
-                cp_async_16_pred(stage + 512u + lane * 16u, wb + (8 + s) * 64, more);
+                for (int s = 0; s < 4; ++s) {
+                    cp_async_16(stage0 + s * kStageBytesAligned, wa + (8 + s) * 64);
+                    cp_async_16(stage0 + s * kStageBytesAligned + 512u, wb + (8 + s) * 64);
+                }
+                cp_async_16(pstage + lane * 16u, pp + 32);
+            } else {
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint32_t c = cg + s;
+                    if (c >= c0 && c < c1) {
+                        const int b = s & 1;
+                        const uint32_t stage = stage0 + s * kStageBytesAligned;
+                        const uint4 cwa = lds_v4(stage), cwb = lds_v4(stage + 512u);
+                        load_x<NT>(xf[b ^ 1], xsrc + (s + 1) * 128, x_mask, p.kp);  // reads past the segment are harmless
+                        consume_chunk<NT>(cwa, cwb, param_of(wsa[s], half_sel), param_of(wsb[s], half_sel),
+                                          param_of(wba[s], half_sel), param_of(wbb[s], half_sel), xf[b], xs + s * xs_step, mg, acc);
+                    }
+                }
+                __syncwarp();
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const bool more = cg + 8 + s < c1;
+                    cp_async_16_pred(stage0 + s * kStageBytesAligned, wa + (8 + s) * 64, more);
+                    cp_async_16_pred(stage0 + s * kStageBytesAligned + 512u, wb + (8 + s) * 64, more);
+                }
+                cp_async_16_pred(pstage + lane * 16u, pp + 32, cg + 8 < c1);
             }
-            cp_async_16_pred(pstage + lane * 16u, pp + 32, cg + 8 < c1);
             cp_async_commit();
             wa += 4 * 64;
             wb += 4 * 64;
@@ -617,11 +664,13 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_fast_kernel(con
         }
         cp_async_wait<0>();
         __syncwarp();
+        if (p.trace && lane == 0) p.trace[blockIdx.x * 4 + 2] = global_ns();
         finish_tile<NT>(p, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index);
         u += c1 - c0;
         ++tile;
         c0 = 0;
     }
+    if (p.trace && lane == 0) p.trace[blockIdx.x * 4 + 3] = global_ns();
 }
 
 }  // namespace q4

@@ -40,6 +40,7 @@ struct GemvParams {
     uint64_t units;        // tiles * cpt
     float *partials;       // [workers][2][column tiles][32][4] fp32 scratch for split tiles
     unsigned int *counters;  // [workers], zero between launches
+    unsigned long long *trace;  // optional [workers][4] globaltimer stamps (start, first data, loop end, done); may be null
 };
 
 }  // namespace q4

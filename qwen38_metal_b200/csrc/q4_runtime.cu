@@ -89,6 +89,9 @@ struct q4b_runtime {
     std::vector<Shard> shards;
     uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident warps per SM
     uint32_t max_workers = 0;
+    Pool trace;
+    bool tracing = false;
+    uint32_t trace_workers = 0;
     Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
     Pool outs[q4::kMaxJobs];
     uint64_t launches = 0;
@@ -226,10 +229,15 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
         // one warp per block, every SM filled to the variant's occupancy; never more warps than units, so
         // every worker owns at least one unit (the split-tile arrival count relies on it)
         uint64_t workers = (uint64_t)rt->sm_count * rt->gemv_ctas[nt][fast];
-        if (workers > p.units) workers = p.units;
+        // at most 8 warps share a tile: the warp that combines a split tile reads its partials one by one
+        const uint64_t min_chunks = (p.cpt + 7u) / 8u;
+        if (workers > p.units / min_chunks) workers = p.units / min_chunks;
+        if (workers == 0) workers = 1;
         p.workers = (uint32_t)workers;
         p.partials = (float *)rt->partials.ptr;
         p.counters = (unsigned int *)rt->counters.ptr;
+        p.trace = rt->tracing ? (unsigned long long *)rt->trace.ptr : nullptr;
+        if (rt->tracing) rt->trace_workers = p.workers;
         cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
         if (rt->profiling) {
             if (rt->prof_used + 2 > rt->prof_events.size()) {
@@ -351,7 +359,7 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
     cudaDeviceSynchronize();
     for (Shard &s : rt->shards)
         if (s.ptr) cudaFree(s.ptr);
-    Pool *pools[] = {&rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
+    Pool *pools[] = {&rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
@@ -771,6 +779,28 @@ extern "C" int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *tota
     if (total_ms) *total_ms = total;
     if (bytes) *bytes = rt->prof_bytes;
     rt->prof_used = 0;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_trace_enable(q4b_runtime *rt, int on) {
+    if (int st = check_rt(rt)) return st;
+    DeviceGuard guard(rt->device);
+    if (on) {
+        Q4B_CUDA(rt->trace.ensure((size_t)rt->max_workers * 4 * 8), "trace buffer");
+        Q4B_CUDA(cudaMemset(rt->trace.ptr, 0, rt->trace.capacity), "trace clear");
+    }
+    rt->tracing = on != 0;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_trace_read(q4b_runtime *rt, uint64_t *stamps, uint32_t max_workers, uint32_t *workers) {
+    if (int st = check_rt(rt)) return st;
+    if (!stamps || !workers) return fail(Q4B_INVALID_ARGUMENT, "trace output pointer is null");
+    DeviceGuard guard(rt->device);
+    Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
+    uint32_t n = rt->trace_workers < max_workers ? rt->trace_workers : max_workers;
+    if (n && rt->trace.ptr) Q4B_CUDA(cudaMemcpy(stamps, rt->trace.ptr, (size_t)n * 32, cudaMemcpyDeviceToHost), "trace download");
+    *workers = n;
     return Q4B_OK;
 }
 
