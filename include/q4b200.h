@@ -167,9 +167,12 @@ int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, uint64_t k, 
  * GPUStartTime/GPUEndTime; here a CUDA event pair is recorded around every projection-kernel launch,
  * on the stream it is launched on). q4b_profile_end synchronises, returns the number of timed
  * launches, the sum of their durations and the algorithmic bytes they moved (packed weights, scales,
- * biases, prepared activations, outputs), and stops recording. Not for use during graph capture. */
+ * biases, prepared activations, outputs) and the multiply-add work (2*m*n*k per projection), and stops recording. Not for use during graph capture. */
 int q4b_profile_begin(q4b_runtime *rt);
-int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes);
+int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes, uint64_t *flops);
+/* Synchronise the device and report asynchronous failures of `_device` calls: a CUDA error, or a kernel
+ * that gave up on one of its bounded waits (CommandFailed, src/metal_runtime.rs:3661-3663). */
+int q4b_device_status(q4b_runtime *rt);
 /* Per-warp timeline of the last fast-variant projection launch (tracing aid): four device-clock stamps in
  * nanoseconds per warp -- start, first weights landed, last chunk done, results stored.
  * Not for use during graph capture. */

@@ -1,0 +1,439 @@
+// Prefill affine-Q4 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// Replaces the reference's prompt path: qwen38_q4_affine_matmul_simdgroup / _simdgroup_wide
+// (shaders/qwen38.metal:3769-3966), and the dequantise-whole-matrix + MPS FP16 GEMM route
+// (qwen38_q4_affine_dequantize_f16, shaders/qwen38.metal:4102-4164; src/mps.rs:93-104;
+// src/metal_runtime.rs:3897-4047). Arithmetic is that path's: w = 16bit(q*scale + bias), products of
+// 16-bit operands, fp32 accumulation -- with bf16 where the reference uses half. No dequantised copy of the
+// matrix is ever written to HBM: tiles are expanded in shared memory right before the MMA reads them.
+//
+// Orientation: the weight tile is the MMA's A operand (128 rows = UMMA M), the activation tile the B operand
+// (up to 256 activation rows = UMMA N), so D[n][m] lands in TMEM with one weight row per lane and the epilogue
+// writes out[m][n] with the lanes of a warp on consecutive n (coalesced). K advances 64 per stage = one affine
+// group, so a producer thread needs one scale and one bias per stage.
+//
+// Warp roles in a block of 14 warps (one block per SM, persistent over output tiles):
+//   warp 0      one thread issues TMA loads of activation tiles (bf16, 128-byte swizzle)
+//   warp 1      allocates TMEM; one thread issues tcgen05.mma and commits to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, store to global (two accumulators alternate)
+//   warps 6-13  dequantise: packed words -> bf16 pairs -> swizzled K-major tile in shared memory
+// Every wait is bounded: a wait that runs out sets an error flag, the block drains and frees its TMEM.
+#include <cuda.h>
+
+#include "q4_kernels.h"
+
+#include "q4_device.cuh"
+
+namespace q4 {
+
+constexpr int kGemmThreads = 14 * 32;
+constexpr int kGemmStages = 4;
+constexpr int kTileN = 128;              // weight rows per tile (UMMA M)
+constexpr int kTileK = 64;               // inputs per stage: one affine group, 128 bytes of bf16
+constexpr uint32_t kATileBytes = kTileN * kTileK * 2;  // 16 KB
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct GemmParams {
+    const uint8_t *w, *s, *b;  // packed weights, scales, biases (any byte alignment)
+    float *out;                // [m][out_stride]
+    uint32_t n, m, k;          // weight rows, activation rows, inputs
+    uint32_t out_stride;
+    uint32_t tiles_n, tiles_m;
+    uint32_t w_misalign;       // (uintptr_t)w & 15
+    uint32_t accumulate;       // out += result
+    int *error_flag;           // set non-zero when a bounded wait runs out
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and raises the block's abort flag) when the limit is reached or another
+// role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], 128 x N x 16, bf16 inputs, fp32 accumulate
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on an mbarrier once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major bf16 tile with 128-byte swizzle: rows are 128 bytes, groups
+// of 8 rows (1024 bytes) follow each other (stride byte offset 1024), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;            // leading byte offset: unused with swizzled K-major layouts
+    d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+    d |= (uint64_t)1 << 46;            // descriptor version
+    d |= (uint64_t)2 << 61;            // 128-byte swizzle
+    return d;
+}
+
+// two nibbles -> bf16x2 of q*scale + bias (one rounding): 0x4300|q is bf16 128+q, minus 128 is exact
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t scale2, uint32_t bias2) {
+    uint32_t biased = (v & 0x000f000fu) | 0x43004300u, q, out;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(biased), "r"(0x43004300u));
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(out) : "r"(q), "r"(scale2), "r"(bias2));
+    return out;
+}
+
+// ---- activation preparation: bf16, each block of 8 inputs reordered k0,k4,k1,k5,k2,k6,k3,k7 (the order the
+// nibble extraction yields), so weights and activations agree on k inside every MMA ----------------------------
+__global__ void __launch_bounds__(256) q4_gemm_prepare_x_kernel(const void *__restrict__ x, int x_is_f32, uint64_t blocks,
+                                                               uint16_t *__restrict__ xp) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= blocks) return;
+    uint32_t bits[8];
+    if (x_is_f32) {
+        const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(x) + i * 8);
+        float4 lo = src[0], hi = src[1];
+        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bits[j] = float_to_bf16_bits(v[j]);
+    } else {
+        uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + i * 8);
+        const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            bits[2 * j] = r[j] & 0xffffu;
+            bits[2 * j + 1] = r[j] >> 16;
+        }
+    }
+    uint4 out;
+    out.x = bits[0] | (bits[4] << 16);
+    out.y = bits[1] | (bits[5] << 16);
+    out.z = bits[2] | (bits[6] << 16);
+    out.w = bits[3] | (bits[7] << 16);
+    *reinterpret_cast<uint4 *>(xp + i * 8) = out;
+}
+
+// ---- the GEMM ------------------------------------------------------------------------------------------------
+
+template <int BN>
+struct GemmSmem {
+    static constexpr uint32_t kBTileBytes = BN * kTileK * 2;
+    static constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr uint32_t kBarrierOffset = kGemmStages * kStageBytes;
+    static constexpr uint32_t kTotal = kBarrierOffset + 256 + 1024;  // barriers + slack for 1024-byte alignment
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                    const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t gemm_smem_raw[];
+    using L = GemmSmem<BN>;
+    const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(gemm_smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + L::kBarrierOffset;
+    // barrier slots (8 bytes each): full_x[4] full_w[4] empty[4] acc_full[2] acc_empty[2], then tmem base, abort flag
+    auto full_x = [&](uint32_t s) { return bars + 8u * s; };
+    auto full_w = [&](uint32_t s) { return bars + 32u + 8u * s; };
+    auto empty = [&](uint32_t s) { return bars + 64u + 8u * s; };
+    auto acc_full = [&](uint32_t a) { return bars + 96u + 8u * a; };
+    auto acc_empty = [&](uint32_t a) { return bars + 112u + 8u * a; };
+    uint8_t *smem_generic = gemm_smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(gemm_smem_raw));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_generic + L::kBarrierOffset + 128);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_generic + L::kBarrierOffset + 136);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two >= 32
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kGemmStages; ++s) {
+            mbar_init(full_x(s), 1);
+            mbar_init(full_w(s), 8);   // one arrival per producer warp
+            mbar_init(empty(s), 1);    // tcgen05.commit
+        }
+        for (uint32_t a = 0; a < 2; ++a) {
+            mbar_init(acc_full(a), 1);
+            mbar_init(acc_empty(a), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(bars + 128u, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t k_blocks = p.k / kTileK;
+    const uint32_t total_tiles = p.tiles_n * p.tiles_m;
+
+    if (warp == 0) {
+        // ---- TMA producer: activation tiles ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const uint32_t m0 = (tile % p.tiles_m) * BN;
+                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
+                    if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(full_x(s), L::kBTileBytes);
+                    tma_load_2d(smem_base + s * L::kStageBytes + kATileBytes, &tmap_x, full_x(s), (int32_t)(kb * kTileK), (int32_t)m0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+                const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(acc_empty(acc), aph ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
+                    if (!mbar_wait(full_x(s), ph, abort_flag) || !mbar_wait(full_w(s), ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * L::kStageBytes, b_addr = a_addr + kATileBytes;
+                    const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(b_addr);
+#pragma unroll
+                    for (uint32_t k16 = 0; k16 < kTileK / 16; ++k16) {
+                        // 16 inputs = 32 bytes further along K inside the 128-byte rows: +2 in 16-byte units
+                        umma_bf16(d_tmem, adesc + 2u * k16, bdesc + 2u * k16, idesc, (kb | k16) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty(s));  // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_full(acc));
+            }
+        }
+    } else if (warp < 6) {
+        // ---- epilogue: TMEM -> registers -> global ----
+        const uint32_t quarter = warp & 3u;  // a warp may touch TMEM lanes 32*(warp%4) .. +31
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+            const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+            const uint32_t n0 = (tile / p.tiles_m) * kTileN, m0 = (tile % p.tiles_m) * BN;
+            if (!mbar_wait(acc_full(acc), aph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t n = n0 + quarter * 32u + lane;
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * BN + c0, r);
+                tmem_ld_wait();
+                if (n < p.n) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t m = m0 + c0 + i;
+                        if (m < p.m) {
+                            float *dst = p.out + (uint64_t)m * p.out_stride + n;
+                            float v = __uint_as_float(r[i]);
+                            if (p.accumulate) v += *dst;
+                            *dst = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(acc));
+        }
+    } else {
+        // ---- dequantise producers: 256 threads, two per weight row, four packed words each ----
+        const uint32_t pid = threadIdx.x - 6 * 32;
+        const uint32_t row = pid >> 1, part = pid & 1u;
+        const uint32_t groups = p.k / 64;
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const uint32_t n0 = (tile / p.tiles_m) * kTileN;
+            uint32_t grow = n0 + row;
+            grow = grow < p.n ? grow : p.n - 1u;  // rows past N are computed from a valid row and never stored
+            const uint8_t *wrow = p.w + (uint64_t)grow * (p.k / 2) + part * 16u;
+            const uint8_t *srow = p.s + (uint64_t)grow * groups * 2u, *brow = p.b + (uint64_t)grow * groups * 2u;
+            for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
+                // fetch before waiting for the stage: global latency overlaps the wait
+                const uint4 packed = p.w_misalign ? ldg_stream_v4_unaligned(wrow + kb * 32u, p.w_misalign) : ldg_stream_v4(wrow + kb * 32u);
+                uint32_t sc = ldg_bf16_bits(srow + 2u * kb), bi = ldg_bf16_bits(brow + 2u * kb);
+                sc |= sc << 16;
+                bi |= bi << 16;
+                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                const uint32_t a_row = smem_base + s * L::kStageBytes + row * 128u;
+                const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+                for (uint32_t wi = 0; wi < 4; ++wi) {
+                    const uint32_t wv = words[wi];
+                    const uint32_t o0 = dequant_pair(wv, sc, bi), o1 = dequant_pair(wv >> 4, sc, bi);
+                    const uint32_t o2 = dequant_pair(wv >> 8, sc, bi), o3 = dequant_pair(wv >> 12, sc, bi);
+                    const uint32_t chunk = part * 4u + wi;  // 16-byte piece of the 128-byte row
+                    const uint32_t dst = a_row + ((chunk ^ (row & 7u)) << 4);  // 128-byte swizzle
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+                }
+                fence_async_smem();  // the tensor core reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_w(s));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (threadIdx.x == 0 && *abort_flag && p.error_flag) *p.error_flag = 1;
+}
+
+}  // namespace q4
+
+// ---------------------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------------------
+
+extern "C" cudaError_t q4k_gemm_prepare_x(const void *x, int x_is_f32, uint64_t elements, uint16_t *xp, cudaStream_t stream) {
+    const uint64_t blocks = elements / 8;
+    q4::q4_gemm_prepare_x_kernel<<<(uint32_t)((blocks + 255) / 256), 256, 0, stream>>>(x, x_is_f32, blocks, xp);
+    return cudaGetLastError();
+}
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+template <int BN>
+cudaError_t launch_gemm(const CUtensorMap &map, const q4::GemmParams &p, uint32_t ctas, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(q4::q4_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)q4::GemmSmem<BN>::kTotal);
+    if (e != cudaSuccess) return e;
+    q4::q4_gemm_tc_kernel<BN><<<ctas, q4::kGemmThreads, q4::GemmSmem<BN>::kTotal, stream>>>(map, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// activation rows per tile the kernel would use for m rows
+extern "C" uint32_t q4k_gemm_tile_m(uint32_t m) {
+    if (m > 128) return 256;
+    if (m > 64) return 128;
+    if (m > 32) return 64;
+    if (m > 16) return 32;
+    return 16;
+}
+
+// xp: prepared activations [m][k] bf16 (q4k_gemm_prepare_x), 16-byte aligned. One projection per launch.
+extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_t *w, const uint8_t *s, const uint8_t *b,
+                                   uint32_t n, float *out, uint32_t out_stride, int accumulate, int *error_flag, uint32_t sm_count,
+                                   cudaStream_t stream) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return cudaErrorNotSupported;
+    const uint32_t bn = q4k_gemm_tile_m(m);
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {k, m};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)q4::kTileK, bn};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(xp), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    q4::GemmParams p;
+    p.w = w;
+    p.s = s;
+    p.b = b;
+    p.out = out;
+    p.n = n;
+    p.m = m;
+    p.k = k;
+    p.out_stride = out_stride;
+    p.tiles_n = (n + q4::kTileN - 1) / q4::kTileN;
+    p.tiles_m = (m + bn - 1) / bn;
+    p.w_misalign = (uint32_t)((uintptr_t)w & 15u);
+    p.accumulate = accumulate ? 1u : 0u;
+    p.error_flag = error_flag;
+    const uint32_t tiles = p.tiles_n * p.tiles_m;
+    const uint32_t ctas = tiles < sm_count ? tiles : sm_count;
+    switch (bn) {
+        case 256: return launch_gemm<256>(map, p, ctas, stream);
+        case 128: return launch_gemm<128>(map, p, ctas, stream);
+        case 64: return launch_gemm<64>(map, p, ctas, stream);
+        case 32: return launch_gemm<32>(map, p, ctas, stream);
+        default: return launch_gemm<16>(map, p, ctas, stream);
+    }
+}

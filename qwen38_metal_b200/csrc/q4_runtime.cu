@@ -89,7 +89,9 @@ struct q4b_runtime {
     std::vector<Shard> shards;
     uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident warps per SM
     uint32_t max_workers = 0;
-    Pool trace;
+    Pool trace, gemm_x, error_flag;
+    uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
+    uint64_t prof_flops = 0;
     bool tracing = false;
     uint32_t trace_workers = 0;
     Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
@@ -172,6 +174,28 @@ bool job_is_fast(const Resolved &r, uint32_t groups) {
     return (((uintptr_t)r.w | (uintptr_t)r.s | (uintptr_t)r.b) & 15u) == 0 && groups % 8u == 0;
 }
 
+int profile_open(q4b_runtime *rt, cudaStream_t stream) {
+    if (!rt->profiling) return Q4B_OK;
+    if (rt->prof_used + 2 > rt->prof_events.size()) {
+        for (int i = 0; i < 2; ++i) {
+            cudaEvent_t ev;
+            Q4B_CUDA(cudaEventCreate(&ev), "cudaEventCreate");
+            rt->prof_events.push_back(ev);
+        }
+    }
+    Q4B_CUDA(cudaEventRecord(rt->prof_events[rt->prof_used], stream), "cudaEventRecord");
+    return Q4B_OK;
+}
+
+int profile_close(q4b_runtime *rt, cudaStream_t stream, uint64_t bytes, uint64_t flops) {
+    if (!rt->profiling) return Q4B_OK;
+    Q4B_CUDA(cudaEventRecord(rt->prof_events[rt->prof_used + 1], stream), "cudaEventRecord");
+    rt->prof_used += 2;
+    rt->prof_bytes += bytes;
+    rt->prof_flops += flops;
+    return Q4B_OK;
+}
+
 // One streaming launch: up to kMaxJobs projections, up to 8 bf16 (2 fp32) activation rows.
 int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m, uint32_t k, const Resolved *jobs,
                      uint32_t n_jobs, float *const *outs, const uint32_t *out_strides, uint32_t flags,
@@ -196,7 +220,7 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
         q4::GemvParams p;
         memset(&p, 0, sizeof p);
         uint32_t tiles = 0, count = 0;
-        uint64_t prof_bytes = 0;
+        uint64_t prof_bytes = 0, prof_rows = 0;
         for (uint32_t i = 0; i < n_jobs; ++i) {
             if ((job_is_fast(jobs[i], groups) ? 1 : 0) != fast) continue;
             q4::GemvJob &j = p.jobs[count++];
@@ -210,6 +234,7 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
             j.w_misalign = (uint32_t)((uintptr_t)jobs[i].w & 15u);
             tiles += (jobs[i].n + 15u) / 16u;
             prof_bytes += (uint64_t)jobs[i].n * (k / 2 + (uint64_t)groups * 4) + (uint64_t)m * jobs[i].n * 4;
+            prof_rows += jobs[i].n;
         }
         if (count == 0) continue;
         p.n_jobs = count;
@@ -238,33 +263,38 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
         p.counters = (unsigned int *)rt->counters.ptr;
         p.trace = rt->tracing ? (unsigned long long *)rt->trace.ptr : nullptr;
         if (rt->tracing) rt->trace_workers = p.workers;
-        cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
-        if (rt->profiling) {
-            if (rt->prof_used + 2 > rt->prof_events.size()) {
-                for (int i = 0; i < 2; ++i) {
-                    cudaEvent_t ev;
-                    Q4B_CUDA(cudaEventCreate(&ev), "cudaEventCreate");
-                    rt->prof_events.push_back(ev);
-                }
-            }
-            ev_start = rt->prof_events[rt->prof_used];
-            ev_stop = rt->prof_events[rt->prof_used + 1];
-            Q4B_CUDA(cudaEventRecord(ev_start, stream), "cudaEventRecord");
-        }
+        if (int st = profile_open(rt, stream)) return st;
         Q4B_CUDA(q4k_gemv(&p, nt, fast, stream), "q4_gemv launch");
         rt->launches++;
-        if (rt->profiling) {
-            Q4B_CUDA(cudaEventRecord(ev_stop, stream), "cudaEventRecord");
-            rt->prof_used += 2;
-            rt->prof_bytes += prof_bytes + (uint64_t)v_cols * kp * 2 + (uint64_t)(kp / 64) * vpad * 4;
-        }
+        if (int st = profile_close(rt, stream, prof_bytes + (uint64_t)v_cols * kp * 2 + (uint64_t)(kp / 64) * vpad * 4, 2ull * m * prof_rows * k)) return st;
     }
     return Q4B_OK;
 }
 
-// Any m, any number of jobs: cut into launches the streaming kernel accepts.
+// Tensor-core path: activations to bf16 once, then one tcgen05 GEMM launch per projection.
+int enqueue_gemm(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k, const std::vector<Resolved> &jobs,
+                 float *const *outs, uint32_t flags, cudaStream_t stream) {
+    Q4B_CUDA(rt->gemm_x.ensure((size_t)m * k * 2), "activation scratch");
+    Q4B_CUDA(q4k_gemm_prepare_x(x_dev, x_dtype == Q4B_F32 ? 1 : 0, m * k, (uint16_t *)rt->gemm_x.ptr, stream),
+             "q4_gemm_prepare_x launch");
+    rt->launches++;
+    for (size_t i = 0; i < jobs.size(); ++i) {
+        if (int st = profile_open(rt, stream)) return st;
+        Q4B_CUDA(q4k_gemm_tc((const uint16_t *)rt->gemm_x.ptr, (uint32_t)m, (uint32_t)k, jobs[i].w, jobs[i].s, jobs[i].b, jobs[i].n,
+                             outs[i], jobs[i].n, (flags & Q4B_FLAG_ACCUMULATE) ? 1 : 0, (int *)rt->error_flag.ptr,
+                             (uint32_t)rt->sm_count, stream),
+                 "q4_gemm_tc launch");
+        rt->launches++;
+        const uint64_t bytes = (uint64_t)jobs[i].n * (k / 2 + (k / 64) * 4) + m * k * 2 + m * jobs[i].n * 4;
+        if (int st = profile_close(rt, stream, bytes, 2ull * m * jobs[i].n * k)) return st;
+    }
+    return Q4B_OK;
+}
+
+// Any m, any number of jobs: tensor-core GEMM from gemm_min_m rows, else launches the streaming kernel accepts.
 int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
                    const std::vector<Resolved> &jobs, float *const *outs, uint32_t flags, cudaStream_t stream) {
+    if (m >= rt->gemm_min_m) return enqueue_gemm(rt, x_dev, x_dtype, m, k, jobs, outs, flags, stream);
     const uint32_t rows_per_launch = x_dtype == Q4B_F32 ? 2u : 8u;
     const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
     for (uint64_t m0 = 0; m0 < m; m0 += rows_per_launch) {
@@ -289,7 +319,13 @@ int check_dtype(int x_dtype) {
 int finish(q4b_runtime *rt, cudaStream_t stream) {
     cudaError_t e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail(Q4B_COMMAND_FAILED, "CUDA command failed: %s", cudaGetErrorString(e));
-    (void)rt;
+    int flag = 0;
+    e = cudaMemcpy(&flag, rt->error_flag.ptr, sizeof flag, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(Q4B_COMMAND_FAILED, "CUDA command failed: %s", cudaGetErrorString(e));
+    if (flag) {
+        cudaMemset(rt->error_flag.ptr, 0, sizeof flag);
+        return fail(Q4B_COMMAND_FAILED, "a kernel gave up on a bounded wait (pipeline stalled); results are invalid");
+    }
     return Q4B_OK;
 }
 
@@ -323,6 +359,12 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     rt->total_bytes = prop.totalGlobalMem;
     snprintf(rt->name, sizeof rt->name, "%s", prop.name);
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
+    if (rt->force_variant == "stream") rt->gemm_min_m = 0xffffffffu;   // never use the tensor-core GEMM
+    if (rt->force_variant == "tensor") rt->gemm_min_m = 1;            // always use it
+    if (const char *min_m = getenv("Q4B_GEMM_MIN_M")) {
+        long v = strtol(min_m, nullptr, 10);
+        if (v > 0) rt->gemm_min_m = (uint32_t)v;
+    }
     e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) {
         delete rt;
@@ -345,6 +387,8 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     e = rt->partials.ensure((size_t)rt->max_workers * 2 * 2 * 32 * 16);
     if (e == cudaSuccess) e = rt->counters.ensure((size_t)rt->max_workers * 4);
     if (e == cudaSuccess) e = cudaMemset(rt->counters.ptr, 0, rt->counters.capacity);
+    if (e == cudaSuccess) e = rt->error_flag.ensure(256);
+    if (e == cudaSuccess) e = cudaMemset(rt->error_flag.ptr, 0, rt->error_flag.capacity);
     if (e != cudaSuccess) {
         q4b_runtime_destroy(rt);
         return fail_cuda(e, "scratch allocation");
@@ -359,7 +403,7 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
     cudaDeviceSynchronize();
     for (Shard &s : rt->shards)
         if (s.ptr) cudaFree(s.ptr);
-    Pool *pools[] = {&rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
+    Pool *pools[] = {&rt->gemm_x, &rt->error_flag, &rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
@@ -761,10 +805,11 @@ extern "C" int q4b_profile_begin(q4b_runtime *rt) {
     rt->profiling = true;
     rt->prof_used = 0;
     rt->prof_bytes = 0;
+    rt->prof_flops = 0;
     return Q4B_OK;
 }
 
-extern "C" int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes) {
+extern "C" int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *total_ms, uint64_t *bytes, uint64_t *flops) {
     if (int st = check_rt(rt)) return st;
     DeviceGuard guard(rt->device);
     rt->profiling = false;
@@ -778,6 +823,7 @@ extern "C" int q4b_profile_end(q4b_runtime *rt, uint64_t *launches, double *tota
     if (launches) *launches = rt->prof_used / 2;
     if (total_ms) *total_ms = total;
     if (bytes) *bytes = rt->prof_bytes;
+    if (flops) *flops = rt->prof_flops;
     rt->prof_used = 0;
     return Q4B_OK;
 }
@@ -802,6 +848,14 @@ extern "C" int q4b_trace_read(q4b_runtime *rt, uint64_t *stamps, uint32_t max_wo
     if (n && rt->trace.ptr) Q4B_CUDA(cudaMemcpy(stamps, rt->trace.ptr, (size_t)n * 32, cudaMemcpyDeviceToHost), "trace download");
     *workers = n;
     return Q4B_OK;
+}
+
+extern "C" int q4b_device_status(q4b_runtime *rt) {
+    if (int st = check_rt(rt)) return st;
+    DeviceGuard guard(rt->device);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(Q4B_COMMAND_FAILED, "CUDA command failed: %s", cudaGetErrorString(e));
+    return finish(rt, rt->stream);
 }
 
 extern "C" int q4b_launch_count(q4b_runtime *rt, uint64_t *launches) {

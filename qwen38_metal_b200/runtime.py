@@ -267,9 +267,13 @@ class CudaRuntime:
 
     def profile_end(self) -> dict:
         """Timed projection-kernel launches since profile_begin: count, summed ms, algorithmic bytes."""
-        n, ms, nbytes = C.c_uint64(), C.c_double(), C.c_uint64()
-        _check(self._lib.q4b_profile_end(self._h, C.byref(n), C.byref(ms), C.byref(nbytes)))
-        return {"launches": n.value, "ms": ms.value, "bytes": nbytes.value}
+        n, ms, nbytes, flops = C.c_uint64(), C.c_double(), C.c_uint64(), C.c_uint64()
+        _check(self._lib.q4b_profile_end(self._h, C.byref(n), C.byref(ms), C.byref(nbytes), C.byref(flops)))
+        return {"launches": n.value, "ms": ms.value, "bytes": nbytes.value, "flops": flops.value}
+
+    def device_status(self) -> None:
+        """Synchronise and raise if a device-resident call failed asynchronously."""
+        _check(self._lib.q4b_device_status(self._h))
 
     def launch_count(self) -> int:
         n = C.c_uint64()

@@ -12,6 +12,8 @@ from helpers import golden_rows, upload_matrix
 pytestmark = pytest.mark.gpu
 
 REL_L2_STREAM = 1e-5  # fp32 outputs of the streaming (decode / short batch) family
+REL_L2_TENSOR = 2e-3  # bf16 tiles on the tensor cores (16 activation rows and more)
+TENSOR_FROM = 16      # default hand-over point of the dispatcher
 
 
 def run_case(rt, case, batch, offset):
@@ -36,9 +38,16 @@ def test_projection_fixtures(case, runtime, oracle, golden):
             for mi, (out, (packed, scales, biases)) in enumerate(zip(outs, tensors)):
                 expected = golden_rows(case, golden[case.name], batch, mi)
                 assert out.shape == expected.shape
-                assert np.max(np.abs(out - expected)) < min(case.tol, 1e-3), (case.name, batch, offset)
                 ref = oracle.matmul_factored_f32(x, packed, scales, biases, packed.shape[0])
-                assert oracle.rel_l2(out, ref) <= REL_L2_STREAM
+                if batch < TENSOR_FROM:
+                    assert np.max(np.abs(out - expected)) < 1e-3, (case.name, batch, offset)
+                    assert oracle.rel_l2(out, ref) <= REL_L2_STREAM
+                else:
+                    # the reference allows 0.08 here (half tiles / MPS); bf16 tiles on these small sums stay far inside
+                    assert np.max(np.abs(out - expected)) < case.tol, (case.name, batch, offset)
+                    assert oracle.rel_l2(out, ref) <= REL_L2_TENSOR
+                    tiles = oracle.matmul_bf16_tiles(x, packed, scales, biases, packed.shape[0], threads=8)
+                    assert oracle.rel_l2(out, tiles) <= 2e-4
 
 
 def test_matvec_convenience_entry(runtime, golden):
@@ -84,7 +93,9 @@ def test_mlp_fixture(runtime, oracle, golden):
         expected = golden_rows(case, golden[case.name], batch)
         tol = case.extra["decode_tol"] if batch == 1 else case.tol
         assert np.max(np.abs(out - expected)) < tol
-        assert oracle.rel_l2(out, oracle.mlp(x, *trips, 64, 64, form=0)) < 2e-3
+        assert oracle.rel_l2(out, oracle.mlp(x, *trips, 64, 64, form=0)) < 4e-3
+        if batch >= TENSOR_FROM:
+            assert oracle.rel_l2(out, oracle.mlp(x, *trips, 64, 64, form=1)) < 5e-4
 
 
 def test_incomplete_group_is_rejected(runtime):

@@ -54,7 +54,11 @@ def test_short_batch_widths_bf16(runtime, oracle, m):
     job = upload_matrix(runtime, *trip)
     out = runtime.q4_affine_matmul_mapped_batch(bits, m, [job])[0]
     assert out.shape == (m, n)
-    assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 1e-5
+    if m < 16:
+        assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 1e-5
+    else:  # tensor-core path: bf16 tiles
+        assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 2e-3
+        assert oracle.rel_l2(out, oracle.matmul_bf16_tiles(xf, *trip, n)) <= 2e-4
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 5])
@@ -170,3 +174,33 @@ def test_full_size_layer_set_by_linearity(runtime, oracle):
             w, s, b = oracle.synth_q4(SEED, 200 + i, 16, k, row0=r0)
             ref = oracle.matmul_factored_f32(x1, w, s, b, 16)[0]
             assert oracle.rel_l2(y1[i][r0:r0 + 16], ref) <= 1e-5
+
+
+@pytest.mark.parametrize("m,n,k,offset", [(16, 200, 1024, 0), (17, 129, 128, 0), (64, 11, 128, 0), (100, 300, 640, 2),
+                                           (256, 3, 128, 1), (300, 513, 1024, 0), (600, 128, 5120, 0), (33, 1000, 17408, 2)])
+def test_tensor_core_gemm_shapes(runtime, oracle, m, n, k, offset):
+    """Prefill path (tcgen05): ragged M and N tiles, every tile width the dispatcher picks, misaligned tensors.
+    Tolerance: relative L2 <= 2e-3 against the exact fp32 oracle (bf16 rounding of w), <= 2e-4 against the
+    oracle that rounds w to bf16 the same way."""
+    trip = synth(oracle, 300 + m, n, k)
+    bits, xf = x_bf16(oracle, 9, m, k)
+    job = upload_matrix(runtime, *trip, offset=offset)
+    out = runtime.q4_affine_matmul_mapped_batch(bits, m, [job])[0]
+    assert oracle.rel_l2(out, oracle.matmul_bf16_tiles(xf, *trip, n, threads=8)) <= 2e-4
+    assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n, threads=8)) <= 2e-3
+    # fp32 activations are rounded to bf16 on this path (the reference rounds to half, shaders/qwen38.metal:3793-3796)
+    out32 = runtime.q4_affine_matmul_mapped_batch(xf.reshape(-1), m, [job])[0]
+    assert np.array_equal(out32, out)
+
+
+def test_tensor_core_gemm_residual_and_grouped(runtime, oracle):
+    m, k = 40, 512
+    trips = [synth(oracle, 400 + i, n, k) for i, n in enumerate((70, 130))]
+    jobs = [upload_matrix(runtime, *t) for t in trips]
+    bits, xf = x_bf16(oracle, 10, m, k)
+    outs = runtime.q4_affine_matmul_mapped_batch(bits, m, jobs)
+    res = [np.full((m, t[0].shape[0]), 0.5, dtype=np.float32) for t in trips]
+    added = runtime.q4_affine_matmul_add_mapped_batch(bits, m, jobs, res)
+    for out, add, t in zip(outs, added, trips):
+        assert oracle.rel_l2(out, oracle.matmul_bf16_tiles(xf, *t, t[0].shape[0])) <= 2e-4
+        assert np.allclose(add, out + 0.5, rtol=0, atol=1e-5)
