@@ -158,6 +158,21 @@ int q4b_synth_q4_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, float s
 int q4b_synth_bf16_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, uint64_t count, uint16_t *out_dev,
                           void *stream);
 
+/* ---- for callers that cannot allocate ---- */
+
+/* No counterpart in the reference. One decode matvec (one projection, one bf16 activation row of k <= 32768
+ * inputs, any byte alignment of the three tensors) that calls no cudaMalloc/cudaFree and no allocating library
+ * routine: every scratch buffer lives in a static device array of about 1.1 MB that each GPU loading the library
+ * holds until exit. For code that only receives pointers and a stream, or runs where allocator traffic is
+ * forbidden. All pointers are device pointers on `device`; out_dev receives n floats. The array is shared by all
+ * calls on a device and keeps the last call's contents: calls that overlap on the GPU race on it, so order them.
+ * The first call on a device also looks up the array's address and the kernel occupancy; make it outside any
+ * stream capture. Shapes beyond the limits are rejected with Q4B_UNSUPPORTED.
+ * q4b_noalloc_last_error() gives the message of the calling thread's last failed call. */
+int q4b_matvec_noalloc(int device, const void *x_bf16_dev, uint64_t k, const void *weights_dev, const void *scales_dev,
+                       const void *biases_dev, uint64_t n, float *out_dev, void *stream);
+const char *q4b_noalloc_last_error(void);
+
 /* ---- introspection ---- */
 
 /* Name of the kernel variant the dispatcher would pick (tracing aid, cf. QWEN38_PAIR_TRACE). */

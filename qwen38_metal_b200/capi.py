@@ -77,6 +77,7 @@ def load() -> C.CDLL:
         "q4b_trace_read": [vp, vp, u32, P(u32)],
         "q4b_profile_end": [vp, P(u64), P(C.c_double), P(u64), P(u64)],
         "q4b_device_status": [vp],
+        "q4b_matvec_noalloc": [i32, vp, u64, vp, vp, vp, u64, vp, vp],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -86,6 +87,8 @@ def load() -> C.CDLL:
     lib.q4b_runtime_destroy.restype = None
     lib.q4b_last_error.argtypes = []
     lib.q4b_last_error.restype = C.c_char_p
+    lib.q4b_noalloc_last_error.argtypes = []
+    lib.q4b_noalloc_last_error.restype = C.c_char_p
     lib.q4b_status_name.argtypes = [i32]
     lib.q4b_status_name.restype = C.c_char_p
     _lib = lib
@@ -98,5 +101,5 @@ EXPORTS = [
     "q4b_shard_info", "q4b_offset_is_aligned", "q4b_matvec_batch", "q4b_matmul_batch", "q4b_argmax_batch",
     "q4b_mlp_batch", "q4b_matmul_add_batch", "q4b_dequantize_row", "q4b_matmul_batch_device",
     "q4b_argmax_batch_device", "q4b_swiglu_device", "q4b_rms_unit_bf16_device", "q4b_synth_q4_device",
-    "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status",
+    "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status", "q4b_matvec_noalloc", "q4b_noalloc_last_error",
 ]
