@@ -153,7 +153,7 @@ def run_ours(args) -> int:
 
     from qwen38_metal_b200 import build, capi
     from qwen38_metal_b200.runtime import CudaRuntime
-    from qwen38_metal_b200.stack import SyntheticStack, token_bytes
+    from qwen38_metal_b200.stack import SyntheticStack, gather_rows, pick_token, token_bytes
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -174,10 +174,7 @@ def run_ours(args) -> int:
     gather = None
     if world > 1:
         def gather(tensor, proj):
-            rows = proj.total_rows // world
-            if rows * world != proj.total_rows:
-                raise SystemExit("row counts must divide the GPU count in this benchmark")
-            dist.all_gather_into_tensor(tensor[:proj.total_rows], tensor[proj.row0:proj.row0 + rows])
+            gather_rows(dist, tensor, proj.total_rows, rank, world)
 
     stream = torch.cuda.Stream()
     host_x = torch.empty(stack.hidden, dtype=torch.bfloat16).pin_memory()
@@ -199,9 +196,7 @@ def run_ours(args) -> int:
             pairs[rank, 0:1].copy_(stack.best)
             pairs[rank, 1:2].copy_(stack.token.to(torch.float32))
             dist.all_gather_into_tensor(pairs.view(-1), pairs[rank])
-            top = pairs[:, 0].max()
-            ids = torch.where(pairs[:, 0] == top, pairs[:, 1], torch.full_like(pairs[:, 1], 3.0e38))
-            stack.token.copy_(ids.min().to(torch.int32).reshape(1))
+            stack.token.copy_(pick_token(pairs).to(torch.int32).reshape(1))
 
         lm_head_pick()
         stream.synchronize()
@@ -243,6 +238,8 @@ def run_ours(args) -> int:
         barrier()
         ms_e2e = e2.elapsed_time(e3)
         clocks = sampler.stop()
+        if world > 1 and rank != 0:
+            pass
         # ---- per-kernel timing of the projection kernel (no graph: events around each launch) -----
         rt.profile_begin()
         stack.decode_token(stream.cuda_stream, gather)
@@ -290,8 +287,13 @@ def run_ours(args) -> int:
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line))
     if world > 1:
+        # A captured graph still references the communicator; tearing the process group down with it alive has
+        # hung at exit, so leave together and let process exit release everything.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

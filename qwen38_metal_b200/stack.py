@@ -52,6 +52,30 @@ def token_bytes(layers: int = 64, hidden: int = HIDDEN, inter: int = INTER, voca
     return layers * per_layer + weight_bytes(vocab, hidden)
 
 
+def gather_rows(dist, tensor, total_rows: int, rank: int, world: int) -> None:
+    """Make a row-sharded output whole on every rank, in place: rank r has written rows
+    [floor(r*N/W), floor((r+1)*N/W)) of `tensor`. Even splits use one all-gather into the tensor itself;
+    uneven splits (N not divisible by W, possibly empty slices) fall back to one broadcast per rank."""
+    if world == 1:
+        return
+    if total_rows % world == 0:
+        rows = total_rows // world
+        dist.all_gather_into_tensor(tensor[:total_rows], tensor[rank * rows:(rank + 1) * rows])
+        return
+    for r in range(world):
+        r0, r1 = shard_rows(total_rows, r, world)
+        if r1 > r0:
+            dist.broadcast(tensor[r0:r1], src=r)
+
+
+def pick_token(pairs):
+    """pairs: [world][2] float tensor of (best logit, token id) per vocabulary slice. The winner is the greatest
+    logit; equal logits go to the lowest id (shaders/qwen38.metal:4218-4221). Returns a 0-d float tensor."""
+    top = pairs[:, 0].max()
+    ids = torch.where(pairs[:, 0] == top, pairs[:, 1], torch.full_like(pairs[:, 1], 3.0e38))
+    return ids.min()
+
+
 @dataclass
 class Projection:
     job: MappedQ4AffineJob | None  # None when this rank owns no rows
