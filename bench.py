@@ -168,7 +168,7 @@ def run_ours(args) -> int:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     build.build()
     rt = CudaRuntime(local_rank)
-    stack = SyntheticStack(rt, layers=args.layers, rank=rank, world=world, seed=SEED, device=local_rank)
+    stack = SyntheticStack(rt, layers=args.layers, rank=rank, world=world, seed=SEED, device=local_rank, misalign=args.misalign)
     total_bytes = token_bytes(layers=args.layers)
 
     gather = None
@@ -211,17 +211,45 @@ def run_ours(args) -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # One GPU: the whole token as one persistent cooperative kernel. The graph of per-stage launches stays as the
+    # multi-GPU path (its all-gathers are NCCL calls between kernels) and is reported beside it on one GPU.
+    chain = None
+    if world == 1 and not args.no_chain:
+        chain = stack.build_chain()
+        with torch.cuda.stream(stream):
+            chain.run(stream.cuda_stream)
+            stream.synchronize()
+        rt.device_status()
+
+    def step():
+        if chain is not None:
+            chain.run(stream.cuda_stream)
+        else:
+            graph.replay()
+
     # ---- device-resident timing: K graph replays --------------------------------------------
     with torch.cuda.stream(stream):
+        ms_graph = None
+        if chain is not None:
+            for _ in range(3):
+                graph.replay()
+            stream.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            g1.record(stream)
+            stream.synchronize()
+            ms_graph = g0.elapsed_time(g1)
         for _ in range(max(3, args.warmup)):
-            graph.replay()
+            step()
         barrier()
         sampler = ClockSampler(local_rank)
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
-            graph.replay()
+            step()
         e1.record(stream)
         barrier()
         ms = e0.elapsed_time(e1)
@@ -231,7 +259,7 @@ def run_ours(args) -> int:
         e2.record(stream)
         for _ in range(args.steps):
             stack.x.copy_(host_x, non_blocking=True)
-            graph.replay()
+            step()
             host_tok[:1].copy_(stack.token, non_blocking=True)
             stream.synchronize()
         e3.record(stream)
@@ -246,6 +274,7 @@ def run_ours(args) -> int:
         stream.synchronize()
         prof = rt.profile_end()
 
+    rt.device_status()
     if world > 1:
         t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -264,21 +293,32 @@ def run_ours(args) -> int:
                        "layers": args.layers, "hidden": stack.hidden, "intermediate": stack.inter,
                        "vocab": stack.vocab, "bytes_per_token": total_bytes, "seed": SEED,
                        "row_sharding": f"{world}-way", "l2": "13.75 GB streamed per step, far larger than L2",
-                       "misaligned": "every other projection starts 2 bytes off a 16-byte boundary"},
+                       "misaligned": f"every other projection starts {args.misalign} bytes off a 16-byte boundary"},
             "tokens_per_s": args.steps / (ms * 1e-3),
             "frac_of_8TBs": value / (NOMINAL_HBM_GBS * world),
             "frac_of_measured_hbm": value / (peak * world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": stack.hidden * 2,
                     "d2h_bytes_per_step": 4, "tokens_per_s": args.steps / (ms_e2e * 1e-3),
                     "what": "pinned input activation -> HBM, captured token graph, token id -> host, sync per step"},
-            "gpu_launches": launches_per_token * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "q4_gemv_kernel", "achieved": achieved, "peak": peak,
+            "gpu_launches": (2 if chain is not None else launches_per_token) * args.steps,
+            "path": "persistent decode chain (one cooperative launch per token)" if chain is not None
+                    else "CUDA graph of per-stage launches + NCCL all-gathers",
+            "roofline": {"bound": "hbm", "kernel": "q4_gemv_fast_kernel / q4_gemv_generic_kernel (per-stage launches)", "achieved": achieved, "peak": peak,
                          "peak_source": peak_source, "unit": UNIT, "frac": achieved / peak if peak else None,
                          "frac_of_8TBs": achieved / NOMINAL_HBM_GBS, "launches": prof["launches"],
                          "avg_launch_us": prof["ms"] * 1e3 / max(1, prof["launches"]),
                          "bytes_per_launch": prof["bytes"] / max(1, prof["launches"]), "traffic": None},
             "clocks": clocks,
         }
+        if chain is not None:
+            # the step IS one launch of q4_stack_kernel: its duration is the step time, its bytes the token's
+            line["roofline_per_stage_launches"] = line["roofline"]
+            line["roofline"] = {"bound": "hbm", "kernel": "q4_stack_kernel", "achieved": value, "peak": peak,
+                                "peak_source": peak_source, "unit": UNIT, "frac": value / peak,
+                                "frac_of_8TBs": value / NOMINAL_HBM_GBS, "launches": args.steps,
+                                "avg_launch_us": ms * 1e3 / args.steps, "bytes_per_launch": total_bytes, "traffic": None}
+            line["launch_per_stage_graph"] = {"value": total_bytes * args.steps / (ms_graph * 1e-3) / 1e9, "unit": UNIT,
+                                              "ms_per_step": ms_graph / args.steps, "gpu_launches": launches_per_token}
         if world == 1 and not args.no_cpu_baseline:
             from oracle import q4_oracle as oracle
 
@@ -306,6 +346,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--misalign", type=int, default=2, help="byte offset of every other projection from a 16-byte boundary")
+    ap.add_argument("--no-chain", action="store_true", help="time the CUDA graph of per-stage launches on one GPU too")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -151,6 +151,41 @@ int q4b_swiglu_device(q4b_runtime *rt, const float *gate_dev, const float *up_de
 int q4b_rms_unit_bf16_device(q4b_runtime *rt, const float *in_dev, uint32_t rows, uint32_t n, float eps,
                              uint16_t *out_bf16_dev, void *stream);
 
+/* ---- persistent decode chain (decode_layers, src/metal_runtime.rs:2022-2081: a whole token in one submission) ---- */
+
+#define Q4B_X_BF16 0u    /* activation = bf16 vector src0[k] */
+#define Q4B_X_SWIGLU 1u  /* activation = bf16(silu(src0) * src1), fp32 vectors (qwen38_swiglu_rows) */
+#define Q4B_X_RMS 2u     /* activation = bf16(src0 / sqrt(mean(src0^2) + eps)), fp32 vector */
+
+/* One stage: build an activation of k elements from device vectors, then run n_jobs projections of it (M=1) into
+ * outputs[i] (device, jobs[i].output_rows floats). Stages run in order; a stage may read what earlier stages wrote. */
+typedef struct q4b_stage {
+    uint32_t x_kind;
+    float eps;
+    uint64_t k;
+    const void *src0;
+    const void *src1;
+    void *x_bf16_out; /* optional: the bf16 activation that was built (k elements) */
+    const q4b_job *jobs;
+    uint32_t n_jobs;
+    float *const *outputs;
+} q4b_stage;
+
+typedef struct q4b_chain q4b_chain;
+
+/* Compiles a list of stages into one cooperative kernel launch (one resident block per SM, grid barriers between
+ * stages, next-stage weights prefetched across the barrier). Requires k % 512 == 0 and k <= q4b_chain_max_k().
+ * If logits is not null, the vocab floats there are reduced to *token_dev (+ index_base; ties to the lowest index)
+ * and the winning value to *best_dev after the last stage. */
+int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32_t n_stages, const float *logits, uint32_t vocab,
+                     uint32_t index_base, uint32_t *token_dev, float *best_dev, q4b_chain **out);
+int q4b_chain_run_device(q4b_chain *chain, void *stream);
+void q4b_chain_destroy(q4b_chain *chain);
+uint64_t q4b_chain_max_k(void);
+/* Per-block, per-stage timeline of the last run of a chain created while tracing was enabled (q4b_trace_enable):
+ * four device-clock stamps in ns -- stage start, activation built, block's work done, barrier passed. */
+int q4b_chain_trace_read(q4b_chain *chain, uint64_t *stamps, uint64_t capacity_words, uint32_t *blocks, uint32_t *stages);
+
 /* ---- seeded synthetic tensors, generated in HBM (benchmark inputs) ---- */
 
 int q4b_synth_q4_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, float sigma, uint64_t row0,

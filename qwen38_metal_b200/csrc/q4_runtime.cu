@@ -754,6 +754,156 @@ extern "C" int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t 
 }
 
 // ------------------------------------------------------------------------------------------
+// persistent decode chain
+// ------------------------------------------------------------------------------------------
+
+struct q4b_chain {
+    q4b_runtime *rt = nullptr;
+    void *stages_dev = nullptr;
+    uint32_t n_stages = 0;
+    uint32_t x_halfs = 0;
+    unsigned int *barrier = nullptr;  // 2 words, then per-block argmax candidates
+    float *part_val = nullptr;
+    uint32_t *part_idx = nullptr;
+    const float *logits = nullptr;
+    uint32_t vocab = 0, index_base = 0;
+    uint32_t *token = nullptr;
+    float *best = nullptr;
+    unsigned long long *trace = nullptr;  // [blocks][stages][4] when tracing was on at creation
+};
+
+extern "C" uint64_t q4b_chain_max_k(void) { return q4k_stack_max_k(); }
+
+extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32_t n_stages, const float *logits, uint32_t vocab,
+                                uint32_t index_base, uint32_t *token_dev, float *best_dev, q4b_chain **out) {
+    if (int st = check_rt(rt)) return st;
+    if (!stages || n_stages == 0 || !out) return fail(Q4B_INVALID_ARGUMENT, "stage list or output handle is null");
+    if (logits && (!token_dev || vocab == 0)) return fail(Q4B_INVALID_ARGUMENT, "token pointer is null or vocabulary empty");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    const uint32_t warps = q4k_stack_warps();
+    const size_t stage_bytes = q4k_stack_stage_bytes();
+    std::vector<uint8_t> image(stage_bytes * n_stages);
+    uint32_t x_halfs = 0;
+    for (uint32_t si = 0; si < n_stages; ++si) {
+        const q4b_stage &S = stages[si];
+        if (S.x_kind > Q4B_X_RMS) return fail(Q4B_INVALID_ARGUMENT, "unknown activation kind %u in stage %u", S.x_kind, si);
+        if (!S.src0 || (S.x_kind == Q4B_X_SWIGLU && !S.src1) || !S.outputs) return fail(Q4B_INVALID_ARGUMENT, "stage %u has a null pointer", si);
+        if (((uintptr_t)S.src0 | (uintptr_t)S.src1) & 15u) return fail(Q4B_INVALID_ARGUMENT, "stage %u: source vectors must be 16-byte aligned", si);
+        if (S.n_jobs > (uint32_t)q4::kMaxJobs) return fail(Q4B_UNSUPPORTED, "stage %u has more than %d projections", si, q4::kMaxJobs);
+        std::vector<Resolved> resolved;
+        if (int st = resolve_jobs(rt, S.jobs, S.n_jobs, 1, S.k, &resolved)) return st;
+        if (S.k % 512 != 0 || S.k > q4k_stack_max_k())
+            return fail(Q4B_UNSUPPORTED, "stage %u: the decode chain needs k %% 512 == 0 and k <= %u", si, q4k_stack_max_k());
+        const uint32_t k = (uint32_t)S.k, groups = k / 64, kp = (k + 127u) & ~127u;
+        x_halfs = kp > x_halfs ? kp : x_halfs;
+        q4::GemvParams p;
+        memset(&p, 0, sizeof p);
+        uint32_t tiles = 0;
+        for (uint32_t i = 0; i < S.n_jobs; ++i) {
+            if (!S.outputs[i]) return fail(Q4B_INVALID_ARGUMENT, "stage %u output %u is null", si, i);
+            q4::GemvJob &j = p.jobs[i];
+            j.w = resolved[i].w;
+            j.s = resolved[i].s;
+            j.b = resolved[i].b;
+            j.out = S.outputs[i];
+            j.n = resolved[i].n;
+            j.out_stride = resolved[i].n;
+            j.tile_begin = tiles;
+            j.w_misalign = (uint32_t)((uintptr_t)resolved[i].w & 15u);
+            tiles += (resolved[i].n + 15u) / 16u;
+        }
+        p.n_jobs = S.n_jobs;
+        p.v_cols = 1;
+        p.vpad = 4;
+        p.m_rows = 1;
+        p.k = k;
+        p.kp = kp;
+        p.groups = groups;
+        p.cpt = (groups + 1u) / 2u;
+        p.units = (uint64_t)tiles * p.cpt;
+        uint64_t workers = (uint64_t)rt->sm_count * warps;
+        const uint64_t min_chunks = (p.cpt + 7u) / 8u;
+        if (workers > p.units / min_chunks) workers = p.units / min_chunks;
+        if (workers == 0) workers = 1;
+        p.workers = (uint32_t)workers;
+        p.partials = (float *)rt->partials.ptr;
+        p.counters = (unsigned int *)rt->counters.ptr;
+        q4k_stack_fill_stage(image.data() + stage_bytes * si, &p, S.x_kind, S.eps, S.src0, S.src1, (uint16_t *)S.x_bf16_out);
+    }
+    if (!q4k_stack_supported(x_halfs, rt->sm_count))
+        return fail(Q4B_UNSUPPORTED, "the decode chain kernel cannot be resident with k = %u on this device", x_halfs);
+    q4b_chain *c = new (std::nothrow) q4b_chain();
+    if (!c) return fail(Q4B_CUDA_ERROR, "out of host memory");
+    c->rt = rt;
+    c->n_stages = n_stages;
+    c->x_halfs = x_halfs;
+    c->logits = logits;
+    c->vocab = vocab;
+    c->index_base = index_base;
+    c->token = token_dev;
+    c->best = best_dev;
+    cudaError_t e = cudaMalloc(&c->stages_dev, image.size());
+    if (e == cudaSuccess) e = cudaMemcpy(c->stages_dev, image.data(), image.size(), cudaMemcpyHostToDevice);
+    void *aux = nullptr;
+    if (e == cudaSuccess) e = cudaMalloc(&aux, 256 + (size_t)rt->sm_count * 8);
+    if (e == cudaSuccess) e = cudaMemset(aux, 0, 256 + (size_t)rt->sm_count * 8);
+    if (e != cudaSuccess) {
+        if (c->stages_dev) cudaFree(c->stages_dev);
+        if (aux) cudaFree(aux);
+        delete c;
+        return fail_cuda(e, "decode chain allocation");
+    }
+    if (rt->tracing) {
+        const size_t tb = (size_t)rt->sm_count * n_stages * 32;
+        if (cudaMalloc((void **)&c->trace, tb) == cudaSuccess) cudaMemset(c->trace, 0, tb);
+        else c->trace = nullptr;
+    }
+    c->barrier = (unsigned int *)aux;
+    c->part_val = (float *)((uint8_t *)aux + 256);
+    c->part_idx = (uint32_t *)((uint8_t *)aux + 256 + (size_t)rt->sm_count * 4);
+    *out = c;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_chain_run_device(q4b_chain *chain, void *stream) {
+    if (!chain || !chain->rt) return fail(Q4B_INVALID_ARGUMENT, "chain handle is null");
+    q4b_runtime *rt = chain->rt;
+    DeviceGuard guard(rt->device);
+    Q4B_CUDA(q4k_stack_launch(chain->stages_dev, chain->n_stages, chain->x_halfs, chain->barrier, (int *)rt->error_flag.ptr,
+                              chain->logits, chain->vocab, chain->index_base, chain->part_val, chain->part_idx, chain->token,
+                              chain->best, chain->trace, rt->sm_count, (cudaStream_t)stream),
+             "decode chain launch");
+    rt->launches++;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_chain_trace_read(q4b_chain *chain, uint64_t *stamps, uint64_t capacity_words, uint32_t *blocks, uint32_t *stages) {
+    if (!chain || !chain->rt || !stamps || !blocks || !stages) return fail(Q4B_INVALID_ARGUMENT, "chain handle or output pointer is null");
+    if (!chain->trace) return fail(Q4B_UNSUPPORTED, "the chain was created without tracing (q4b_trace_enable before q4b_chain_create)");
+    DeviceGuard guard(chain->rt->device);
+    const uint64_t words = (uint64_t)chain->rt->sm_count * chain->n_stages * 4;
+    if (capacity_words < words) return fail(Q4B_WRONG_LENGTH, "trace buffer has %llu elements, expected %llu", (unsigned long long)capacity_words, (unsigned long long)words);
+    Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
+    Q4B_CUDA(cudaMemcpy(stamps, chain->trace, words * 8, cudaMemcpyDeviceToHost), "trace download");
+    *blocks = (uint32_t)chain->rt->sm_count;
+    *stages = chain->n_stages;
+    return Q4B_OK;
+}
+
+extern "C" void q4b_chain_destroy(q4b_chain *chain) {
+    if (!chain) return;
+    if (chain->rt) {
+        DeviceGuard guard(chain->rt->device);
+        cudaDeviceSynchronize();
+        if (chain->stages_dev) cudaFree(chain->stages_dev);
+        if (chain->barrier) cudaFree(chain->barrier);
+        if (chain->trace) cudaFree(chain->trace);
+    }
+    delete chain;
+}
+
+// ------------------------------------------------------------------------------------------
 // synthetic tensors, introspection
 // ------------------------------------------------------------------------------------------
 

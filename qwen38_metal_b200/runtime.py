@@ -248,6 +248,23 @@ class CudaRuntime:
     def rms_unit_bf16_device(self, in_ptr: int, rows: int, n: int, eps: float, out_ptr: int, stream: int = 0) -> None:
         _check(self._lib.q4b_rms_unit_bf16_device(self._h, in_ptr, rows, n, eps, out_ptr, stream))
 
+    # -- persistent decode chain ----------------------------------------------------------------------
+    def chain_create(self, stages, logits_ptr: int = 0, vocab: int = 0, index_base: int = 0, token_ptr: int = 0,
+                     best_ptr: int = 0) -> "DecodeChain":
+        """stages: list of dicts {x_kind, k, src0, src1, x_bf16_out, jobs, outputs, eps} with raw device pointers."""
+        arr = (capi.Stage * len(stages))()
+        keep = []
+        for i, s in enumerate(stages):
+            jobs = _jobs(s["jobs"])
+            outs = (C.c_void_p * len(s["jobs"]))(*s["outputs"])
+            keep += [jobs, outs]
+            arr[i] = capi.Stage(s["x_kind"], s.get("eps", 1e-6), s["k"], s["src0"], s.get("src1") or None,
+                                s.get("x_bf16_out") or None, jobs, len(s["jobs"]), outs)
+        handle = C.c_void_p()
+        _check(self._lib.q4b_chain_create(self._h, arr, len(stages), logits_ptr or None, vocab, index_base,
+                                          token_ptr or None, best_ptr or None, C.byref(handle)))
+        return DecodeChain(self, handle)
+
     # -- synthetic tensors ---------------------------------------------------------------------
     def synth_q4(self, seed: int, tensor: int, sigma: float, row0: int, rows: int, k: int, job) -> None:
         cj = job.to_c()
@@ -279,3 +296,18 @@ class CudaRuntime:
         n = C.c_uint64()
         _check(self._lib.q4b_launch_count(self._h, C.byref(n)))
         return n.value
+
+
+class DecodeChain:
+    """A compiled list of stages run by one cooperative kernel launch (`q4b_chain_*`)."""
+
+    def __init__(self, rt: CudaRuntime, handle):
+        self._rt, self._h = rt, handle
+
+    def run(self, stream: int = 0) -> None:
+        _check(self._rt._lib.q4b_chain_run_device(self._h, stream))
+
+    def close(self) -> None:
+        if self._h:
+            self._rt._lib.q4b_chain_destroy(self._h)
+            self._h = None

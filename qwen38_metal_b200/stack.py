@@ -143,6 +143,27 @@ class SyntheticStack:
         if jobs:
             self.rt.matmul_batch_device(x_ptr, capi.Q4B_BF16, 1, k, jobs, ptrs, 0, stream)
 
+    def build_chain(self):
+        """The whole token as one persistent kernel (single GPU): stage list for `CudaRuntime.chain_create`."""
+        if self.world != 1:
+            raise ValueError("the persistent decode chain covers one GPU; sharded stacks use decode_token with gathers")
+        stages = []
+        gate, up = self.outs[self.gate_i], self.outs[self.up_i]
+        for layer in range(self.layers):
+            projs = self.proj[layer]
+            first = layer == 0
+            stages.append({"x_kind": capi.X_BF16 if first else capi.X_RMS, "k": self.hidden,
+                           "src0": self.x.data_ptr() if first else self.d.data_ptr(), "eps": 1e-6,
+                           "x_bf16_out": 0 if first else self.x.data_ptr(),
+                           "jobs": [p.job for p in projs], "outputs": [o.data_ptr() for o in self.outs]})
+            stages.append({"x_kind": capi.X_SWIGLU, "k": self.inter, "src0": gate.data_ptr(), "src1": up.data_ptr(),
+                           "x_bf16_out": self.h.data_ptr(), "jobs": [self.down[layer].job], "outputs": [self.d.data_ptr()]})
+        self.logits = torch.zeros(self.vocab, dtype=torch.float32, device=self.device)
+        stages.append({"x_kind": capi.X_RMS, "k": self.hidden, "src0": self.d.data_ptr(), "eps": 1e-6,
+                       "x_bf16_out": self.x.data_ptr(), "jobs": [self.lm_head.job], "outputs": [self.logits.data_ptr()]})
+        return self.rt.chain_create(stages, self.logits.data_ptr(), self.vocab, 0, self.token.data_ptr(),
+                                    self.best.data_ptr())
+
     def decode_token(self, stream: int = 0, gather=None) -> None:
         """Enqueue one token on `stream` (a raw cudaStream_t). `gather(tensor, proj)` makes a row-sharded
         output whole on every rank; it is None on one GPU."""

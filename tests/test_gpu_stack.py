@@ -47,3 +47,44 @@ def test_small_stack_matches_oracle_chain(runtime, oracle):
     order = np.sort(logits)
     if order[-1] - order[-2] > 1e-2 * abs(order[-1]):
         assert int(stack.token.item()) == int(np.argmax(logits))
+
+
+@pytest.mark.parametrize("misalign", [0, 2, 6])
+def test_persistent_chain_matches_launch_per_stage_path(runtime, oracle, misalign):
+    """One cooperative launch for the whole token against the same stack run stage by stage."""
+    import torch
+
+    from qwen38_metal_b200.stack import SyntheticStack
+
+    layers, hidden, inter, vocab = 3, 512, 1024, 1000
+    rows = (96, 32, 16, 48, 1024, 1024)
+    stack = SyntheticStack(runtime, layers=layers, hidden=hidden, inter=inter, vocab=vocab, layer_rows=rows,
+                           seed=78, misalign=misalign)
+    stream = torch.cuda.current_stream().cuda_stream
+    stack.reset_input(stream)
+    torch.cuda.synchronize()
+    x0 = stack.x.clone()
+    stack.decode_token(stream)
+    runtime.device_status()
+    ref_d, ref_token = stack.d.clone(), int(stack.token.item())
+    ref_outs = [o.clone() for o in stack.outs]
+    ref_x = stack.x.clone()
+
+    chain = stack.build_chain()
+    for _ in range(2):  # twice: barrier words, counters and partial slots must be reusable
+        stack.x.copy_(x0)
+        stack.d.zero_()
+        stack.token.zero_()
+        torch.cuda.synchronize()
+        chain.run(stream)
+        runtime.device_status()
+        assert oracle.rel_l2(stack.d.cpu().numpy(), ref_d.cpu().numpy()) <= 2e-3
+        for got, ref in zip(stack.outs, ref_outs):
+            assert oracle.rel_l2(got.cpu().numpy(), ref.cpu().numpy()) <= 2e-3
+        assert torch.equal(stack.x, ref_x) or oracle.rel_l2(stack.x.float().cpu().numpy(), ref_x.float().cpu().numpy()) <= 1e-2
+        logits = stack.logits.cpu().numpy()
+        assert int(stack.token.item()) == int(np.argmax(logits))
+        order = np.sort(logits)
+        if order[-1] - order[-2] > 1e-2 * abs(order[-1]):
+            assert int(stack.token.item()) == ref_token
+    chain.close()
