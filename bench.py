@@ -211,11 +211,12 @@ def run_ours(args) -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # One GPU: the whole token as one persistent cooperative kernel. The graph of per-stage launches stays as the
-    # multi-GPU path (its all-gathers are NCCL calls between kernels) and is reported beside it on one GPU.
+    # The whole token as one persistent cooperative kernel per GPU; with several GPUs the kernels exchange the
+    # row-sharded outputs with peer stores and share their barriers. The CUDA graph of per-stage launches (with
+    # NCCL all-gathers between kernels when sharded) is timed beside it.
     chain = None
-    if world == 1 and not args.no_chain:
-        chain = stack.build_chain()
+    if not args.no_chain:
+        chain = stack.build_chain() if world == 1 else stack.build_chain_sharded(dist)
         with torch.cuda.stream(stream):
             chain.run(stream.cuda_stream)
             stream.synchronize()
@@ -301,7 +302,8 @@ def run_ours(args) -> int:
                     "d2h_bytes_per_step": 4, "tokens_per_s": args.steps / (ms_e2e * 1e-3),
                     "what": "pinned input activation -> HBM, captured token graph, token id -> host, sync per step"},
             "gpu_launches": (2 if chain is not None else launches_per_token) * args.steps,
-            "path": "persistent decode chain (one cooperative launch per token)" if chain is not None
+            "path": ("persistent decode chain (one cooperative launch per token and GPU"
+                     + (", peer stores + cross-GPU barriers)" if world > 1 else ")")) if chain is not None
                     else "CUDA graph of per-stage launches + NCCL all-gathers",
             "roofline": {"bound": "hbm", "kernel": "q4_gemv_fast_kernel / q4_gemv_generic_kernel (per-stage launches)", "achieved": achieved, "peak": peak,
                          "peak_source": peak_source, "unit": UNIT, "frac": achieved / peak if peak else None,

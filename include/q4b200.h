@@ -169,16 +169,37 @@ typedef struct q4b_stage {
     const q4b_job *jobs;
     uint32_t n_jobs;
     float *const *outputs;
+    /* Row-sharded chains only, else null: peer_outputs[i * 8 + r] is where rank r keeps the rows of job i that this
+     * rank computes (peer memory opened with q4b_arena_open), or null when that output is not needed elsewhere. */
+    float *const *peer_outputs;
 } q4b_stage;
+
+/* The ranks of a row-sharded chain (one process per GPU). flags[r] and cand[r] are two small zeroed device arrays
+ * (8 x u32, 8 x 2 floats) living on rank r: entry [rank] is this GPU's own, the others are peer memory. */
+typedef struct q4b_peers {
+    uint32_t world;
+    uint32_t rank;
+    void *flags[8];
+    void *cand[8];
+} q4b_peers;
+
+/* Device memory that other processes on the same node may map: `handle` receives the 64-byte CUDA IPC handle to send
+ * to them; q4b_arena_open maps a peer's arena here and enables peer access. Zero-filled on creation. */
+int q4b_arena_create(q4b_runtime *rt, uint64_t bytes, void **device_ptr, uint8_t handle[64]);
+int q4b_arena_open(q4b_runtime *rt, const uint8_t handle[64], void **peer_ptr);
 
 typedef struct q4b_chain q4b_chain;
 
 /* Compiles a list of stages into one cooperative kernel launch (one resident block per SM, grid barriers between
  * stages, next-stage weights prefetched across the barrier). Requires k % 512 == 0 and k <= q4b_chain_max_k().
  * If logits is not null, the vocab floats there are reduced to *token_dev (+ index_base; ties to the lowest index)
- * and the winning value to *best_dev after the last stage. */
+ * and the winning value to *best_dev after the last stage.
+ * With `peers` (row-sharded stack, every rank creates the same chain over its own row slices) results are also stored
+ * into the other ranks' buffers with peer stores, every barrier spans all ranks, `vocab`/`index_base` describe this
+ * rank's slice and the token is the winner over all slices. All ranks must launch the chain the same number of
+ * times; a multi-rank chain must not be captured in a CUDA graph (its barrier epoch is a launch argument). */
 int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32_t n_stages, const float *logits, uint32_t vocab,
-                     uint32_t index_base, uint32_t *token_dev, float *best_dev, q4b_chain **out);
+                     uint32_t index_base, uint32_t *token_dev, float *best_dev, const q4b_peers *peers, q4b_chain **out);
 int q4b_chain_run_device(q4b_chain *chain, void *stream);
 void q4b_chain_destroy(q4b_chain *chain);
 uint64_t q4b_chain_max_k(void);

@@ -35,7 +35,14 @@ class Stage(C.Structure):
         ("x_kind", C.c_uint32), ("eps", C.c_float), ("k", C.c_uint64),
         ("src0", C.c_void_p), ("src1", C.c_void_p), ("x_bf16_out", C.c_void_p),
         ("jobs", C.POINTER(Job)), ("n_jobs", C.c_uint32), ("outputs", C.POINTER(C.c_void_p)),
+        ("peer_outputs", C.POINTER(C.c_void_p)),
     ]
+
+
+class Peers(C.Structure):
+    """q4b_peers: the ranks of a row-sharded chain."""
+
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("flags", C.c_void_p * 8), ("cand", C.c_void_p * 8)]
 
 
 X_BF16, X_SWIGLU, X_RMS = 0, 1, 2
@@ -89,7 +96,9 @@ def load() -> C.CDLL:
         "q4b_trace_read": [vp, vp, u32, P(u32)],
         "q4b_profile_end": [vp, P(u64), P(C.c_double), P(u64), P(u64)],
         "q4b_device_status": [vp],
-        "q4b_chain_create": [vp, P(Stage), u32, vp, u32, u32, vp, vp, P(vp)],
+        "q4b_chain_create": [vp, P(Stage), u32, vp, u32, u32, vp, vp, P(Peers), P(vp)],
+        "q4b_arena_create": [vp, u64, P(vp), C.c_char_p],
+        "q4b_arena_open": [vp, C.c_char_p, P(vp)],
         "q4b_chain_run_device": [vp, vp],
         "q4b_chain_trace_read": [vp, vp, u64, P(u32), P(u32)],
         "q4b_matvec_noalloc": [i32, vp, u64, vp, vp, vp, u64, vp, vp],
@@ -121,5 +130,5 @@ EXPORTS = [
     "q4b_mlp_batch", "q4b_matmul_add_batch", "q4b_dequantize_row", "q4b_matmul_batch_device",
     "q4b_argmax_batch_device", "q4b_swiglu_device", "q4b_rms_unit_bf16_device", "q4b_synth_q4_device",
     "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status", "q4b_matvec_noalloc", "q4b_noalloc_last_error", "q4b_chain_create", "q4b_chain_run_device",
-    "q4b_chain_destroy", "q4b_chain_max_k", "q4b_chain_trace_read",
+    "q4b_chain_destroy", "q4b_chain_max_k", "q4b_chain_trace_read", "q4b_arena_create", "q4b_arena_open",
 ]

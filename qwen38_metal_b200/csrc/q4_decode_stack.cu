@@ -17,6 +17,8 @@
 // leaves the kernel.
 #include <cooperative_groups.h>
 
+#include <cstring>
+
 #include "q4_gemv_core.cuh"
 
 namespace q4 {
@@ -33,6 +35,16 @@ struct StackStage {
     uint16_t *x_bf16_out;   // optional: block 0 stores the bf16 activation it built (next token's input, inspection)
 };
 
+// Cross-GPU part of a row-sharded chain. Every rank runs the same chain on its row slices; outputs that feed a
+// later stage are stored into every rank's buffers, and each grid barrier also waits for the other ranks.
+struct StackPeers {
+    uint32_t world, rank;
+    unsigned int *flags_local;             // [kMaxPeers] generation last announced by each rank, in this GPU's memory
+    unsigned int *flags_peer[kMaxPeers];   // the same array on every rank (this rank writes entry [rank] of each)
+    float2 *cand_local;                    // [kMaxPeers] (best logit, token id) candidates, in this GPU's memory
+    float2 *cand_peer[kMaxPeers];
+};
+
 struct StackParams {
     const StackStage *stages;
     uint32_t n_stages;
@@ -45,6 +57,8 @@ struct StackParams {
     uint32_t *part_idx;     // [gridDim.x]
     uint32_t *token;
     float *best;
+    const StackPeers *peers;    // null on one GPU
+    unsigned int epoch;         // with peers: barrier generations consumed by earlier launches (flags only grow)
     unsigned long long *trace;  // optional [blocks][n_stages][4] device-clock stamps (stage start, activation built, work done, barrier passed)
 };
 
@@ -64,25 +78,50 @@ __device__ __forceinline__ void lds_f32_keep(float &v, uint32_t addr, bool pred)
     asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.shared.f32 %0, [%1];\n\t}" : "+f"(v) : "r"(addr), "r"((uint32_t)pred) : "memory");
 }
 
-// Grid-wide barrier with a bounded wait. Returns false when it gave up (error flag raised).
-__device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &generation, int *error_flag) {
+// Grid-wide barrier with a bounded wait; with peers it is also a barrier across the GPUs of the chain.
+// Generations only grow (`generation` starts at the launch's epoch), so nothing has to be reset between launches.
+// Returns false when it gave up (error flag raised).
+__device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &generation, int *error_flag, const StackPeers *peers) {
     __syncthreads();
     int ok = 1;
     ++generation;
     if (threadIdx.x == 0) {
-        __threadfence();
+        if (peers) __threadfence_system();  // this block's peer stores are visible before its arrival counts
+        else __threadfence();
         const unsigned int old = atomicAdd(&bar[0], 1u);
         if (old == gridDim.x - 1) {
             bar[0] = 0;
+            if (peers) {
+                // every block of this GPU has arrived: tell the other ranks, then wait for all of them
+                for (uint32_t r = 0; r < peers->world; ++r) {
+                    if (r == peers->rank) continue;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers->flags_peer[r] + peers->rank), "r"(generation) : "memory");
+                }
+                for (uint32_t r = 0; r < peers->world && ok; ++r) {
+                    if (r == peers->rank) continue;
+                    uint32_t spins = 0;
+                    while (true) {
+                        unsigned int seen;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(peers->flags_local + r) : "memory");
+                        if ((int)(seen - generation) >= 0) break;
+                        if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
+                            *error_flag = 1;
+                            ok = 0;
+                            break;
+                        }
+                        __nanosleep(20);
+                    }
+                }
+            }
             __threadfence();
-            atomicExch(&bar[1], generation);
+            atomicExch(&bar[1], ok ? generation : 0xffffffffu);
         } else {
             uint32_t spins = 0;
             while (true) {
                 unsigned int seen;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar + 1) : "memory");
                 if (seen == generation) break;
-                if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
+                if (seen == 0xffffffffu || ++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
                     *error_flag = 1;
                     ok = 0;
                     break;
@@ -90,7 +129,8 @@ __device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &genera
                 __nanosleep(20);
             }
         }
-        __threadfence();
+        if (peers) __threadfence_system();
+        else __threadfence();
     }
     return __syncthreads_and(ok) != 0;
 }
@@ -304,7 +344,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
 #pragma unroll
         for (int w = 0; w < 4; ++w) xf[b][0][w] = make_uint4(0, 0, 0, 0);
 
-    uint32_t generation = 0;
+    uint32_t generation = sp.peers ? sp.epoch : 0;
     bool prefetched = false;
     Segment sg;
     uint32_t job_index = 0;
@@ -440,7 +480,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             __syncthreads();
             if (threadIdx.x == 0) tr[2] = stack_ns();
         }
-        if (!grid_barrier(sp.barrier, generation, sp.error_flag)) return;
+        if (!grid_barrier(sp.barrier, generation, sp.error_flag, sp.peers)) return;
         if (tr && threadIdx.x == 0) tr[3] = stack_ns();
     }
 
@@ -471,7 +511,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             sp.part_val[blockIdx.x] = bv;
             sp.part_idx[blockIdx.x] = bi;
         }
-        if (!grid_barrier(sp.barrier, generation, sp.error_flag)) return;
+        if (!grid_barrier(sp.barrier, generation, sp.error_flag, sp.peers)) return;
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             float fv = -INFINITY;
             uint32_t fi = 0xffffffffu;
@@ -480,8 +520,29 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                 const uint32_t ix = __ldcg(sp.part_idx + i);
                 if (v > fv || (v == fv && ix < fi)) { fv = v; fi = ix; }
             }
-            *sp.token = (fi == 0xffffffffu ? 0u : fi) + sp.index_base;
-            if (sp.best) *sp.best = fv;
+            const uint32_t mine = (fi == 0xffffffffu ? 0u : fi) + sp.index_base;
+            if (!sp.peers) {
+                *sp.token = mine;
+                if (sp.best) *sp.best = fv;
+            } else {
+                // candidates of every vocabulary slice go to every rank; the barrier below publishes them
+                const float2 c = make_float2(fv, __uint_as_float(mine));
+                for (uint32_t r = 0; r < sp.peers->world; ++r) sp.peers->cand_peer[r][sp.peers->rank] = c;
+            }
+        }
+        if (sp.peers) {
+            if (!grid_barrier(sp.barrier, generation, sp.error_flag, sp.peers)) return;
+            if (blockIdx.x == 0 && threadIdx.x == 0) {
+                float fv = -INFINITY;
+                uint32_t fi = 0xffffffffu;
+                for (uint32_t r = 0; r < sp.peers->world; ++r) {
+                    const float2 c = __ldcg(sp.peers->cand_local + r);
+                    const uint32_t ix = __float_as_uint(c.y);
+                    if (c.x > fv || (c.x == fv && ix < fi)) { fv = c.x; fi = ix; }
+                }
+                *sp.token = fi;
+                if (sp.best) *sp.best = fv;
+            }
         }
     }
 }
@@ -500,6 +561,19 @@ size_t stack_smem_bytes(uint32_t x_halfs) {
 }
 }  // namespace
 
+extern "C" size_t q4k_stack_peers_bytes(void) { return sizeof(q4::StackPeers); }
+extern "C" void q4k_stack_fill_peers(void *image, uint32_t world, uint32_t rank, void *const *flags, void *const *cand) {
+    q4::StackPeers *p = static_cast<q4::StackPeers *>(image);
+    memset(p, 0, sizeof *p);
+    p->world = world;
+    p->rank = rank;
+    p->flags_local = static_cast<unsigned int *>(flags[rank]);
+    p->cand_local = static_cast<float2 *>(cand[rank]);
+    for (uint32_t r = 0; r < world; ++r) {
+        p->flags_peer[r] = static_cast<unsigned int *>(flags[r]);
+        p->cand_peer[r] = static_cast<float2 *>(cand[r]);
+    }
+}
 extern "C" size_t q4k_stack_stage_bytes(void) { return sizeof(q4::StackStage); }
 extern "C" uint32_t q4k_stack_warps(void) { return kStackWarps; }
 extern "C" uint32_t q4k_stack_max_k(void) { return q4::kStackMaxIters * kStackWarps * 32 * 8; }
@@ -534,8 +608,8 @@ extern "C" int q4k_stack_supported(uint32_t x_halfs, int sm_count) {
 
 extern "C" cudaError_t q4k_stack_launch(const void *stages_dev, uint32_t n_stages, uint32_t x_halfs, unsigned int *barrier,
                                         int *error_flag, const float *logits, uint32_t vocab, uint32_t index_base, float *part_val,
-                                        uint32_t *part_idx, uint32_t *token, float *best, unsigned long long *trace, int sm_count,
-                                        cudaStream_t stream) {
+                                        uint32_t *part_idx, uint32_t *token, float *best, unsigned long long *trace, const void *peers,
+                                        unsigned int epoch, int sm_count, cudaStream_t stream) {
     q4::StackParams sp;
     sp.stages = static_cast<const q4::StackStage *>(stages_dev);
     sp.n_stages = n_stages;
@@ -550,8 +624,13 @@ extern "C" cudaError_t q4k_stack_launch(const void *stages_dev, uint32_t n_stage
     sp.token = token;
     sp.best = best;
     sp.trace = trace;
-    cudaError_t e = cudaMemsetAsync(barrier, 0, 8, stream);
-    if (e != cudaSuccess) return e;
+    sp.peers = static_cast<const q4::StackPeers *>(peers);
+    sp.epoch = epoch;
+    cudaError_t e = cudaSuccess;
+    if (!peers) {  // with peers generations only grow; on one GPU the two words restart at zero
+        e = cudaMemsetAsync(barrier, 0, 8, stream);
+        if (e != cudaSuccess) return e;
+    }
     void *args[] = {&sp};
     return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(q4::q4_stack_kernel<kStackWarps>), dim3(sm_count), dim3(kStackWarps * 32),
                                        args, stack_smem_bytes(x_halfs), stream);

@@ -196,6 +196,12 @@ __device__ __forceinline__ void store_tile(const GemvParams &p, const float *row
             float *dst = job.out + (uint64_t)m * job.out_stride + row;
             if (p.accumulate) y += *dst;  // residual form: dst += projection
             *dst = y;
+            if (p.mirror) {  // the other ranks' copies of a row-sharded output (peer stores over NVLink)
+                for (uint32_t r = 0; r < p.world; ++r) {
+                    float *peer = p.mirror[job_index * kMaxPeers + r];
+                    if (r != p.rank && peer) peer[(uint64_t)m * job.out_stride + row] = y;
+                }
+            }
         }
     }
 }

@@ -41,7 +41,13 @@ struct GemvParams {
     float *partials;       // [workers][2][column tiles][32][4] fp32 scratch for split tiles
     unsigned int *counters;  // [workers], zero between launches
     unsigned long long *trace;  // optional [workers][4] globaltimer stamps (start, first data, loop end, done); may be null
+    // Row-sharded multi-GPU runs: mirror[job * kMaxPeers + r] is where rank r keeps the same output rows
+    // (peer memory), or null; every result is stored there too. Null table on one GPU.
+    float *const *mirror;
+    uint32_t world, rank;
 };
+
+constexpr int kMaxPeers = 8;
 
 }  // namespace q4
 
@@ -69,7 +75,10 @@ void q4k_stack_fill_stage(void *stage_image, const q4::GemvParams *gemv, uint32_
 int q4k_stack_supported(uint32_t x_halfs, int sm_count);
 cudaError_t q4k_stack_launch(const void *stages_dev, uint32_t n_stages, uint32_t x_halfs, unsigned int *barrier, int *error_flag,
                              const float *logits, uint32_t vocab, uint32_t index_base, float *part_val, uint32_t *part_idx,
-                             uint32_t *token, float *best, unsigned long long *trace, int sm_count, cudaStream_t stream);
+                             uint32_t *token, float *best, unsigned long long *trace, const void *peers, unsigned int epoch,
+                             int sm_count, cudaStream_t stream);
+size_t q4k_stack_peers_bytes(void);
+void q4k_stack_fill_peers(void *image, uint32_t world, uint32_t rank, void *const *flags, void *const *cand);
 
 cudaError_t q4k_gemm_prepare_x(const void *x, int x_is_f32, uint64_t elements, uint16_t *xp, cudaStream_t stream);
 uint32_t q4k_gemm_tile_m(uint32_t m);

@@ -89,6 +89,7 @@ struct q4b_runtime {
     std::vector<Shard> shards;
     uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident warps per SM
     uint32_t max_workers = 0;
+    std::vector<void *> arenas, peer_arenas;
     Pool trace, gemm_x, error_flag;
     uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
     uint64_t prof_flops = 0;
@@ -403,6 +404,8 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
     cudaDeviceSynchronize();
     for (Shard &s : rt->shards)
         if (s.ptr) cudaFree(s.ptr);
+    for (void *p : rt->peer_arenas) cudaIpcCloseMemHandle(p);
+    for (void *p : rt->arenas) cudaFree(p);
     Pool *pools[] = {&rt->gemm_x, &rt->error_flag, &rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
@@ -770,17 +773,59 @@ struct q4b_chain {
     uint32_t *token = nullptr;
     float *best = nullptr;
     unsigned long long *trace = nullptr;  // [blocks][stages][4] when tracing was on at creation
+    void *peers_dev = nullptr;            // StackPeers image, multi-rank chains
+    std::vector<void *> mirror_tables;    // per-stage device tables of peer output pointers
+    unsigned int epoch = 0, barriers_per_run = 0;
 };
+
+extern "C" int q4b_arena_create(q4b_runtime *rt, uint64_t bytes, void **device_ptr, uint8_t handle[64]) {
+    if (int st = check_rt(rt)) return st;
+    if (!device_ptr || !handle) return fail(Q4B_INVALID_ARGUMENT, "output pointer is null");
+    if (bytes == 0) return fail(Q4B_EMPTY_BUFFER, "CUDA buffers cannot be empty");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    void *p = nullptr;
+    Q4B_CUDA(cudaMalloc(&p, bytes), "arena allocation");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail_cuda(e, "arena export");
+    }
+    memcpy(handle, &h, 64);
+    rt->arenas.push_back(p);
+    *device_ptr = p;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_arena_open(q4b_runtime *rt, const uint8_t handle[64], void **peer_ptr) {
+    if (int st = check_rt(rt)) return st;
+    if (!peer_ptr || !handle) return fail(Q4B_INVALID_ARGUMENT, "output pointer is null");
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void *p = nullptr;
+    Q4B_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "arena import");
+    rt->peer_arenas.push_back(p);
+    *peer_ptr = p;
+    return Q4B_OK;
+}
 
 extern "C" uint64_t q4b_chain_max_k(void) { return q4k_stack_max_k(); }
 
 extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32_t n_stages, const float *logits, uint32_t vocab,
-                                uint32_t index_base, uint32_t *token_dev, float *best_dev, q4b_chain **out) {
+                                uint32_t index_base, uint32_t *token_dev, float *best_dev, const q4b_peers *peers, q4b_chain **out) {
     if (int st = check_rt(rt)) return st;
     if (!stages || n_stages == 0 || !out) return fail(Q4B_INVALID_ARGUMENT, "stage list or output handle is null");
     if (logits && (!token_dev || vocab == 0)) return fail(Q4B_INVALID_ARGUMENT, "token pointer is null or vocabulary empty");
+    if (peers && (peers->world < 2 || peers->world > (uint32_t)q4::kMaxPeers || peers->rank >= peers->world))
+        return fail(Q4B_INVALID_ARGUMENT, "a multi-rank chain needs 2..%d ranks and a rank below the world size", q4::kMaxPeers);
     std::lock_guard<std::mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
+    std::vector<void *> mirror_tables;
     const uint32_t warps = q4k_stack_warps();
     const size_t stage_bytes = q4k_stack_stage_bytes();
     std::vector<uint8_t> image(stage_bytes * n_stages);
@@ -829,6 +874,19 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         p.workers = (uint32_t)workers;
         p.partials = (float *)rt->partials.ptr;
         p.counters = (unsigned int *)rt->counters.ptr;
+        if (peers && S.peer_outputs) {
+            void *table = nullptr;
+            const size_t tb = (size_t)q4::kMaxJobs * q4::kMaxPeers * sizeof(float *);
+            std::vector<float *> host_table((size_t)q4::kMaxJobs * q4::kMaxPeers, nullptr);
+            for (uint32_t i = 0; i < S.n_jobs; ++i)
+                for (uint32_t rr = 0; rr < peers->world; ++rr) host_table[(size_t)i * q4::kMaxPeers + rr] = S.peer_outputs[(size_t)i * 8 + rr];
+            Q4B_CUDA(cudaMalloc(&table, tb), "mirror table allocation");
+            mirror_tables.push_back(table);
+            Q4B_CUDA(cudaMemcpy(table, host_table.data(), tb, cudaMemcpyHostToDevice), "mirror table upload");
+            p.mirror = (float *const *)table;
+            p.world = peers->world;
+            p.rank = peers->rank;
+        }
         q4k_stack_fill_stage(image.data() + stage_bytes * si, &p, S.x_kind, S.eps, S.src0, S.src1, (uint16_t *)S.x_bf16_out);
     }
     if (!q4k_stack_supported(x_halfs, rt->sm_count))
@@ -859,6 +917,18 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         if (cudaMalloc((void **)&c->trace, tb) == cudaSuccess) cudaMemset(c->trace, 0, tb);
         else c->trace = nullptr;
     }
+    c->mirror_tables = mirror_tables;
+    c->barriers_per_run = n_stages + (logits ? 1u : 0u) + ((logits && peers) ? 1u : 0u);
+    if (peers) {
+        std::vector<uint8_t> pimage(q4k_stack_peers_bytes());
+        q4k_stack_fill_peers(pimage.data(), peers->world, peers->rank, peers->flags, peers->cand);
+        if (cudaMalloc(&c->peers_dev, pimage.size()) != cudaSuccess ||
+            cudaMemcpy(c->peers_dev, pimage.data(), pimage.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+            cudaGetLastError();
+            q4b_chain_destroy(c);
+            return fail(Q4B_CUDA_ERROR, "peer table allocation failed");
+        }
+    }
     c->barrier = (unsigned int *)aux;
     c->part_val = (float *)((uint8_t *)aux + 256);
     c->part_idx = (uint32_t *)((uint8_t *)aux + 256 + (size_t)rt->sm_count * 4);
@@ -872,8 +942,9 @@ extern "C" int q4b_chain_run_device(q4b_chain *chain, void *stream) {
     DeviceGuard guard(rt->device);
     Q4B_CUDA(q4k_stack_launch(chain->stages_dev, chain->n_stages, chain->x_halfs, chain->barrier, (int *)rt->error_flag.ptr,
                               chain->logits, chain->vocab, chain->index_base, chain->part_val, chain->part_idx, chain->token,
-                              chain->best, chain->trace, rt->sm_count, (cudaStream_t)stream),
+                              chain->best, chain->trace, chain->peers_dev, chain->epoch, rt->sm_count, (cudaStream_t)stream),
              "decode chain launch");
+    if (chain->peers_dev) chain->epoch += chain->barriers_per_run;
     rt->launches++;
     return Q4B_OK;
 }
@@ -899,6 +970,8 @@ extern "C" void q4b_chain_destroy(q4b_chain *chain) {
         if (chain->stages_dev) cudaFree(chain->stages_dev);
         if (chain->barrier) cudaFree(chain->barrier);
         if (chain->trace) cudaFree(chain->trace);
+        if (chain->peers_dev) cudaFree(chain->peers_dev);
+        for (void *t : chain->mirror_tables) cudaFree(t);
     }
     delete chain;
 }

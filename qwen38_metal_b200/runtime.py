@@ -249,20 +249,44 @@ class CudaRuntime:
         _check(self._lib.q4b_rms_unit_bf16_device(self._h, in_ptr, rows, n, eps, out_ptr, stream))
 
     # -- persistent decode chain ----------------------------------------------------------------------
+    def arena_create(self, nbytes: int) -> tuple[int, bytes]:
+        """Zeroed device memory that peer processes can map: (device pointer, 64-byte IPC handle)."""
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        _check(self._lib.q4b_arena_create(self._h, nbytes, C.byref(ptr), handle))
+        return ptr.value, handle.raw
+
+    def arena_open(self, handle: bytes) -> int:
+        ptr = C.c_void_p()
+        _check(self._lib.q4b_arena_open(self._h, handle, C.byref(ptr)))
+        return ptr.value
+
     def chain_create(self, stages, logits_ptr: int = 0, vocab: int = 0, index_base: int = 0, token_ptr: int = 0,
-                     best_ptr: int = 0) -> "DecodeChain":
-        """stages: list of dicts {x_kind, k, src0, src1, x_bf16_out, jobs, outputs, eps} with raw device pointers."""
+                     best_ptr: int = 0, peers=None) -> "DecodeChain":
+        """stages: list of dicts {x_kind, k, src0, src1, x_bf16_out, jobs, outputs, eps[, peer_outputs]} with raw
+        device pointers; peers: None or {world, rank, flags: [ptr]*world, cand: [ptr]*world}."""
         arr = (capi.Stage * len(stages))()
         keep = []
         for i, s in enumerate(stages):
             jobs = _jobs(s["jobs"])
             outs = (C.c_void_p * len(s["jobs"]))(*s["outputs"])
             keep += [jobs, outs]
+            mirrors = None
+            if s.get("peer_outputs") is not None:
+                flat = [p or None for row in s["peer_outputs"] for p in (list(row) + [0] * 8)[:8]]
+                mirrors = (C.c_void_p * len(flat))(*flat)
+                keep.append(mirrors)
             arr[i] = capi.Stage(s["x_kind"], s.get("eps", 1e-6), s["k"], s["src0"], s.get("src1") or None,
-                                s.get("x_bf16_out") or None, jobs, len(s["jobs"]), outs)
+                                s.get("x_bf16_out") or None, jobs, len(s["jobs"]), outs, mirrors)
+        cpeers = None
+        if peers is not None:
+            cpeers = capi.Peers(peers["world"], peers["rank"])
+            for r in range(peers["world"]):
+                cpeers.flags[r] = peers["flags"][r]
+                cpeers.cand[r] = peers["cand"][r]
         handle = C.c_void_p()
         _check(self._lib.q4b_chain_create(self._h, arr, len(stages), logits_ptr or None, vocab, index_base,
-                                          token_ptr or None, best_ptr or None, C.byref(handle)))
+                                          token_ptr or None, best_ptr or None,
+                                          C.byref(cpeers) if cpeers is not None else None, C.byref(handle)))
         return DecodeChain(self, handle)
 
     # -- synthetic tensors ---------------------------------------------------------------------

@@ -164,6 +164,64 @@ class SyntheticStack:
         return self.rt.chain_create(stages, self.logits.data_ptr(), self.vocab, 0, self.token.data_ptr(),
                                     self.best.data_ptr())
 
+    def build_chain_sharded(self, dist):
+        """The whole token as one persistent kernel per rank of a row-sharded stack. Outputs that feed a later stage
+        (gate, up, down) live in an exchange arena that every rank maps; each rank stores its rows into every
+        arena with peer stores and the chain's barriers span all ranks -- no collective library on the data path.
+        `dist` (torch.distributed) only carries the 64-byte IPC handles at set-up."""
+        world, rank, rt = self.world, self.rank, self.rt
+
+        def align(n):
+            return (n + 255) & ~255
+
+        off_gate, off_up = 0, align(self.inter * 4)
+        off_d = off_up + align(self.inter * 4)
+        off_flags = off_d + align(self.hidden * 4)
+        off_cand = off_flags + 256
+        size = off_cand + 256
+        base, handle = rt.arena_create(size)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        arena = [base if r == rank else rt.arena_open(handles[r]) for r in range(world)]
+        self.arena_base, self.arena_offsets = base, {"gate": off_gate, "up": off_up, "d": off_d}
+
+        def stage_jobs(projs, outs_local, shared):
+            """shared[i]: arena offset of job i's output buffer, or None when the output stays local."""
+            jobs, outs, mirrors = [], [], []
+            for p, o, sh in zip(projs, outs_local, shared):
+                if p.job is None:
+                    continue
+                jobs.append(p.job)
+                if sh is None:
+                    outs.append(o.data_ptr() + 4 * p.row0)
+                    mirrors.append([0] * 8)
+                else:
+                    outs.append(base + sh + 4 * p.row0)
+                    mirrors.append([0 if r == rank else arena[r] + sh + 4 * p.row0 for r in range(world)] + [0] * (8 - world))
+            return jobs, outs, mirrors
+
+        stages = []
+        for layer in range(self.layers):
+            shared = [None] * len(self.layer_rows)
+            shared[self.gate_i], shared[self.up_i] = off_gate, off_up
+            jobs, outs, mirrors = stage_jobs(self.proj[layer], self.outs, shared)
+            first = layer == 0
+            stages.append({"x_kind": capi.X_BF16 if first else capi.X_RMS, "k": self.hidden,
+                           "src0": self.x.data_ptr() if first else base + off_d, "eps": 1e-6,
+                           "x_bf16_out": 0 if first else self.x.data_ptr(), "jobs": jobs, "outputs": outs,
+                           "peer_outputs": mirrors})
+            jobs, outs, mirrors = stage_jobs([self.down[layer]], [self.d], [off_d])
+            stages.append({"x_kind": capi.X_SWIGLU, "k": self.inter, "src0": base + off_gate, "src1": base + off_up,
+                           "x_bf16_out": self.h.data_ptr(), "jobs": jobs, "outputs": outs, "peer_outputs": mirrors})
+        p = self.lm_head
+        self.logits = torch.zeros(max(p.rows, 1), dtype=torch.float32, device=self.device)
+        stages.append({"x_kind": capi.X_RMS, "k": self.hidden, "src0": base + off_d, "eps": 1e-6,
+                       "x_bf16_out": self.x.data_ptr(), "jobs": [p.job], "outputs": [self.logits.data_ptr()],
+                       "peer_outputs": [[0] * 8]})
+        peers = {"world": world, "rank": rank, "flags": [a + off_flags for a in arena], "cand": [a + off_cand for a in arena]}
+        dist.barrier()  # every arena is mapped everywhere before the first launch
+        return rt.chain_create(stages, self.logits.data_ptr(), p.rows, p.row0, self.token.data_ptr(), self.best.data_ptr(), peers)
+
     def decode_token(self, stream: int = 0, gather=None) -> None:
         """Enqueue one token on `stream` (a raw cudaStream_t). `gather(tensor, proj)` makes a row-sharded
         output whole on every rank; it is None on one GPU."""
