@@ -51,7 +51,29 @@ typedef enum q4b_status {
     Q4B_COMMAND_FAILED = 11,        /* CommandFailed: a kernel or copy reported an error */
     Q4B_CUDA_ERROR = 12,            /* Library/Function/Pipeline analogue: CUDA call failed */
     Q4B_INVALID_ARGUMENT = 13,      /* null pointer, unknown dtype, bad handle */
-    Q4B_UNSUPPORTED = 14            /* shape outside what this build handles */
+    Q4B_UNSUPPORTED = 14,           /* shape outside what this build handles */
+    /* weight store and projection API (q4b_weights.h): ModelFormatError, src/model.rs:566-608, and the
+     * projection-related variants of NativeError, src/native.rs:5518-5560 */
+    Q4B_IO_ERROR = 15,                  /* ModelFormatError::Read */
+    Q4B_JSON_ERROR = 16,                /* ::Json */
+    Q4B_MISSING_QUANTIZATION = 17,      /* ::MissingQuantization */
+    Q4B_UNSUPPORTED_QUANTIZATION = 18,  /* ::UnsupportedQuantization */
+    Q4B_UNSAFE_SHARD_PATH = 19,         /* ::UnsafeShardPath */
+    Q4B_INVALID_HEADER_LENGTH = 20,     /* ::InvalidHeaderLength */
+    Q4B_MISSING_INDEXED_TENSOR = 21,    /* ::MissingIndexedTensor */
+    Q4B_INVALID_TENSOR_OFFSETS = 22,    /* ::InvalidTensorOffsets */
+    Q4B_INVALID_TENSOR_METADATA = 23,   /* ::InvalidTensorMetadata */
+    Q4B_MISSING_TENSOR = 24,            /* ::MissingRuntimeTensor, NativeError::MissingTensor */
+    Q4B_INVALID_RUNTIME_TENSOR = 25,    /* ::InvalidRuntimeTensor */
+    Q4B_UNSUPPORTED_DTYPE = 26,         /* ::UnsupportedRuntimeDtype */
+    Q4B_INCOMPLETE_AFFINE_GROUP = 27,   /* ::IncompleteAffineGroup */
+    Q4B_NOT_QUANTIZED_WEIGHT = 28,      /* NativeError::NotQuantizedWeight */
+    Q4B_INVALID_QUANTIZED_WEIGHT = 29,  /* NativeError::InvalidQuantizedWeight */
+    Q4B_INVALID_AFFINE_TENSOR = 30,     /* NativeError::InvalidAffineTensor */
+    Q4B_TENSOR_BYTE_LENGTH = 31,        /* NativeError::TensorByteLength */
+    Q4B_INPUT_DIMENSION = 32,           /* NativeError::InputDimension */
+    Q4B_INVALID_CONFIG = 33,            /* NativeError::InvalidConfig */
+    Q4B_TOKEN_OUT_OF_RANGE = 34         /* NativeError::TokenOutOfRange */
 } q4b_status;
 
 typedef enum q4b_dtype {
@@ -99,6 +121,9 @@ int q4b_shard_alloc(q4b_runtime *rt, uint64_t bytes, uint32_t *shard_id);
 /* Copy into an existing shard (partial uploads, row slices). */
 int q4b_shard_write(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, const void *host_bytes, uint64_t bytes);
 int q4b_shard_read(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, void *host_bytes, uint64_t bytes);
+/* Releases a shard's device memory (MappedWeightBuffers dropped, src/metal_runtime.rs:608-612). The id is not
+ * reused; using it afterwards is Q4B_MISSING_SHARD. Waits for the device to go idle first. */
+int q4b_shard_free(q4b_runtime *rt, uint32_t shard_id);
 /* MappedWeightBuffers::shard_count, src/metal_runtime.rs:624-626 */
 int q4b_shard_count(q4b_runtime *rt, uint32_t *count);
 int q4b_shard_info(q4b_runtime *rt, uint32_t shard_id, void **device_ptr, uint64_t *bytes);

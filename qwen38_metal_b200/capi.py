@@ -1,4 +1,4 @@
-"""ctypes prototypes of include/q4b200.h. The library is required: there is no fallback."""
+"""ctypes prototypes of include/q4b200.h and include/q4b_weights.h. The library is required: there is no fallback."""
 from __future__ import annotations
 
 import ctypes as C
@@ -13,7 +13,12 @@ STATUS_NAMES = {
     0: "Ok", 1: "NoDevice", 2: "EmptyBuffer", 3: "ActivationPoolPoisoned", 4: "EmptyDimension",
     5: "InputNotGrouped", 6: "WrongLength", 7: "MissingMappedShard", 8: "InvalidBufferOffset",
     9: "MappedTensorOutOfRange", 10: "DimensionOverflow", 11: "CommandFailed", 12: "CudaError",
-    13: "InvalidArgument", 14: "Unsupported",
+    13: "InvalidArgument", 14: "Unsupported", 15: "Read", 16: "Json", 17: "MissingQuantization",
+    18: "UnsupportedQuantization", 19: "UnsafeShardPath", 20: "InvalidHeaderLength", 21: "MissingIndexedTensor",
+    22: "InvalidTensorOffsets", 23: "InvalidTensorMetadata", 24: "MissingTensor", 25: "InvalidRuntimeTensor",
+    26: "UnsupportedRuntimeDtype", 27: "IncompleteAffineGroup", 28: "NotQuantizedWeight",
+    29: "InvalidQuantizedWeight", 30: "InvalidAffineTensor", 31: "TensorByteLength", 32: "InputDimension",
+    33: "InvalidConfig", 34: "TokenOutOfRange",
 }
 
 
@@ -25,6 +30,24 @@ class Job(C.Structure):
         ("aligned", C.c_int32),
         ("weight_offset", C.c_uint64), ("scale_offset", C.c_uint64), ("bias_offset", C.c_uint64),
         ("output_rows", C.c_uint64),
+    ]
+
+
+class TensorInfo(C.Structure):
+    """q4b_tensor_info: MlxTensor of the reference (src/model.rs:58-65)."""
+
+    _fields_ = [
+        ("dtype", C.c_char * 16), ("rank", C.c_uint32), ("shard_index", C.c_uint32), ("shape", C.c_uint64 * 8),
+        ("byte_offset", C.c_uint64), ("byte_len", C.c_uint64),
+    ]
+
+
+class Q4Matrix(C.Structure):
+    """q4b_q4_matrix: Q4AffineMatrix of the reference (src/native.rs:5383-5393)."""
+
+    _fields_ = [
+        ("weight", TensorInfo), ("scales", TensorInfo), ("biases", TensorInfo),
+        ("input_elements", C.c_uint64), ("output_rows", C.c_uint64), ("row_begin", C.c_uint64), ("total_rows", C.c_uint64),
     ]
 
 
@@ -102,6 +125,32 @@ def load() -> C.CDLL:
         "q4b_chain_run_device": [vp, vp],
         "q4b_chain_trace_read": [vp, vp, u64, P(u32), P(u32)],
         "q4b_matvec_noalloc": [i32, vp, u64, vp, vp, vp, u64, vp, vp],
+        "q4b_shard_free": [vp, u32],
+        "q4b_store_open": [C.c_char_p, P(vp)],
+        "q4b_store_tensor_count": [vp, P(u64)],
+        "q4b_store_shard_count": [vp, P(u64)],
+        "q4b_store_mapped_bytes": [vp, P(u64)],
+        "q4b_store_indexed_tensor_bytes": [vp, P(u64)],
+        "q4b_store_quantized_groups": [vp, P(u64)],
+        "q4b_store_tensor": [vp, C.c_char_p, P(TensorInfo)],
+        "q4b_store_tensor_name": [vp, u64, P(C.c_char_p)],
+        "q4b_store_tensor_data": [vp, C.c_char_p, P(vp), P(u64)],
+        "q4b_store_shard_data": [vp, u64, P(vp), P(u64)],
+        "q4b_store_tensor_values_f32": [vp, C.c_char_p, vp, u64, P(u64)],
+        "q4b_store_q4_matrix": [vp, C.c_char_p, P(Q4Matrix)],
+        "q4b_q4_matrix_from_tensors": [C.c_char_p, P(TensorInfo), P(TensorInfo), P(TensorInfo), P(Q4Matrix)],
+        "q4b_weights_open": [vp, C.c_char_p, P(vp)],
+        "q4b_weights_open_sharded": [vp, C.c_char_p, u32, u32, P(vp)],
+        "q4b_weights_store": [vp, P(vp)],
+        "q4b_weights_shard_count": [vp, P(u64)],
+        "q4b_weights_device_bytes": [vp, P(u64)],
+        "q4b_weights_q4_matrix": [vp, C.c_char_p, P(Q4Matrix)],
+        "q4b_weights_jobs": [vp, P(Q4Matrix), u32, u64, P(Job)],
+        "q4b_weights_matvec_batch": [vp, P(Q4Matrix), u32, vp, u64, P(vp)],
+        "q4b_weights_matmul_batch": [vp, P(Q4Matrix), u32, vp, u64, u64, P(vp)],
+        "q4b_weights_argmax_batch": [vp, P(Q4Matrix), vp, u64, u64, vp],
+        "q4b_weights_mlp_batch": [vp, P(Q4Matrix), P(Q4Matrix), P(Q4Matrix), vp, u64, u64, vp],
+        "q4b_weights_dequantized_row": [vp, P(Q4Matrix), u64, vp],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -111,6 +160,9 @@ def load() -> C.CDLL:
     lib.q4b_runtime_destroy.restype = None
     lib.q4b_last_error.argtypes = []
     lib.q4b_last_error.restype = C.c_char_p
+    for name in ("q4b_store_close", "q4b_weights_close"):
+        getattr(lib, name).argtypes = [vp]
+        getattr(lib, name).restype = None
     lib.q4b_chain_destroy.argtypes = [vp]
     lib.q4b_chain_destroy.restype = None
     lib.q4b_chain_max_k.argtypes = []
@@ -131,4 +183,16 @@ EXPORTS = [
     "q4b_argmax_batch_device", "q4b_swiglu_device", "q4b_rms_unit_bf16_device", "q4b_synth_q4_device",
     "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status", "q4b_matvec_noalloc", "q4b_noalloc_last_error", "q4b_chain_create", "q4b_chain_run_device",
     "q4b_chain_destroy", "q4b_chain_max_k", "q4b_chain_trace_read", "q4b_arena_create", "q4b_arena_open",
+    "q4b_shard_free",
+]
+
+# include/q4b_weights.h
+WEIGHTS_EXPORTS = [
+    "q4b_store_open", "q4b_store_close", "q4b_store_tensor_count", "q4b_store_shard_count", "q4b_store_mapped_bytes",
+    "q4b_store_indexed_tensor_bytes", "q4b_store_quantized_groups", "q4b_store_tensor", "q4b_store_tensor_name",
+    "q4b_store_tensor_data", "q4b_store_shard_data", "q4b_store_tensor_values_f32", "q4b_store_q4_matrix",
+    "q4b_q4_matrix_from_tensors", "q4b_weights_open", "q4b_weights_open_sharded", "q4b_weights_close",
+    "q4b_weights_store", "q4b_weights_shard_count", "q4b_weights_device_bytes", "q4b_weights_q4_matrix",
+    "q4b_weights_jobs", "q4b_weights_matvec_batch", "q4b_weights_matmul_batch", "q4b_weights_argmax_batch",
+    "q4b_weights_mlp_batch", "q4b_weights_dequantized_row",
 ]

@@ -216,9 +216,14 @@ __device__ __forceinline__ void finish_tile(const GemvParams &p, const float *ro
         store_tile<NT>(p, row_inv, tile, acc, g, t, job_index);
         return;
     }
+    const uint64_t u0 = (uint64_t)tile * split.cpt;
     uint32_t first, last;
     q4_split_contributors(split, tile, &first, &last);
-    float4 *slot = reinterpret_cast<float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, worker, tile) * NT) * 32u;
+    const uint64_t first_begin = q4_split_begin(split, first);
+    // only the first contributor can have started in an earlier tile (slot 1); everyone else starts inside this one
+    const uint32_t first_slot = 2u * first + (first_begin < u0 ? 1u : 0u);
+    const uint32_t my_slot = worker == first ? first_slot : 2u * worker;
+    float4 *slot = reinterpret_cast<float4 *>(p.partials) + ((uint64_t)my_slot * NT) * 32u;
 #pragma unroll
     for (int j = 0; j < NT; ++j) slot[j * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
     __threadfence();
@@ -230,15 +235,28 @@ __device__ __forceinline__ void finish_tile(const GemvParams &p, const float *ro
         __threadfence();
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-        for (uint32_t w = first; w <= last; ++w) {
-            const float4 *src = reinterpret_cast<const float4 *>(p.partials) + ((uint64_t)q4_split_slot(split, w, tile) * NT) * 32u;
+        // partial slots are read four at a time (independent loads in flight) and added in worker order
+        for (uint32_t w0 = first; w0 <= last; w0 += 4) {
+            float4 pv[4][NT];
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                float4 pv = __ldcg(src + j * 32 + lane);
-                acc[j][0] += pv.x;
-                acc[j][1] += pv.y;
-                acc[j][2] += pv.z;
-                acc[j][3] += pv.w;
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t w = w0 + i <= last ? w0 + i : last;
+                const uint32_t ws = w == first ? first_slot : 2u * w;
+                const float4 *src = reinterpret_cast<const float4 *>(p.partials) + ((uint64_t)ws * NT) * 32u;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) pv[i][j] = __ldcg(src + j * 32 + lane);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (w0 + i <= last) {
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        acc[j][0] += pv[i][j].x;
+                        acc[j][1] += pv[i][j].y;
+                        acc[j][2] += pv[i][j].z;
+                        acc[j][3] += pv[i][j].w;
+                    }
+                }
             }
         }
         store_tile<NT>(p, row_inv, tile, acc, g, t, job_index);

@@ -31,6 +31,18 @@ int fail(int status, const char *fmt, ...) {
     return status;
 }
 
+}  // namespace
+
+// lets the other translation units of the library (weight store) leave their message where q4b_last_error reads it
+namespace q4 {
+int set_error(int status, const char *message) {
+    g_last_error = message;
+    return status;
+}
+}  // namespace q4
+
+namespace {
+
 int fail_cuda(cudaError_t e, const char *what) {
     return fail(Q4B_CUDA_ERROR, "CUDA call failed in %s: %s", what, cudaGetErrorString(e));
 }
@@ -87,6 +99,8 @@ struct q4b_runtime {
     cudaStream_t stream = nullptr;
     std::mutex mu;
     std::vector<Shard> shards;
+    void *stage[2] = {nullptr, nullptr};  // pinned staging for uploads from pageable (mmap'd) memory
+    cudaEvent_t stage_done[2] = {nullptr, nullptr};
     uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident warps per SM
     uint32_t max_workers = 0;
     std::vector<void *> arenas, peer_arenas;
@@ -255,8 +269,8 @@ int launch_streaming(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m
         // one warp per block, every SM filled to the variant's occupancy; never more warps than units, so
         // every worker owns at least one unit (the split-tile arrival count relies on it)
         uint64_t workers = (uint64_t)rt->sm_count * rt->gemv_ctas[nt][fast];
-        // at most 8 warps share a tile: the warp that combines a split tile reads its partials one by one
-        const uint64_t min_chunks = (p.cpt + 7u) / 8u;
+        // at most 32 warps share a tile: the warp that combines a split tile reads their partials four at a time
+        const uint64_t min_chunks = (p.cpt + 31u) / 32u;
         if (workers > p.units / min_chunks) workers = p.units / min_chunks;
         if (workers == 0) workers = 1;
         p.workers = (uint32_t)workers;
@@ -411,6 +425,10 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
     for (cudaEvent_t ev : rt->prof_events) cudaEventDestroy(ev);
+    for (int i = 0; i < 2; ++i) {
+        if (rt->stage[i]) cudaFreeHost(rt->stage[i]);
+        if (rt->stage_done[i]) cudaEventDestroy(rt->stage_done[i]);
+    }
     if (rt->stream) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -434,6 +452,26 @@ extern "C" const char *q4b_status_name(int status) {
         case Q4B_CUDA_ERROR: return "CudaError";
         case Q4B_INVALID_ARGUMENT: return "InvalidArgument";
         case Q4B_UNSUPPORTED: return "Unsupported";
+        case Q4B_IO_ERROR: return "Read";
+        case Q4B_JSON_ERROR: return "Json";
+        case Q4B_MISSING_QUANTIZATION: return "MissingQuantization";
+        case Q4B_UNSUPPORTED_QUANTIZATION: return "UnsupportedQuantization";
+        case Q4B_UNSAFE_SHARD_PATH: return "UnsafeShardPath";
+        case Q4B_INVALID_HEADER_LENGTH: return "InvalidHeaderLength";
+        case Q4B_MISSING_INDEXED_TENSOR: return "MissingIndexedTensor";
+        case Q4B_INVALID_TENSOR_OFFSETS: return "InvalidTensorOffsets";
+        case Q4B_INVALID_TENSOR_METADATA: return "InvalidTensorMetadata";
+        case Q4B_MISSING_TENSOR: return "MissingTensor";
+        case Q4B_INVALID_RUNTIME_TENSOR: return "InvalidRuntimeTensor";
+        case Q4B_UNSUPPORTED_DTYPE: return "UnsupportedRuntimeDtype";
+        case Q4B_INCOMPLETE_AFFINE_GROUP: return "IncompleteAffineGroup";
+        case Q4B_NOT_QUANTIZED_WEIGHT: return "NotQuantizedWeight";
+        case Q4B_INVALID_QUANTIZED_WEIGHT: return "InvalidQuantizedWeight";
+        case Q4B_INVALID_AFFINE_TENSOR: return "InvalidAffineTensor";
+        case Q4B_TENSOR_BYTE_LENGTH: return "TensorByteLength";
+        case Q4B_INPUT_DIMENSION: return "InputDimension";
+        case Q4B_INVALID_CONFIG: return "InvalidConfig";
+        case Q4B_TOKEN_OUT_OF_RANGE: return "TokenOutOfRange";
         default: return "Unknown";
     }
 }
@@ -465,6 +503,45 @@ static int shard_new(q4b_runtime *rt, uint64_t bytes, uint32_t *shard_id) {
     return Q4B_OK;
 }
 
+// Host-to-device copy of a large pageable range (a mapped safetensors file): the range is moved through two
+// pinned staging buffers so that the host-side copy (and the page faults behind it) of one piece overlaps the DMA
+// of the previous one. Small copies go straight through cudaMemcpy.
+constexpr size_t kStageBytes = 16u << 20;
+
+static cudaError_t staged_h2d(q4b_runtime *rt, uint8_t *dst, const uint8_t *src, uint64_t bytes) {
+    if (bytes <= kStageBytes / 2) return cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice);
+    for (int i = 0; i < 2; ++i) {
+        if (!rt->stage[i]) {
+            cudaError_t e = cudaHostAlloc(&rt->stage[i], kStageBytes, cudaHostAllocDefault);
+            if (e != cudaSuccess) {
+                rt->stage[i] = nullptr;
+                cudaGetLastError();
+                return cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice);  // no pinned memory to be had: plain copy
+            }
+            e = cudaEventCreateWithFlags(&rt->stage_done[i], cudaEventDisableTiming);
+            if (e != cudaSuccess) return e;
+        }
+    }
+    uint64_t done = 0;
+    int slot = 0;
+    bool used[2] = {false, false};
+    while (done < bytes) {
+        const uint64_t n = bytes - done < kStageBytes ? bytes - done : kStageBytes;
+        if (used[slot]) {
+            cudaError_t e = cudaEventSynchronize(rt->stage_done[slot]);
+            if (e != cudaSuccess) return e;
+        }
+        memcpy(rt->stage[slot], src + done, n);
+        cudaError_t e = cudaMemcpyAsync(dst + done, rt->stage[slot], n, cudaMemcpyHostToDevice, rt->stream);
+        if (e == cudaSuccess) e = cudaEventRecord(rt->stage_done[slot], rt->stream);
+        if (e != cudaSuccess) return e;
+        used[slot] = true;
+        done += n;
+        slot ^= 1;
+    }
+    return cudaStreamSynchronize(rt->stream);
+}
+
 extern "C" int q4b_shard_upload(q4b_runtime *rt, const void *host_bytes, uint64_t bytes, uint32_t *shard_id) {
     if (int st = check_rt(rt)) return st;
     if (!host_bytes && bytes) return fail(Q4B_INVALID_ARGUMENT, "host pointer is null");
@@ -472,13 +549,28 @@ extern "C" int q4b_shard_upload(q4b_runtime *rt, const void *host_bytes, uint64_
     DeviceGuard guard(rt->device);
     uint32_t id = 0;
     if (int st = shard_new(rt, bytes, &id)) return st;
-    cudaError_t e = cudaMemcpy(rt->shards[id].ptr, host_bytes, bytes, cudaMemcpyHostToDevice);
+    cudaError_t e = staged_h2d(rt, rt->shards[id].ptr, (const uint8_t *)host_bytes, bytes);
     if (e != cudaSuccess) {
         cudaFree(rt->shards[id].ptr);
         rt->shards.pop_back();
         return fail_cuda(e, "shard upload");
     }
     *shard_id = id;
+    return Q4B_OK;
+}
+
+// MappedWeightBuffers going out of scope in the reference: the device copy is released; the id stays taken and
+// later use of it reports Q4B_MISSING_SHARD.
+extern "C" int q4b_shard_free(q4b_runtime *rt, uint32_t shard_id) {
+    if (int st = check_rt(rt)) return st;
+    std::lock_guard<std::mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    if (shard_id >= rt->shards.size() || !rt->shards[shard_id].ptr)
+        return fail(Q4B_MISSING_SHARD, "mapped safetensors shard %u is absent", shard_id);
+    Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
+    cudaFree(rt->shards[shard_id].ptr);
+    rt->shards[shard_id].ptr = nullptr;
+    rt->shards[shard_id].bytes = 0;
     return Q4B_OK;
 }
 
@@ -506,7 +598,7 @@ extern "C" int q4b_shard_write(q4b_runtime *rt, uint32_t shard_id, uint64_t offs
     if (int st = shard_range(rt, shard_id, offset, bytes)) return st;
     if (bytes == 0) return Q4B_OK;
     if (!host_bytes) return fail(Q4B_INVALID_ARGUMENT, "host pointer is null");
-    Q4B_CUDA(cudaMemcpy(rt->shards[shard_id].ptr + offset, host_bytes, bytes, cudaMemcpyHostToDevice), "shard write");
+    Q4B_CUDA(staged_h2d(rt, rt->shards[shard_id].ptr + offset, (const uint8_t *)host_bytes, bytes), "shard write");
     return Q4B_OK;
 }
 
@@ -868,7 +960,7 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         p.cpt = (groups + 1u) / 2u;
         p.units = (uint64_t)tiles * p.cpt;
         uint64_t workers = (uint64_t)rt->sm_count * warps;
-        const uint64_t min_chunks = (p.cpt + 7u) / 8u;
+        const uint64_t min_chunks = (p.cpt + 31u) / 32u;
         if (workers > p.units / min_chunks) workers = p.units / min_chunks;
         if (workers == 0) workers = 1;
         p.workers = (uint32_t)workers;

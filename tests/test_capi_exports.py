@@ -16,15 +16,15 @@ def lib():
     return capi.load()
 
 
-def declared_functions():
-    text = open(os.path.join(ROOT, "include", "q4b200.h")).read()
+def declared_functions(header="q4b200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(q4b_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported(lib):
-    names = declared_functions()
-    assert len(names) >= 25
+    names = declared_functions() + declared_functions("q4b_weights.h")
+    assert len(names) >= 60
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in q4b200.h but not exported"
 
@@ -33,12 +33,14 @@ def test_python_prototypes_cover_the_header():
     from qwen38_metal_b200 import capi
 
     assert sorted(capi.EXPORTS) == declared_functions()
+    assert sorted(capi.WEIGHTS_EXPORTS) == declared_functions("q4b_weights.h")
 
 
 def test_job_struct_layout_matches_header():
     from qwen38_metal_b200 import capi
 
     assert C.sizeof(capi.Job) == 48
+    assert C.sizeof(capi.TensorInfo) == 104 and C.sizeof(capi.Q4Matrix) == 3 * 104 + 32
     assert capi.Job.weight_offset.offset == 16 and capi.Job.output_rows.offset == 40
 
 

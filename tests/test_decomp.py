@@ -57,6 +57,9 @@ def test_split_is_a_partition_with_consistent_bookkeeping(shim, tiles, cpt, work
             assert len(set(slots)) == len(slots)
             for w, s in zip(who, slots):
                 assert s // 2 == w
+            # the kernel's shortcut: only the first contributor can be in its second slot, and only when its range
+            # starts before the tile does
+            assert slots == [2 * w + (1 if (w == who[0] and begins[w] < t * cpt) else 0) for w in who]
     # a warp touches at most two split tiles (head and tail), and they use different slots
     for w in range(workers):
         mine = sorted({u // cpt for u in range(begins[w], begins[w + 1])})
