@@ -43,6 +43,103 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured (MEASURED_PEAKS.json)"
+    return 1590.0, 1400.0, "fallback"
+
+
+def secondary_metrics(torch, rt, stack, stream, capi):
+    """The other two headline figures, on the stack's own weights (one GPU): the prefill GEMM (config 2: M=2048 on
+    gate, up and down) in TFLOP/s, and the small-M sweep (config 3: M = 1..64 on gate/up and down) in GB/s per
+    kernel variant with the M at which the tensor-core variant overtakes the streaming one. Every iteration uses
+    another layer's weights, so the weight stream never comes from L2."""
+    dev, raw = stack.device, stream.cuda_stream
+    hidden, inter, layers = stack.hidden, stack.inter, stack.layers
+    m_max = 2048
+    xa = torch.empty(m_max * hidden, dtype=torch.bfloat16, device=dev)
+    xh = torch.empty(m_max * inter, dtype=torch.bfloat16, device=dev)
+    rt.synth_bf16(SEED, 900_001, xa.numel(), xa.data_ptr(), raw)
+    rt.synth_bf16(SEED, 900_002, xh.numel(), xh.data_ptr(), raw)
+    og = torch.empty(m_max * inter, dtype=torch.float32, device=dev)
+    ou = torch.empty(m_max * inter, dtype=torch.float32, device=dev)
+    od = torch.empty(m_max * hidden, dtype=torch.float32, device=dev)
+
+    # In the stack `gate` (position 7 of the grouped set) and the down projection of odd layers start 2 bytes off a
+    # 16-byte boundary; `up` and the down projection of even layers are aligned. "pair" = two 17408 x 5120
+    # projections sharing one activation in one call, the shape of gate+up.
+    def pair_of(index):
+        def fn(layer, m, flags):
+            a, b = stack.proj[layer][index], stack.proj[(layer + 1) % layers][index]
+            rt.matmul_batch_device(xa.data_ptr(), capi.Q4B_BF16, m, hidden, [a.job, b.job], [og.data_ptr(), ou.data_ptr()], flags, raw)
+        return fn
+
+    def down_of(parity):
+        def fn(layer, m, flags):
+            layer = (layer * 2 + parity) % layers if layers > 1 else 0
+            rt.matmul_batch_device(xh.data_ptr(), capi.Q4B_BF16, m, inter, [stack.down[layer].job], [od.data_ptr()], flags, raw)
+        return fn
+
+    gate_up, down = pair_of(stack.up_i), down_of(0)            # aligned
+    gate_up_mis, down_mis = pair_of(stack.gate_i), down_of(1)  # 2 bytes off
+
+    def timed(fn, m, flags, iters, warm=2):
+        """ms per call: `iters` calls on different layers captured in one CUDA graph (no host launch cost between
+        them), replayed once untimed and once timed."""
+        for i in range(warm):
+            fn(i % layers, m, flags)  # sizes the scratch pools before capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(iters):
+                fn((warm + i) % layers, m, flags)
+        graph.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        rt.device_status()
+        return e0.elapsed_time(e1) / iters
+
+    out = {}
+    with torch.cuda.stream(stream):
+        burst, sustained, source = measured_tensor_peaks()
+        f_gu, f_d = 2.0 * m_max * 2 * inter * hidden, 2.0 * m_max * hidden * inter
+        ms_gu, ms_d = timed(gate_up, m_max, 0, 12, 3), timed(down, m_max, 0, 12, 3)
+        tf_gu, tf_d = f_gu / ms_gu / 1e9, f_d / ms_d / 1e9
+        tf_all = (f_gu + f_d) / (ms_gu + ms_d) / 1e9
+        ms_gu_mis, ms_d_mis = timed(gate_up_mis, m_max, 0, 12, 3), timed(down_mis, m_max, 0, 12, 3)
+        out["prefill_gemm"] = {
+            "workload": "config2-prefill: M=2048, gate+up (K=5120, N=17408 each, one call) and down (K=17408, N=5120); "
+                        "16-byte aligned tensors (the same shapes 2 bytes off a boundary under 'misaligned')",
+            "misaligned": {"gate_up": f_gu / ms_gu_mis / 1e9, "down": f_d / ms_d_mis / 1e9,
+                           "gate_up_down": (f_gu + f_d) / (ms_gu_mis + ms_d_mis) / 1e9},
+            "kernel": "q4_gemm_tc_kernel (tcgen05, in-kernel dequant)", "unit": "TFLOP/s", "dtype": "bf16 x bf16(u4) -> f32",
+            "gate_up": tf_gu, "down": tf_d, "gate_up_down": tf_all, "ms": {"gate_up": ms_gu, "down": ms_d},
+            "peak_burst": burst, "peak_sustained": sustained, "peak_source": source, "peak_datasheet": 2250.0,
+            "frac_of_burst": tf_all / burst, "frac_of_sustained": tf_all / sustained, "frac_of_datasheet": tf_all / 2250.0}
+        sweep = {"workload": "config3-small-M sweep: weight-stream GB/s (0.5625 B per weight) per activation rows M, aligned tensors",
+                 "unit": "GB/s", "gate_up": {}, "down": {}}
+        bytes_gu, bytes_d = 2 * 0.5625 * inter * hidden, 0.5625 * hidden * inter
+        for shape, fn, nbytes in (("gate_up", gate_up, bytes_gu), ("down", down, bytes_d)):
+            cross = None
+            for m in (1, 2, 4, 8, 16, 32, 64):
+                ms_s = timed(fn, m, capi.FLAG_STREAM, 8)
+                ms_t = timed(fn, m, capi.FLAG_TENSOR, 8)
+                sweep[shape][str(m)] = {"stream": nbytes / ms_s / 1e6, "tensor": nbytes / ms_t / 1e6}
+                if cross is None and ms_t < ms_s:
+                    cross = m
+            sweep[shape]["tensor_wins_from_m"] = cross
+        out["small_m_sweep"] = sweep
+    del xa, xh, og, ou, od
+    return out
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons during the timed region."""
 
@@ -321,6 +418,8 @@ def run_ours(args) -> int:
                                 "avg_launch_us": ms * 1e3 / args.steps, "bytes_per_launch": total_bytes, "traffic": None}
             line["launch_per_stage_graph"] = {"value": total_bytes * args.steps / (ms_graph * 1e-3) / 1e9, "unit": UNIT,
                                               "ms_per_step": ms_graph / args.steps, "gpu_launches": launches_per_token}
+        if world == 1 and not args.no_secondary:
+            line.update(secondary_metrics(torch, rt, stack, stream, capi))
         if world == 1 and not args.no_cpu_baseline:
             from oracle import q4_oracle as oracle
 
@@ -349,6 +448,7 @@ def main() -> int:
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--misalign", type=int, default=2, help="byte offset of every other projection from a 16-byte boundary")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the prefill GEMM and small-M sweep figures")
     ap.add_argument("--no-chain", action="store_true", help="time the CUDA graph of per-stage launches on one GPU too")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -160,6 +160,8 @@ int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t k, uint64_t
  *      src/metal_runtime.rs:5476-6832) ---- */
 
 #define Q4B_FLAG_ACCUMULATE 1u /* out += projection */
+#define Q4B_FLAG_STREAM 2u     /* this call uses the streaming (decode) kernels whatever m is */
+#define Q4B_FLAG_TENSOR 4u     /* this call uses the tensor-core GEMM whatever m is */
 
 int q4b_matmul_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
                             const q4b_job *jobs, uint32_t n_jobs, float *const *outputs_dev, uint32_t flags,

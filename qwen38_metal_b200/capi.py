@@ -7,7 +7,7 @@ import os
 from . import build as _build
 
 Q4B_F32, Q4B_BF16 = 0, 1
-FLAG_ACCUMULATE = 1
+FLAG_ACCUMULATE, FLAG_STREAM, FLAG_TENSOR = 1, 2, 4
 
 STATUS_NAMES = {
     0: "Ok", 1: "NoDevice", 2: "EmptyBuffer", 3: "ActivationPoolPoisoned", 4: "EmptyDimension",

@@ -12,11 +12,15 @@
 // writes out[m][n] with the lanes of a warp on consecutive n (coalesced). K advances 64 per stage = one affine
 // group, so a producer thread needs one scale and one bias per stage.
 //
-// Warp roles in a block of 14 warps (one block per SM, persistent over output tiles):
+// Warp roles in a block of 15 warps (one block per SM, persistent over output tiles):
 //   warp 0      one thread issues TMA loads of activation tiles (bf16, 128-byte swizzle)
 //   warp 1      allocates TMEM; one thread issues tcgen05.mma and commits to mbarriers
 //   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, store to global (two accumulators alternate)
 //   warps 6-13  dequantise: packed words -> bf16 pairs -> swizzled K-major tile in shared memory
+//   warp 14     one thread issues TMA loads of packed weight tiles (128 rows x 128 bytes = four K stages) into a
+//               staging ring, when the weights are 16-byte aligned; whole 128-byte lines per row keep DRAM pages
+//               and L2 sectors fully used and take the fetch latency off the dequantising warps. Weights at other
+//               alignments are fetched by the dequantising threads themselves, a few stages ahead, into registers.
 // Every wait is bounded: a wait that runs out sets an error flag, the block drains and frees its TMEM.
 #include <cuda.h>
 
@@ -26,12 +30,21 @@
 
 namespace q4 {
 
-constexpr int kGemmThreads = 14 * 32;
+constexpr int kGemmThreads = 15 * 32;
 constexpr int kGemmStages = 4;
 constexpr int kTileN = 128;              // weight rows per tile (UMMA M)
 constexpr int kTileK = 64;               // inputs per stage: one affine group, 128 bytes of bf16
 constexpr uint32_t kATileBytes = kTileN * kTileK * 2;  // 16 KB
 constexpr uint32_t kSpinLimit = 1u << 24;
+// Packed weights are staged in shared memory by TMA, a few K stages of all 128 rows at a time:
+//   16-byte aligned tensors: 128-byte rows (four stages), 128-byte swizzle, so the 16-byte reads of a warp spread
+//                            over all banks;
+//   any other alignment:     the tensor map starts at the address rounded down to 16 bytes and a tile holds an
+//                            80-byte window per row (two stages plus the misalignment), unswizzled; readers take
+//                            two 16-byte pieces and funnel-shift (the byte-addressed twin of the aligned read).
+constexpr uint32_t kWAlignedStages = 4, kWAlignedPitch = 128, kWAlignedBytes = kTileN * kWAlignedPitch;  // 16 KB
+constexpr uint32_t kWWindowStages = 2, kWWindowPitch = 80, kWWindowBytes = kTileN * kWWindowPitch;       // 10 KB
+constexpr uint32_t kParamPeriod = 8;     // K stages whose scales (or biases) one 16-byte load covers
 
 struct GemmParams {
     const uint8_t *w, *s, *b;  // packed weights, scales, biases (any byte alignment)
@@ -177,23 +190,36 @@ template <int BN>
 struct GemmSmem {
     static constexpr uint32_t kBTileBytes = BN * kTileK * 2;
     static constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr uint32_t kBarrierOffset = kGemmStages * kStageBytes;
+    static constexpr uint32_t kWBufs = BN >= 256 ? 2 : 4;  // staged packed-weight tiles in flight
+    static constexpr uint32_t kWStageOffset = kGemmStages * kStageBytes;
+    static constexpr uint32_t kWRingBytes = kWBufs * kWAlignedBytes;
+    static constexpr uint32_t kWWindowBufs = kWRingBytes / kWWindowBytes;  // 3 or 6 tiles of the window form
+    static constexpr uint32_t kBarrierOffset = kWStageOffset + kWRingBytes;
     static constexpr uint32_t kTotal = kBarrierOffset + 256 + 1024;  // barriers + slack for 1024-byte alignment
 };
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                    const __grid_constant__ CUtensorMap tmap_w,
                                                                     const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t gemm_smem_raw[];
     using L = GemmSmem<BN>;
     const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(gemm_smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = smem_base + L::kBarrierOffset;
-    // barrier slots (8 bytes each): full_x[4] full_w[4] empty[4] acc_full[2] acc_empty[2], then tmem base, abort flag
+    // barrier slots (8 bytes each): full_x[4] full_w[4] empty[4] acc_full[2] acc_empty[2], tmem base and abort flag
+    // at +128/+136, then staged_full[6] at +144 and staged_empty[6] at +192
     auto full_x = [&](uint32_t s) { return bars + 8u * s; };
     auto full_w = [&](uint32_t s) { return bars + 32u + 8u * s; };
     auto empty = [&](uint32_t s) { return bars + 64u + 8u * s; };
     auto acc_full = [&](uint32_t a) { return bars + 96u + 8u * a; };
     auto acc_empty = [&](uint32_t a) { return bars + 112u + 8u * a; };
+    auto staged_full = [&](uint32_t b) { return bars + 144u + 8u * b; };
+    auto staged_empty = [&](uint32_t b) { return bars + 192u + 8u * b; };
+    // geometry of the staged weight tiles for this launch
+    const bool windowed = p.w_misalign != 0;
+    const uint32_t w_bufs = windowed ? L::kWWindowBufs : L::kWBufs;
+    const uint32_t w_stages = windowed ? kWWindowStages : kWAlignedStages;
+    const uint32_t w_bytes = windowed ? kWWindowBytes : kWAlignedBytes;
     uint8_t *smem_generic = gemm_smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(gemm_smem_raw));
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_generic + L::kBarrierOffset + 128);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_generic + L::kBarrierOffset + 136);
@@ -210,6 +236,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         for (uint32_t a = 0; a < 2; ++a) {
             mbar_init(acc_full(a), 1);
             mbar_init(acc_empty(a), 4);  // one arrival per epilogue warp
+        }
+        for (uint32_t b = 0; b < 6; ++b) {
+            mbar_init(staged_full(b), 1);
+            mbar_init(staged_empty(b), 8);  // one arrival per producer warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -268,6 +298,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
                 if (ok) umma_commit(acc_full(acc));
             }
         }
+    } else if (warp == 14) {
+        // ---- TMA producer: packed weight tiles ----
+        if (lane == 0) {
+            const uint32_t w_tiles = (k_blocks + w_stages - 1) / w_stages;
+            uint32_t wit = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const uint32_t n0 = (tile / p.tiles_m) * kTileN;
+                for (uint32_t wt = 0; wt < w_tiles; ++wt, ++wit) {
+                    const uint32_t wb = wit % w_bufs, ph = (wit / w_bufs) & 1u;
+                    if (!mbar_wait(staged_empty(wb), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(staged_full(wb), w_bytes);
+                    // x is a byte offset from the (rounded-down) tensor base: a multiple of 16 in both forms
+                    tma_load_2d(smem_base + L::kWStageOffset + wb * w_bytes, &tmap_w, staged_full(wb), (int32_t)(wt * w_stages * 32u), (int32_t)n0);
+                }
+            }
+        }
     } else if (warp < 6) {
         // ---- epilogue: TMEM -> registers -> global ----
         const uint32_t quarter = warp & 3u;  // a warp may touch TMEM lanes 32*(warp%4) .. +31
@@ -306,36 +353,69 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         const uint32_t pid = threadIdx.x - 6 * 32;
         const uint32_t row = pid >> 1, part = pid & 1u;
         const uint32_t groups = p.k / 64;
-        uint32_t it = 0;
+        uint32_t it = 0, wit = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const uint32_t n0 = (tile / p.tiles_m) * kTileN;
             uint32_t grow = n0 + row;
-            grow = grow < p.n ? grow : p.n - 1u;  // rows past N are computed from a valid row and never stored
-            const uint8_t *wrow = p.w + (uint64_t)grow * (p.k / 2) + part * 16u;
+            grow = grow < p.n ? grow : p.n - 1u;  // rows past N take a valid row's parameters and are never stored
             const uint8_t *srow = p.s + (uint64_t)grow * groups * 2u, *brow = p.b + (uint64_t)grow * groups * 2u;
-            for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
-                const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
-                // fetch before waiting for the stage: global latency overlaps the wait
-                const uint4 packed = p.w_misalign ? ldg_stream_v4_unaligned(wrow + kb * 32u, p.w_misalign) : ldg_stream_v4(wrow + kb * 32u);
-                uint32_t sc = ldg_bf16_bits(srow + 2u * kb), bi = ldg_bf16_bits(brow + 2u * kb);
-                sc |= sc << 16;
-                bi |= bi << 16;
-                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-                const uint32_t a_row = smem_base + s * L::kStageBytes + row * 128u;
-                const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-                for (uint32_t wi = 0; wi < 4; ++wi) {
-                    const uint32_t wv = words[wi];
-                    const uint32_t o0 = dequant_pair(wv, sc, bi), o1 = dequant_pair(wv >> 4, sc, bi);
-                    const uint32_t o2 = dequant_pair(wv >> 8, sc, bi), o3 = dequant_pair(wv >> 12, sc, bi);
-                    const uint32_t chunk = part * 4u + wi;  // 16-byte piece of the 128-byte row
-                    const uint32_t dst = a_row + ((chunk ^ (row & 7u)) << 4);  // 128-byte swizzle
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+            // Scales and biases of eight stages come in one 16-byte load each (any byte alignment), one period ahead,
+            // so that no load is waited for in the stage loop.
+            auto params = [&](const uint8_t *base, uint32_t kb) {
+                const uint8_t *q = base + 2u * kb;
+                return ldg_stream_v4_unaligned(q, (uint32_t)(reinterpret_cast<uintptr_t>(q) & 15u));
+            };
+            uint4 sc_next = params(srow, 0), bi_next = params(brow, 0);
+            for (uint32_t kb0 = 0; kb0 < k_blocks && ok; kb0 += kParamPeriod) {
+                const uint4 sc8 = sc_next, bi8 = bi_next;
+                if (kb0 + kParamPeriod < k_blocks) {
+                    sc_next = params(srow, kb0 + kParamPeriod);
+                    bi_next = params(brow, kb0 + kParamPeriod);
                 }
-                fence_async_smem();  // the tensor core reads shared memory through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_w(s));
+                const uint32_t scw[4] = {sc8.x, sc8.y, sc8.z, sc8.w}, biw[4] = {bi8.x, bi8.y, bi8.z, bi8.w};
+#pragma unroll
+                for (uint32_t j = 0; j < kParamPeriod; ++j) {
+                    const uint32_t kb = kb0 + j;
+                    if (kb >= k_blocks) break;
+                    const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
+                    const uint32_t wb = wit % w_bufs;
+                    const uint32_t jj = windowed ? (j % kWWindowStages) : (j % kWAlignedStages);  // stage inside the staged tile
+                    if (jj == 0 && !mbar_wait(staged_full(wb), (wit / w_bufs) & 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t staged = smem_base + L::kWStageOffset + wb * w_bytes;
+                    uint4 packed;
+                    if (!windowed) {
+                        const uint32_t chunk = 2u * jj + part;
+                        packed = lds_v4(staged + row * kWAlignedPitch + ((chunk ^ (row & 7u)) << 4));
+                    } else {
+                        const uint32_t at = staged + row * kWWindowPitch + jj * 32u + part * 16u;
+                        packed = realign_16(lds_v4(at), lds_v4(at + 16u), p.w_misalign);
+                    }
+                    // both halves of the register get the stage's bf16 parameter
+                    const uint32_t sel = (j & 1u) ? 0x3232u : 0x1010u;
+                    const uint32_t sc = __byte_perm(scw[j >> 1], 0u, sel), bi = __byte_perm(biw[j >> 1], 0u, sel);
+                    if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t a_row = smem_base + s * L::kStageBytes + row * 128u;
+                    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+                    for (uint32_t wi = 0; wi < 4; ++wi) {
+                        const uint32_t wv = words[wi];
+                        const uint32_t o0 = dequant_pair(wv, sc, bi), o1 = dequant_pair(wv >> 4, sc, bi);
+                        const uint32_t o2 = dequant_pair(wv >> 8, sc, bi), o3 = dequant_pair(wv >> 12, sc, bi);
+                        const uint32_t chunk = part * 4u + wi;  // 16-byte piece of the 128-byte row
+                        const uint32_t dst = a_row + ((chunk ^ (row & 7u)) << 4);  // 128-byte swizzle
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+                    }
+                    fence_async_smem();  // the tensor core reads shared memory through the async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_w(s));
+                    ++it;
+                    if (jj == w_stages - 1u || kb + 1u == k_blocks) {
+                        // the warp's reads of the staged tile are complete (their values were consumed above)
+                        if (lane == 0) mbar_arrive(staged_empty(wb));
+                        ++wit;
+                    }
+                }
             }
         }
     }
@@ -378,11 +458,11 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int BN>
-cudaError_t launch_gemm(const CUtensorMap &map, const q4::GemmParams &p, uint32_t ctas, cudaStream_t stream) {
+cudaError_t launch_gemm(const CUtensorMap &map, const CUtensorMap &wmap, const q4::GemmParams &p, uint32_t ctas, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(q4::q4_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)q4::GemmSmem<BN>::kTotal);
     if (e != cudaSuccess) return e;
-    q4::q4_gemm_tc_kernel<BN><<<ctas, q4::kGemmThreads, q4::GemmSmem<BN>::kTotal, stream>>>(map, p);
+    q4::q4_gemm_tc_kernel<BN><<<ctas, q4::kGemmThreads, q4::GemmSmem<BN>::kTotal, stream>>>(map, wmap, p);
     return cudaGetLastError();
 }
 
@@ -413,6 +493,21 @@ extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, c
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
+    // packed weights as a byte matrix [n][k/2] from the tensor's address rounded down to 16 bytes (TMA needs that;
+    // the row pitch k/2 is a multiple of 32): 128-byte swizzled rows when the tensor is aligned, 80-byte windows else.
+    // The matrix is declared 16 bytes wider than k/2 in the window form so the last window of a row is in range; the
+    // extra bytes are the next row's first bytes or, after the last row, the padding every shard carries.
+    CUtensorMap wmap;
+    const uint32_t w_mis = (uint32_t)((uintptr_t)w & 15u);
+    {
+        const cuuint64_t wdims[2] = {(cuuint64_t)k / 2 + (w_mis ? 16u : 0u), n};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)k / 2};
+        const cuuint32_t wbox[2] = {w_mis ? q4::kWWindowPitch : q4::kWAlignedPitch, (cuuint32_t)q4::kTileN};
+        if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w - w_mis), wdims, wstrides, wbox, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, w_mis ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     q4::GemmParams p;
     p.w = w;
     p.s = s;
@@ -424,16 +519,16 @@ extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, c
     p.out_stride = out_stride;
     p.tiles_n = (n + q4::kTileN - 1) / q4::kTileN;
     p.tiles_m = (m + bn - 1) / bn;
-    p.w_misalign = (uint32_t)((uintptr_t)w & 15u);
+    p.w_misalign = w_mis;
     p.accumulate = accumulate ? 1u : 0u;
     p.error_flag = error_flag;
     const uint32_t tiles = p.tiles_n * p.tiles_m;
     const uint32_t ctas = tiles < sm_count ? tiles : sm_count;
     switch (bn) {
-        case 256: return launch_gemm<256>(map, p, ctas, stream);
-        case 128: return launch_gemm<128>(map, p, ctas, stream);
-        case 64: return launch_gemm<64>(map, p, ctas, stream);
-        case 32: return launch_gemm<32>(map, p, ctas, stream);
-        default: return launch_gemm<16>(map, p, ctas, stream);
+        case 256: return launch_gemm<256>(map, wmap, p, ctas, stream);
+        case 128: return launch_gemm<128>(map, wmap, p, ctas, stream);
+        case 64: return launch_gemm<64>(map, wmap, p, ctas, stream);
+        case 32: return launch_gemm<32>(map, wmap, p, ctas, stream);
+        default: return launch_gemm<16>(map, wmap, p, ctas, stream);
     }
 }

@@ -309,7 +309,8 @@ int enqueue_gemm(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, ui
 // Any m, any number of jobs: tensor-core GEMM from gemm_min_m rows, else launches the streaming kernel accepts.
 int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
                    const std::vector<Resolved> &jobs, float *const *outs, uint32_t flags, cudaStream_t stream) {
-    if (m >= rt->gemm_min_m) return enqueue_gemm(rt, x_dev, x_dtype, m, k, jobs, outs, flags, stream);
+    const bool tensor = (flags & Q4B_FLAG_TENSOR) ? true : (flags & Q4B_FLAG_STREAM) ? false : m >= rt->gemm_min_m;
+    if (tensor) return enqueue_gemm(rt, x_dev, x_dtype, m, k, jobs, outs, flags, stream);
     const uint32_t rows_per_launch = x_dtype == Q4B_F32 ? 2u : 8u;
     const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
     for (uint64_t m0 = 0; m0 < m; m0 += rows_per_launch) {

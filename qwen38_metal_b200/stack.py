@@ -12,8 +12,8 @@ not projections and are left out; what remains per layer is
     a' = bf16(d / rms(d))                              weightless RMS-norm keeps |a| near 1
 
 and after the last layer lm_head -> argmax. Weights are generated in HBM from a seed
-(`CudaRuntime.synth_q4`); every other projection starts two bytes off a 16-byte boundary, which is
-how tensors sit in real safetensors shards. With `world > 1` each rank holds rows
+(`CudaRuntime.synth_q4`); every other projection (odd positions of the grouped set, the down projection of odd
+layers) starts two bytes off a 16-byte boundary, which is how tensors sit in real safetensors shards. With `world > 1` each rank holds rows
 [floor(r*N/W), floor((r+1)*N/W)) of every projection; the caller gathers `h`, `d` and the argmax
 candidates between ranks (`gather` callbacks), all other work is local.
 
@@ -96,13 +96,13 @@ class SyntheticStack:
         tensor = 0
         self.proj: list[list[Projection]] = []
         self.down: list[Projection] = []
-        for _ in range(layers):
+        for layer in range(layers):
             row = []
             for i, n in enumerate(self.layer_rows):
                 row.append(self._make(tensor, n, hidden, misalign if i % 2 else 0))
                 tensor += 1
             self.proj.append(row)
-            self.down.append(self._make(tensor, hidden, inter, misalign))
+            self.down.append(self._make(tensor, hidden, inter, misalign if layer % 2 else 0))
             tensor += 1
         self.lm_head = self._make(tensor, vocab, hidden, 0)
         self.x0_tensor = tensor + 1

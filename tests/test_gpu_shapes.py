@@ -204,3 +204,28 @@ def test_tensor_core_gemm_residual_and_grouped(runtime, oracle):
     for out, add, t in zip(outs, added, trips):
         assert oracle.rel_l2(out, oracle.matmul_bf16_tiles(xf, *t, t[0].shape[0])) <= 2e-4
         assert np.allclose(add, out + 0.5, rtol=0, atol=1e-5)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 20])
+def test_per_call_variant_flags(runtime, oracle, m):
+    """Q4B_FLAG_STREAM / Q4B_FLAG_TENSOR pick the kernel family for one call whatever M is (the small-M sweep times
+    both at every M): both stay inside their tolerance of the oracle."""
+    import torch
+
+    from qwen38_metal_b200 import capi
+
+    n, k = 200, 1024
+    trip = synth(oracle, 500 + m, n, k)
+    bits, xf = x_bf16(oracle, 12, m, k)
+    job = upload_matrix(runtime, *trip)
+    x = torch.from_numpy(bits.view(np.int16).copy()).cuda()
+    outs = {}
+    for name, flag in (("stream", capi.FLAG_STREAM), ("tensor", capi.FLAG_TENSOR)):
+        y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+        runtime.matmul_batch_device(x.data_ptr(), capi.Q4B_BF16, m, k, [job], [y.data_ptr()], flag, 0)
+        torch.cuda.synchronize()
+        runtime.device_status()
+        outs[name] = y.cpu().numpy().reshape(m, n)
+    assert oracle.rel_l2(outs["stream"], oracle.matmul_f64(xf, *trip, n)) <= 1e-5
+    assert oracle.rel_l2(outs["tensor"], oracle.matmul_bf16_tiles(xf, *trip, n)) <= 2e-4
+    assert oracle.rel_l2(outs["tensor"], oracle.matmul_f64(xf, *trip, n)) <= 2e-3
