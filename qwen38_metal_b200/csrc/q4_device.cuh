@@ -88,6 +88,12 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
     return v;
 }
 
+__device__ __forceinline__ uint2 lds_v2(uint32_t smem_addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(smem_addr) : "memory");
+    return v;
+}
+
 // 16 bytes starting `mis` (0..15) bytes into the 32-byte window {lo, hi}
 __device__ __forceinline__ uint4 realign_16(uint4 lo, uint4 hi, uint32_t mis) {
     uint32_t w0 = lo.x, w1 = lo.y, w2 = lo.z, w3 = lo.w, w4 = hi.x, w5 = hi.y, w6 = hi.z, w7 = hi.w;

@@ -12,15 +12,18 @@
 // writes out[m][n] with the lanes of a warp on consecutive n (coalesced). K advances 64 per stage = one affine
 // group, so a producer thread needs one scale and one bias per stage.
 //
-// Warp roles in a block of 15 warps (one block per SM, persistent over output tiles):
+// Warp roles in a block of 23 warps (one block per SM, persistent over output tiles):
 //   warp 0      one thread issues TMA loads of activation tiles (bf16, 128-byte swizzle)
 //   warp 1      allocates TMEM; one thread issues tcgen05.mma and commits to mbarriers
 //   warps 2-5   epilogue: tcgen05.ld the fp32 accumulators, store to global (two accumulators alternate)
-//   warps 6-13  dequantise: packed words -> bf16 pairs -> swizzled K-major tile in shared memory
-//   warp 14     one thread issues TMA loads of packed weight tiles (128 rows x 128 bytes = four K stages) into a
+//   warp 6      one thread issues TMA loads of packed weight tiles (128 rows x 128 bytes = four K stages) into a
 //               staging ring, when the weights are 16-byte aligned; whole 128-byte lines per row keep DRAM pages
 //               and L2 sectors fully used and take the fetch latency off the dequantising warps. Weights at other
 //               alignments are fetched by the dequantising threads themselves, a few stages ahead, into registers.
+//   warps 7-22  dequantise: packed words (from the staging ring) -> bf16 pairs -> swizzled K-major tile in shared
+//               memory; four threads per weight row, two packed words each per stage. Sixteen warps, because a
+//               stage's work per warp is a short dependent chain (wait, read, convert, store, fence, arrive) and
+//               only other warps can fill its latencies.
 // Every wait is bounded: a wait that runs out sets an error flag, the block drains and frees its TMEM.
 #include <cuda.h>
 
@@ -30,10 +33,14 @@
 
 namespace q4 {
 
-constexpr int kGemmThreads = 15 * 32;
-constexpr int kGemmStages = 4;
+constexpr int kProducerWarps = 16;
+constexpr int kFirstProducerWarp = 7;
+constexpr int kGemmThreads = (kFirstProducerWarp + kProducerWarps) * 32;
 constexpr int kTileN = 128;              // weight rows per tile (UMMA M)
 constexpr int kTileK = 64;               // inputs per stage: one affine group, 128 bytes of bf16
+constexpr uint32_t kThreadsPerRow = kProducerWarps * 32 / kTileN;  // 4
+constexpr uint32_t kWordsPerThread = 8 / kThreadsPerRow;        // packed words of a row's stage per thread
+static_assert(kThreadsPerRow == 4 && kWordsPerThread == 2, "the producer indexing below assumes four threads per row");
 constexpr uint32_t kATileBytes = kTileN * kTileK * 2;  // 16 KB
 constexpr uint32_t kSpinLimit = 1u << 24;
 // Packed weights are staged in shared memory by TMA, a few K stages of all 128 rows at a time:
@@ -188,14 +195,17 @@ __global__ void __launch_bounds__(256) q4_gemm_prepare_x_kernel(const void *__re
 
 template <int BN>
 struct GemmSmem {
+    // more stages where the activation tile is small: a stage's round trip (free -> TMA fetch -> MMA -> free) is
+    // set by the fetch latency, whatever the tile size
+    static constexpr uint32_t kStages = BN >= 128 ? 4 : (BN == 64 ? 6 : 8);
     static constexpr uint32_t kBTileBytes = BN * kTileK * 2;
     static constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
     static constexpr uint32_t kWBufs = BN >= 256 ? 2 : 4;  // staged packed-weight tiles in flight
-    static constexpr uint32_t kWStageOffset = kGemmStages * kStageBytes;
+    static constexpr uint32_t kWStageOffset = kStages * kStageBytes;
     static constexpr uint32_t kWRingBytes = kWBufs * kWAlignedBytes;
     static constexpr uint32_t kWWindowBufs = kWRingBytes / kWWindowBytes;  // 3 or 6 tiles of the window form
     static constexpr uint32_t kBarrierOffset = kWStageOffset + kWRingBytes;
-    static constexpr uint32_t kTotal = kBarrierOffset + 256 + 1024;  // barriers + slack for 1024-byte alignment
+    static constexpr uint32_t kTotal = kBarrierOffset + 384 + 1024;  // barriers + slack for 1024-byte alignment
 };
 
 template <int BN>
@@ -206,23 +216,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
     using L = GemmSmem<BN>;
     const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(gemm_smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = smem_base + L::kBarrierOffset;
-    // barrier slots (8 bytes each): full_x[4] full_w[4] empty[4] acc_full[2] acc_empty[2], tmem base and abort flag
-    // at +128/+136, then staged_full[6] at +144 and staged_empty[6] at +192
+    // barrier slots (8 bytes each): full_x[8] full_w[8] empty[8] acc_full[2] acc_empty[2], the TMEM base and the
+    // abort flag, staged_full[6] staged_empty[6]
+    constexpr uint32_t kGemmStages = L::kStages;
     auto full_x = [&](uint32_t s) { return bars + 8u * s; };
-    auto full_w = [&](uint32_t s) { return bars + 32u + 8u * s; };
-    auto empty = [&](uint32_t s) { return bars + 64u + 8u * s; };
-    auto acc_full = [&](uint32_t a) { return bars + 96u + 8u * a; };
-    auto acc_empty = [&](uint32_t a) { return bars + 112u + 8u * a; };
-    auto staged_full = [&](uint32_t b) { return bars + 144u + 8u * b; };
-    auto staged_empty = [&](uint32_t b) { return bars + 192u + 8u * b; };
+    auto full_w = [&](uint32_t s) { return bars + 64u + 8u * s; };
+    auto empty = [&](uint32_t s) { return bars + 128u + 8u * s; };
+    auto acc_full = [&](uint32_t a) { return bars + 192u + 8u * a; };
+    auto acc_empty = [&](uint32_t a) { return bars + 208u + 8u * a; };
+    auto staged_full = [&](uint32_t b) { return bars + 240u + 8u * b; };
+    auto staged_empty = [&](uint32_t b) { return bars + 288u + 8u * b; };
     // geometry of the staged weight tiles for this launch
     const bool windowed = p.w_misalign != 0;
     const uint32_t w_bufs = windowed ? L::kWWindowBufs : L::kWBufs;
     const uint32_t w_stages = windowed ? kWWindowStages : kWAlignedStages;
     const uint32_t w_bytes = windowed ? kWWindowBytes : kWAlignedBytes;
     uint8_t *smem_generic = gemm_smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(gemm_smem_raw));
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_generic + L::kBarrierOffset + 128);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_generic + L::kBarrierOffset + 136);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_generic + L::kBarrierOffset + 224);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_generic + L::kBarrierOffset + 232);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two >= 32
@@ -230,7 +241,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kGemmStages; ++s) {
             mbar_init(full_x(s), 1);
-            mbar_init(full_w(s), 8);   // one arrival per producer warp
+            mbar_init(full_w(s), kProducerWarps);   // one arrival per producer warp
             mbar_init(empty(s), 1);    // tcgen05.commit
         }
         for (uint32_t a = 0; a < 2; ++a) {
@@ -239,13 +250,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         }
         for (uint32_t b = 0; b < 6; ++b) {
             mbar_init(staged_full(b), 1);
-            mbar_init(staged_empty(b), 8);  // one arrival per producer warp
+            mbar_init(staged_empty(b), kProducerWarps);  // one arrival per producer warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(bars + 128u, kTmemCols);
+        tmem_alloc(bars + 224u, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -298,20 +309,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
                 if (ok) umma_commit(acc_full(acc));
             }
         }
-    } else if (warp == 14) {
+    } else if (warp == 6) {
         // ---- TMA producer: packed weight tiles ----
         if (lane == 0) {
             const uint32_t w_tiles = (k_blocks + w_stages - 1) / w_stages;
-            uint32_t wit = 0;
+            uint32_t wb = 0, ph = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const uint32_t n0 = (tile / p.tiles_m) * kTileN;
-                for (uint32_t wt = 0; wt < w_tiles; ++wt, ++wit) {
-                    const uint32_t wb = wit % w_bufs, ph = (wit / w_bufs) & 1u;
+                for (uint32_t wt = 0; wt < w_tiles; ++wt) {
                     if (!mbar_wait(staged_empty(wb), ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(staged_full(wb), w_bytes);
                     // x is a byte offset from the (rounded-down) tensor base: a multiple of 16 in both forms
                     tma_load_2d(smem_base + L::kWStageOffset + wb * w_bytes, &tmap_w, staged_full(wb), (int32_t)(wt * w_stages * 32u), (int32_t)n0);
+                    if (++wb == w_bufs) {
+                        wb = 0;
+                        ph ^= 1u;
+                    }
                 }
             }
         }
@@ -349,11 +363,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
             if (lane == 0) mbar_arrive(acc_empty(acc));
         }
     } else {
-        // ---- dequantise producers: 256 threads, two per weight row, four packed words each ----
-        const uint32_t pid = threadIdx.x - 6 * 32;
-        const uint32_t row = pid >> 1, part = pid & 1u;
+        // ---- dequantise producers: 512 threads, four per weight row, two packed words each ----
+        const uint32_t pid = threadIdx.x - kFirstProducerWarp * 32;
+        const uint32_t row = pid >> 2, part = pid & 3u;
         const uint32_t groups = p.k / 64;
-        uint32_t it = 0, wit = 0;
+        uint32_t s = 0, ph = 0;      // stage ring position
+        uint32_t wb = 0, wph = 0;    // staging ring position
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const uint32_t n0 = (tile / p.tiles_m) * kTileN;
@@ -378,42 +393,49 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
                 for (uint32_t j = 0; j < kParamPeriod; ++j) {
                     const uint32_t kb = kb0 + j;
                     if (kb >= k_blocks) break;
-                    const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
-                    const uint32_t wb = wit % w_bufs;
                     const uint32_t jj = windowed ? (j % kWWindowStages) : (j % kWAlignedStages);  // stage inside the staged tile
-                    if (jj == 0 && !mbar_wait(staged_full(wb), (wit / w_bufs) & 1u, abort_flag)) { ok = false; break; }
+                    if (jj == 0 && !mbar_wait(staged_full(wb), wph, abort_flag)) { ok = false; break; }
                     const uint32_t staged = smem_base + L::kWStageOffset + wb * w_bytes;
-                    uint4 packed;
+                    uint32_t words[kWordsPerThread];  // this thread's 8 bytes: 16 of the row's 64 weights
                     if (!windowed) {
-                        const uint32_t chunk = 2u * jj + part;
-                        packed = lds_v4(staged + row * kWAlignedPitch + ((chunk ^ (row & 7u)) << 4));
+                        const uint32_t chunk = 2u * jj + (part >> 1);
+                        const uint2 v = lds_v2(staged + row * kWAlignedPitch + ((chunk ^ (row & 7u)) << 4) + (part & 1u) * 8u);
+                        words[0] = v.x;
+                        words[1] = v.y;
                     } else {
-                        const uint32_t at = staged + row * kWWindowPitch + jj * 32u + part * 16u;
-                        packed = realign_16(lds_v4(at), lds_v4(at + 16u), p.w_misalign);
+                        const uint32_t at = staged + row * kWWindowPitch + jj * 32u + (part >> 1) * 16u;
+                        const uint4 v = realign_16(lds_v4(at), lds_v4(at + 16u), p.w_misalign);
+                        words[0] = (part & 1u) ? v.z : v.x;
+                        words[1] = (part & 1u) ? v.w : v.y;
                     }
                     // both halves of the register get the stage's bf16 parameter
                     const uint32_t sel = (j & 1u) ? 0x3232u : 0x1010u;
                     const uint32_t sc = __byte_perm(scw[j >> 1], 0u, sel), bi = __byte_perm(biw[j >> 1], 0u, sel);
                     if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t a_row = smem_base + s * L::kStageBytes + row * 128u;
-                    const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
-                    for (uint32_t wi = 0; wi < 4; ++wi) {
+                    for (uint32_t wi = 0; wi < kWordsPerThread; ++wi) {
                         const uint32_t wv = words[wi];
                         const uint32_t o0 = dequant_pair(wv, sc, bi), o1 = dequant_pair(wv >> 4, sc, bi);
                         const uint32_t o2 = dequant_pair(wv >> 8, sc, bi), o3 = dequant_pair(wv >> 12, sc, bi);
-                        const uint32_t chunk = part * 4u + wi;  // 16-byte piece of the 128-byte row
+                        const uint32_t chunk = part * kWordsPerThread + wi;  // 16-byte piece of the 128-byte row
                         const uint32_t dst = a_row + ((chunk ^ (row & 7u)) << 4);  // 128-byte swizzle
                         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
                     }
                     fence_async_smem();  // the tensor core reads shared memory through the async proxy
                     __syncwarp();
                     if (lane == 0) mbar_arrive(full_w(s));
-                    ++it;
+                    if (++s == kGemmStages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                     if (jj == w_stages - 1u || kb + 1u == k_blocks) {
                         // the warp's reads of the staged tile are complete (their values were consumed above)
                         if (lane == 0) mbar_arrive(staged_empty(wb));
-                        ++wit;
+                        if (++wb == w_bufs) {
+                            wb = 0;
+                            wph ^= 1u;
+                        }
                     }
                 }
             }
