@@ -97,8 +97,12 @@ __device__ __forceinline__ uint2 lds_v2(uint32_t smem_addr) {
 // 16 bytes starting `mis` (0..15) bytes into the 32-byte window {lo, hi}
 __device__ __forceinline__ uint4 realign_16(uint4 lo, uint4 hi, uint32_t mis) {
     uint32_t w0 = lo.x, w1 = lo.y, w2 = lo.z, w3 = lo.w, w4 = hi.x, w5 = hi.y, w6 = hi.z, w7 = hi.w;
-    if (mis & 4) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
-    if (mis & 8) { w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = w6; }
+    // `mis` is the same for every lane of a warp (one tensor), so this is a branch, not a row of selects: offsets
+    // below four bytes -- two, for tensors that follow an odd-sized safetensors header -- need the shifts only
+    if (mis & 12u) {
+        if (mis & 4) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
+        if (mis & 8) { w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = w6; }
+    }
     const uint32_t sh = (mis & 3u) * 8u;
     uint4 out;
     out.x = __funnelshift_r(w0, w1, sh);
