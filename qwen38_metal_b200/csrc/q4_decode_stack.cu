@@ -266,6 +266,7 @@ __device__ __forceinline__ void build_activation(const StackStage &S, uint8_t *x
 // One contiguous run of chunks of one tile, as seen by one lane.
 struct Segment {
     uint32_t tile, c0, c1, cbase, job_index;
+    uint32_t c0v, c1v;               // the run in the job's virtual chunk numbering (c0, c1 are clamped to real chunks)
     uint32_t mis_w, mis_s, mis_b;   // byte misalignment (address & 15) of the job's three tensors
     uint32_t pmis;                   // misalignment of the parameter array this lane copies
     const uint8_t *wa, *wb, *pp;     // cursors at chunk cbase (weights: this lane's aligned window)
@@ -274,13 +275,17 @@ struct Segment {
 __device__ __forceinline__ void segment_setup(const GemvParams &P, uint64_t u, uint64_t u1, uint32_t &job_index, uint32_t lane,
                                               Segment &sg) {
     const uint32_t g = lane >> 2, t = lane & 3u, cpt = P.cpt;
-    sg.tile = (uint32_t)(u / cpt);
-    sg.c0 = (uint32_t)(u - (uint64_t)sg.tile * cpt);
-    const uint64_t left = u1 - u;
-    sg.c1 = (left < (uint64_t)(cpt - sg.c0)) ? sg.c0 + (uint32_t)left : cpt;
-    while (job_index + 1 < P.n_jobs && sg.tile >= P.jobs[job_index + 1].tile_begin) ++job_index;
+    while (job_index + 1 < P.n_jobs && u >= P.jobs[job_index + 1].unit_begin) ++job_index;
     sg.job_index = job_index;
     const GemvJob &job = P.jobs[job_index];
+    const uint32_t rel = (uint32_t)(u - job.unit_begin), vcpt = job.vcpt;
+    const uint32_t tile_local = rel / vcpt;
+    sg.tile = job.tile_begin + tile_local;
+    sg.c0v = rel - tile_local * vcpt;
+    const uint64_t left = u1 - u;
+    sg.c1v = (left < (uint64_t)(vcpt - sg.c0v)) ? sg.c0v + (uint32_t)left : vcpt;
+    sg.c0 = sg.c0v < cpt ? sg.c0v : cpt;
+    sg.c1 = sg.c1v < cpt ? sg.c1v : cpt;
     sg.cbase = sg.c0 & ~3u;
     sg.mis_w = job.w_misalign;
     sg.mis_s = (uint32_t)((uintptr_t)job.s & 15u);
@@ -301,7 +306,7 @@ __device__ __forceinline__ void segment_setup(const GemvParams &P, uint64_t u, u
 // Async copies of the first two groups of four chunks. With misaligned weights the chunk after the segment is
 // copied as well: the last lane of a quad completes its 16 bytes from the next chunk's first window.
 __device__ __forceinline__ void segment_prologue(const Segment &sg, uint32_t ring, uint32_t pring, uint32_t lane) {
-    const uint32_t wend = sg.c1 + (sg.mis_w ? 1u : 0u);
+    const uint32_t wend = sg.c1 + ((sg.mis_w && sg.c1 > sg.c0) ? 1u : 0u);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -371,7 +376,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                 first = false;
                 const uint32_t c0 = sg.c0, c1 = sg.c1;
                 const uint32_t mis_w = sg.mis_w, mis_s = sg.mis_s, mis_b = sg.mis_b;
-                const uint32_t wend = c1 + (mis_w ? 1u : 0u);
+                const uint32_t wend = c1 + ((mis_w && c1 > c0) ? 1u : 0u);
                 const uint8_t *wa = sg.wa, *wb = sg.wb, *pp = sg.pp;
                 uint32_t xa = xp_addr + sg.cbase * 256u;           // this lane's fragment of chunk cbase
                 uint32_t xs = xsum_addr + sg.cbase * 8u;           // group sum of this lane's group in chunk cbase
@@ -456,8 +461,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                 }
                 cp_async_wait<0>();
                 __syncwarp();
-                finish_tile<1>(P, inv_smem, split, worker, sg.tile, c0 == 0 && c1 == P.cpt, acc, lane, g, t, sg.job_index);
-                u += c1 - c0;
+                {
+                    const GemvJob &job = P.jobs[sg.job_index];
+                    finish_tile<1>(P, inv_smem, split, worker, sg.tile, sg.c0v == 0 && sg.c1v == job.vcpt, acc, lane, g, t, sg.job_index,
+                                   (uint64_t)job.unit_begin + (uint64_t)(sg.tile - job.tile_begin) * job.vcpt, job.vcpt);
+                }
+                u += sg.c1v - sg.c0v;
             }
         }
 

@@ -31,11 +31,15 @@ Q4_HD uint32_t q4_split_owner(const Q4Split &s, uint64_t u) {
     return (uint32_t)((((u + 1) * (uint64_t)s.workers) - 1) / s.units);
 }
 
-// workers contributing to tile t: [first, last]
-Q4_HD void q4_split_contributors(const Q4Split &s, uint32_t tile, uint32_t *first, uint32_t *last) {
-    uint64_t u0 = (uint64_t)tile * s.cpt;
+// workers contributing to the units [u0, u0 + span): [first, last]
+Q4_HD void q4_split_span_contributors(const Q4Split &s, uint64_t u0, uint32_t span, uint32_t *first, uint32_t *last) {
     *first = q4_split_owner(s, u0);
-    *last = q4_split_owner(s, u0 + s.cpt - 1);
+    *last = q4_split_owner(s, u0 + span - 1);
+}
+
+// workers contributing to tile t when every tile has s.cpt units: [first, last]
+Q4_HD void q4_split_contributors(const Q4Split &s, uint32_t tile, uint32_t *first, uint32_t *last) {
+    q4_split_span_contributors(s, (uint64_t)tile * s.cpt, s.cpt, first, last);
 }
 
 // partial slot worker w uses for tile t: slot 0 when t is the tile its range starts in, else 1

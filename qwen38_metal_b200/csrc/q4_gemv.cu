@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_generic_kernel(
         }
         cp_async_wait<0>();
 
-        finish_tile<NT>(p, p.row_inv, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index);
+        finish_tile<NT>(p, p.row_inv, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index, (uint64_t)tile * cpt, cpt);
         u += n;
         ++tile;
         c0 = 0;
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_fast_kernel(con
         cp_async_wait<0>();
         __syncwarp();
         if (p.trace && lane == 0) p.trace[blockIdx.x * 4 + 2] = global_ns();
-        finish_tile<NT>(p, p.row_inv, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index);
+        finish_tile<NT>(p, p.row_inv, split, worker, tile, c0 == 0 && c1 == cpt, acc, lane, g, t, job_index, (uint64_t)tile * cpt, cpt);
         u += c1 - c0;
         ++tile;
         c0 = 0;

@@ -207,18 +207,17 @@ __device__ __forceinline__ void store_tile(const GemvParams &p, const float *row
 }
 
 // A whole tile is stored at once; a tile split between warps is parked in the warp's partial slot and
-// summed, in worker order, by the last warp to arrive.
+// summed, in worker order, by the last warp to arrive. The tile occupies the units [u0, u0 + span) of the launch.
 template <int NT>
 __device__ __forceinline__ void finish_tile(const GemvParams &p, const float *row_inv, const Q4Split &split, uint32_t worker,
                                             uint32_t tile, bool whole, float (&acc)[NT][4], uint32_t lane, uint32_t g,
-                                            uint32_t t, uint32_t job_index) {
+                                            uint32_t t, uint32_t job_index, uint64_t u0, uint32_t span) {
     if (whole) {
         store_tile<NT>(p, row_inv, tile, acc, g, t, job_index);
         return;
     }
-    const uint64_t u0 = (uint64_t)tile * split.cpt;
     uint32_t first, last;
-    q4_split_contributors(split, tile, &first, &last);
+    q4_split_span_contributors(split, u0, span, &first, &last);
     const uint64_t first_begin = q4_split_begin(split, first);
     // only the first contributor can have started in an earlier tile (slot 1); everyone else starts inside this one
     const uint32_t first_slot = 2u * first + (first_begin < u0 ? 1u : 0u);

@@ -19,6 +19,11 @@ struct GemvJob {
     uint32_t out_stride;   // elements between activation rows of `out`
     uint32_t tile_begin;   // first 16-row tile of this job in the launch
     uint32_t w_misalign;   // (uintptr_t)w & 15
+    // persistent decode kernel only: a tile of this job counts as `vcpt` >= cpt units when the launch's work is cut
+    // into equal ranges -- the units past cpt are empty, so projections whose chunks cost more (weights at a byte
+    // offset) get proportionally fewer real chunks per warp; unit_begin = first unit of the job
+    uint32_t vcpt;
+    uint32_t unit_begin;
 };
 
 struct GemvParams {

@@ -106,6 +106,7 @@ struct q4b_runtime {
     std::vector<void *> arenas, peer_arenas;
     Pool trace, gemm_x, error_flag;
     uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
+    uint32_t chain_offset_cost = 120;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
     uint64_t prof_flops = 0;
     bool tracing = false;
     uint32_t trace_workers = 0;
@@ -374,6 +375,10 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     rt->sm_count = prop.multiProcessorCount;
     rt->total_bytes = prop.totalGlobalMem;
     snprintf(rt->name, sizeof rt->name, "%s", prop.name);
+    if (const char *cost = getenv("Q4B_CHAIN_OFFSET_COST")) {
+        const long v = strtol(cost, nullptr, 10);
+        if (v >= 100 && v <= 300) rt->chain_offset_cost = (uint32_t)v;
+    }
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
     if (rt->force_variant == "stream") rt->gemm_min_m = 0xffffffffu;   // never use the tensor-core GEMM
     if (rt->force_variant == "tensor") rt->gemm_min_m = 1;            // always use it
@@ -937,7 +942,13 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         x_halfs = kp > x_halfs ? kp : x_halfs;
         q4::GemvParams p;
         memset(&p, 0, sizeof p);
-        uint32_t tiles = 0;
+        // A chunk of a projection whose weights sit at a byte offset costs more instructions than an aligned one. The
+        // stage's work is cut into equal unit ranges, so such a projection's tiles are given `vcpt` > cpt units each
+        // (the extra ones empty): its warps get fewer real chunks and all warps finish together.
+        const uint32_t cpt = (groups + 1u) / 2u;
+        const uint32_t vcpt_offset = (cpt * rt->chain_offset_cost + 50u) / 100u;
+        uint32_t tiles = 0, vcpt_max = cpt;
+        uint64_t units = 0;
         for (uint32_t i = 0; i < S.n_jobs; ++i) {
             if (!S.outputs[i]) return fail(Q4B_INVALID_ARGUMENT, "stage %u output %u is null", si, i);
             q4::GemvJob &j = p.jobs[i];
@@ -949,7 +960,13 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
             j.out_stride = resolved[i].n;
             j.tile_begin = tiles;
             j.w_misalign = (uint32_t)((uintptr_t)resolved[i].w & 15u);
-            tiles += (resolved[i].n + 15u) / 16u;
+            j.vcpt = j.w_misalign ? vcpt_offset : cpt;
+            if (units > 0xffffffffull) return fail(Q4B_UNSUPPORTED, "stage %u is too large for the decode chain", si);
+            j.unit_begin = (uint32_t)units;
+            const uint32_t job_tiles = (resolved[i].n + 15u) / 16u;
+            tiles += job_tiles;
+            units += (uint64_t)job_tiles * j.vcpt;
+            vcpt_max = j.vcpt > vcpt_max ? j.vcpt : vcpt_max;
         }
         p.n_jobs = S.n_jobs;
         p.v_cols = 1;
@@ -958,10 +975,10 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         p.k = k;
         p.kp = kp;
         p.groups = groups;
-        p.cpt = (groups + 1u) / 2u;
-        p.units = (uint64_t)tiles * p.cpt;
+        p.cpt = cpt;
+        p.units = units;
         uint64_t workers = (uint64_t)rt->sm_count * warps;
-        const uint64_t min_chunks = (p.cpt + 31u) / 32u;
+        const uint64_t min_chunks = (vcpt_max + 31u) / 32u;
         if (workers > p.units / min_chunks) workers = p.units / min_chunks;
         if (workers == 0) workers = 1;
         p.workers = (uint32_t)workers;
