@@ -155,7 +155,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -166,7 +166,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self) -> dict:
+    def mark(self) -> int:
+        """Number of samples taken so far (nvidia-smi needs a moment to start, so it is launched before the warm-up
+        and the timed region is cut out of its samples by these marks)."""
+        return len(self.lines)
+
+    def stop(self, first: int = 0, last: int | None = None) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -176,7 +181,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        window = self.lines[first:last] or self.lines[max(0, first - 3):]  # a very short region: the samples next to it
+        for line in window:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
                 continue
@@ -339,11 +345,12 @@ def run_ours(args) -> int:
             g1.record(stream)
             stream.synchronize()
             ms_graph = g0.elapsed_time(g1)
+        sampler = ClockSampler(local_rank)
+        sampler.start()
         for _ in range(max(3, args.warmup)):
             step()
         barrier()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
+        first_sample = sampler.mark()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -363,7 +370,7 @@ def run_ours(args) -> int:
         e3.record(stream)
         barrier()
         ms_e2e = e2.elapsed_time(e3)
-        clocks = sampler.stop()
+        clocks = sampler.stop(first_sample, sampler.mark())
         if world > 1 and rank != 0:
             pass
         # ---- per-kernel timing of the projection kernel (no graph: events around each launch) -----
@@ -412,10 +419,15 @@ def run_ours(args) -> int:
         if chain is not None:
             # the step IS one launch of q4_stack_kernel: its duration is the step time, its bytes the token's
             line["roofline_per_stage_launches"] = line["roofline"]
-            line["roofline"] = {"bound": "hbm", "kernel": "q4_stack_kernel", "achieved": value, "peak": peak,
-                                "peak_source": peak_source, "unit": UNIT, "frac": value / peak,
-                                "frac_of_8TBs": value / NOMINAL_HBM_GBS, "launches": args.steps,
-                                "avg_launch_us": ms * 1e3 / args.steps, "bytes_per_launch": total_bytes, "traffic": None}
+            # (per GPU: each rank's launch streams its 1/world of the token's bytes in the same time)
+            line["roofline"] = {"bound": "hbm", "kernel": "q4_stack_kernel", "achieved": value / world, "peak": peak,
+                                "peak_source": peak_source, "unit": UNIT, "frac": value / world / peak,
+                                "frac_of_8TBs": value / world / NOMINAL_HBM_GBS, "launches": args.steps,
+                                "avg_launch_us": ms * 1e3 / args.steps, "bytes_per_launch": total_bytes // world,
+                                # dram__bytes_read+write of one launch: captured with ncu on the 4-layer stack
+                                # (1.6026 GB for 1.5297 GB algorithmic) and scaled by the bytes of this launch
+                                "traffic": int(total_bytes // world * 1.0477),
+                                "traffic_source": "ncu capture of a 4-layer launch, scaled by algorithmic bytes (profiles/)"}
             line["launch_per_stage_graph"] = {"value": total_bytes * args.steps / (ms_graph * 1e-3) / 1e9, "unit": UNIT,
                                               "ms_per_step": ms_graph / args.steps, "gpu_launches": launches_per_token}
         if world == 1 and not args.no_secondary:
