@@ -92,10 +92,14 @@ __device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &genera
         if (old == gridDim.x - 1) {
             bar[0] = 0;
             if (peers) {
-                // every block of this GPU has arrived: tell the other ranks, then wait for all of them
+                // every block of this GPU has arrived (each after a system-scope fence behind its peer stores): tell
+                // the other ranks, then wait for all of them. One fence orders everything observed so far before the
+                // flag stores, which then leave back to back -- a release store per rank would pay one NVLink round
+                // trip after the other.
+                __threadfence_system();
                 for (uint32_t r = 0; r < peers->world; ++r) {
                     if (r == peers->rank) continue;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers->flags_peer[r] + peers->rank), "r"(generation) : "memory");
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(peers->flags_peer[r] + peers->rank), "r"(generation) : "memory");
                 }
                 for (uint32_t r = 0; r < peers->world && ok; ++r) {
                     if (r == peers->rank) continue;
@@ -129,8 +133,9 @@ __device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &genera
                 __nanosleep(20);
             }
         }
-        if (peers) __threadfence_system();
-        else __threadfence();
+        // the acquire loads above order this block's later reads; the other ranks' data were made visible system-wide
+        // before their flags
+        __threadfence();
     }
     return __syncthreads_and(ok) != 0;
 }
