@@ -229,3 +229,81 @@ def test_per_call_variant_flags(runtime, oracle, m):
     assert oracle.rel_l2(outs["stream"], oracle.matmul_f64(xf, *trip, n)) <= 1e-5
     assert oracle.rel_l2(outs["tensor"], oracle.matmul_bf16_tiles(xf, *trip, n)) <= 2e-4
     assert oracle.rel_l2(outs["tensor"], oracle.matmul_f64(xf, *trip, n)) <= 2e-3
+
+
+def _synth_job(runtime, tensor, n, k, off):
+    from qwen38_metal_b200.runtime import MappedQ4AffineJob
+
+    wb = runtime.alloc_shard(n * k // 2 + off)
+    sb = runtime.alloc_shard(n * (k // 64) * 2 + off)
+    bb = runtime.alloc_shard(n * (k // 64) * 2 + off)
+    job = MappedQ4AffineJob(wb, off, sb, off, bb, off, n, off == 0)
+    runtime.synth_q4(SEED, tensor, 0.02, 0, n, k, job)
+    return job
+
+
+FULL_SHAPES = [("gate", 17408, 5120, 0), ("down", 5120, 17408, 0), ("gate at +2", 17408, 5120, 2), ("down at +2", 5120, 17408, 2)]
+
+
+@pytest.mark.parametrize("name,n,k,off", FULL_SHAPES, ids=[s[0] for s in FULL_SHAPES])
+def test_prefill_2048_rows_full_shapes_sampled(runtime, oracle, name, n, k, off):
+    """The prefill configuration at full size (M = 2048 activation rows; gate/up 17408 x 5120 and down 5120 x 17408,
+    weights generated in HBM): weight rows sampled from the first, a middle and the last tile, regenerated on the CPU,
+    must agree for all 2048 activation rows -- <= 2e-4 against the oracle that rounds w to bf16, <= 2e-3 against the
+    exact one -- and a second run is bit-identical."""
+    import torch
+
+    from qwen38_metal_b200 import capi
+
+    m = 2048
+    job = _synth_job(runtime, 600 + (n + k + off) % 97, n, k, off)
+    x = torch.empty(m * k, dtype=torch.bfloat16, device="cuda")
+    runtime.synth_bf16(SEED, 7000 + k, m * k, x.data_ptr(), 0)
+    out = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+    runtime.matmul_batch_device(x.data_ptr(), capi.Q4B_BF16, m, k, [job], [out.data_ptr()], 0, 0)
+    torch.cuda.synchronize()
+    runtime.device_status()
+    y = out.cpu().numpy().reshape(m, n)
+    runtime.matmul_batch_device(x.data_ptr(), capi.Q4B_BF16, m, k, [job], [out.data_ptr()], 0, 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().reshape(m, n), y)
+    xf = oracle.bf16_to_f32(x.view(torch.int16).cpu().numpy().view(np.uint16)).reshape(m, k)
+    for r0 in (0, (n // 2) & ~15, n - 16):
+        w, s, b = oracle.synth_q4(SEED, 600 + (n + k + off) % 97, 16, k, row0=r0)
+        assert oracle.rel_l2(y[:, r0:r0 + 16], oracle.matmul_bf16_tiles(xf, w, s, b, 16, threads=8)) <= 2e-4
+        assert oracle.rel_l2(y[:, r0:r0 + 16], oracle.matmul_factored_f32(xf, w, s, b, 16, threads=8)) <= 2e-3
+
+
+@pytest.mark.parametrize("name,n,k,off", FULL_SHAPES[:2] + FULL_SHAPES[3:], ids=[s[0] for s in FULL_SHAPES[:2] + FULL_SHAPES[3:]])
+def test_small_m_sweep_full_shapes_sampled(runtime, oracle, name, n, k, off):
+    """The sweep configuration at full size: M = 1, 2, 4, 8, 16, 32, 64 on the gate/up and down shapes, both kernel
+    families at every M, sampled weight rows against the oracle with each family's tolerance."""
+    import torch
+
+    from qwen38_metal_b200 import capi
+
+    tensor = 700 + (n + k + off) % 89
+    job = _synth_job(runtime, tensor, n, k, off)
+    m_max = 64
+    x = torch.empty(m_max * k, dtype=torch.bfloat16, device="cuda")
+    runtime.synth_bf16(SEED, 8000 + k, m_max * k, x.data_ptr(), 0)
+    xf = oracle.bf16_to_f32(x.view(torch.int16).cpu().numpy().view(np.uint16)).reshape(m_max, k)
+    samples = []
+    for r0 in (0, n - 16):
+        w, s, b = oracle.synth_q4(SEED, tensor, 16, k, row0=r0)
+        samples.append((r0, oracle.matmul_f64(xf, w, s, b, 16), oracle.matmul_bf16_tiles(xf, w, s, b, 16)))
+    out = torch.zeros(m_max * n, dtype=torch.float32, device="cuda")
+    for m in (1, 2, 4, 8, 16, 32, 64):
+        for flag in (capi.FLAG_STREAM, capi.FLAG_TENSOR):
+            out.zero_()
+            runtime.matmul_batch_device(x.data_ptr(), capi.Q4B_BF16, m, k, [job], [out.data_ptr()], flag, 0)
+            torch.cuda.synchronize()
+            runtime.device_status()
+            y = out[:m * n].cpu().numpy().reshape(m, n)
+            for r0, exact, tiles in samples:
+                got = y[:, r0:r0 + 16]
+                if flag == capi.FLAG_STREAM:
+                    assert oracle.rel_l2(got, exact[:m]) <= 1e-5, (m, r0)
+                else:
+                    assert oracle.rel_l2(got, tiles[:m]) <= 2e-4, (m, r0)
+                    assert oracle.rel_l2(got, exact[:m]) <= 2e-3, (m, r0)
