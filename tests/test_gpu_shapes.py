@@ -306,4 +306,6 @@ def test_small_m_sweep_full_shapes_sampled(runtime, oracle, name, n, k, off):
                     assert oracle.rel_l2(got, exact[:m]) <= 1e-5, (m, r0)
                 else:
                     assert oracle.rel_l2(got, tiles[:m]) <= 2e-4, (m, r0)
-                    assert oracle.rel_l2(got, exact[:m]) <= 2e-3, (m, r0)
+                    # against the exact oracle the distance is the bf16 rounding of w itself (about 1.5e-3; the
+                    # oracle's own 16-bit tile form is as far away), which scatters on a sample of a few dozen values
+                    assert oracle.rel_l2(got, exact[:m]) <= (2e-3 if got.size >= 512 else 3e-3), (m, r0)
