@@ -202,7 +202,9 @@ typedef struct q4b_stage {
 } q4b_stage;
 
 /* The ranks of a row-sharded chain (one process per GPU). flags[r] and cand[r] are two small zeroed device arrays
- * (8 x u32, 8 x 2 floats) living on rank r: entry [rank] is this GPU's own, the others are peer memory. */
+ * (32 and 64 bytes, 8-byte aligned) living on rank r: entry [rank] is this GPU's own, the others are peer memory.
+ * flags holds the 64-bit barrier arrival counter that every block of every rank adds to; cand holds one
+ * (best logit, token id) pair per rank. All ranks must run on GPUs with the same SM count. */
 typedef struct q4b_peers {
     uint32_t world;
     uint32_t rank;

@@ -39,8 +39,8 @@ struct StackStage {
 // later stage are stored into every rank's buffers, and each grid barrier also waits for the other ranks.
 struct StackPeers {
     uint32_t world, rank;
-    unsigned int *flags_local;             // [kMaxPeers] generation last announced by each rank, in this GPU's memory
-    unsigned int *flags_peer[kMaxPeers];   // the same array on every rank (this rank writes entry [rank] of each)
+    unsigned long long *arrivals_local;            // barrier arrivals of all blocks of all ranks, in this GPU's memory
+    unsigned long long *arrivals_peer[kMaxPeers];  // the same counter on every rank (every block adds to all of them)
     float2 *cand_local;                    // [kMaxPeers] (best logit, token id) candidates, in this GPU's memory
     float2 *cand_peer[kMaxPeers];
 };
@@ -81,60 +81,57 @@ __device__ __forceinline__ void lds_f32_keep(float &v, uint32_t addr, bool pred)
 // Grid-wide barrier with a bounded wait; with peers it is also a barrier across the GPUs of the chain.
 // Generations only grow (`generation` starts at the launch's epoch), so nothing has to be reset between launches.
 // Returns false when it gave up (error flag raised).
+//
+// Across GPUs every block announces itself directly in every rank's memory: after a system-scope fence behind its peer
+// stores it adds one to an arrival counter on each rank (remote reductions over NVLink, sent back to back) and then
+// polls the counter in its own GPU's memory until all blocks of all ranks have arrived `generation` times. There is no
+// gather-then-forward step: the critical path is one fence, one NVLink hop and a local poll. All ranks run the same
+// number of blocks. A rank that runs ahead into its next barrier only adds arrivals that the others wait for anyway.
 __device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &generation, int *error_flag, const StackPeers *peers) {
     __syncthreads();
     int ok = 1;
     ++generation;
     if (threadIdx.x == 0) {
-        if (peers) __threadfence_system();  // this block's peer stores are visible before its arrival counts
-        else __threadfence();
-        const unsigned int old = atomicAdd(&bar[0], 1u);
-        if (old == gridDim.x - 1) {
-            bar[0] = 0;
-            if (peers) {
-                // every block of this GPU has arrived (each after a system-scope fence behind its peer stores): tell
-                // the other ranks, then wait for all of them. One fence orders everything observed so far before the
-                // flag stores, which then leave back to back -- a release store per rank would pay one NVLink round
-                // trip after the other.
-                __threadfence_system();
-                for (uint32_t r = 0; r < peers->world; ++r) {
-                    if (r == peers->rank) continue;
-                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(peers->flags_peer[r] + peers->rank), "r"(generation) : "memory");
-                }
-                for (uint32_t r = 0; r < peers->world && ok; ++r) {
-                    if (r == peers->rank) continue;
-                    uint32_t spins = 0;
-                    while (true) {
-                        unsigned int seen;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(peers->flags_local + r) : "memory");
-                        if ((int)(seen - generation) >= 0) break;
-                        if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
-                            *error_flag = 1;
-                            ok = 0;
-                            break;
-                        }
-                        __nanosleep(20);
-                    }
-                }
-            }
-            __threadfence();
-            atomicExch(&bar[1], ok ? generation : 0xffffffffu);
-        } else {
+        if (peers) {
+            __threadfence_system();  // this block's stores (peer stores included) are visible before its arrival counts
+            for (uint32_t r = 0; r < peers->world; ++r)
+                asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(peers->arrivals_peer[r]), "l"(1ull) : "memory");
+            const unsigned long long target = (unsigned long long)generation * gridDim.x * peers->world;
             uint32_t spins = 0;
             while (true) {
-                unsigned int seen;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar + 1) : "memory");
-                if (seen == generation) break;
-                if (seen == 0xffffffffu || ++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
+                unsigned long long seen;
+                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(peers->arrivals_local) : "memory");
+                if (seen >= target) break;
+                if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
                     *error_flag = 1;
                     ok = 0;
                     break;
                 }
                 __nanosleep(20);
             }
+        } else {
+            __threadfence();
+            const unsigned int old = atomicAdd(&bar[0], 1u);
+            if (old == gridDim.x - 1) {
+                bar[0] = 0;
+                __threadfence();
+                atomicExch(&bar[1], generation);
+            } else {
+                uint32_t spins = 0;
+                while (true) {
+                    unsigned int seen;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar + 1) : "memory");
+                    if (seen == generation) break;
+                    if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
+                        *error_flag = 1;
+                        ok = 0;
+                        break;
+                    }
+                    __nanosleep(20);
+                }
+            }
         }
-        // the acquire loads above order this block's later reads; the other ranks' data were made visible system-wide
-        // before their flags
+        // the acquire loads above order this block's later reads behind the arrivals they observed
         __threadfence();
     }
     return __syncthreads_and(ok) != 0;
@@ -581,10 +578,10 @@ extern "C" void q4k_stack_fill_peers(void *image, uint32_t world, uint32_t rank,
     memset(p, 0, sizeof *p);
     p->world = world;
     p->rank = rank;
-    p->flags_local = static_cast<unsigned int *>(flags[rank]);
+    p->arrivals_local = static_cast<unsigned long long *>(flags[rank]);
     p->cand_local = static_cast<float2 *>(cand[rank]);
     for (uint32_t r = 0; r < world; ++r) {
-        p->flags_peer[r] = static_cast<unsigned int *>(flags[r]);
+        p->arrivals_peer[r] = static_cast<unsigned long long *>(flags[r]);
         p->cand_peer[r] = static_cast<float2 *>(cand[r]);
     }
 }

@@ -61,6 +61,11 @@ struct GemmParams {
     uint32_t tiles_n, tiles_m;
     uint32_t w_misalign;       // (uintptr_t)w & 15
     uint32_t accumulate;       // out += result
+    // With fewer output tiles than SMs the K range is cut into k_splits parts (each a multiple of eight stages) that
+    // different blocks work on; part s writes its partial sums to out + s * split_stride and a second kernel adds the
+    // parts in order (same result on every run).
+    uint32_t k_splits, split_blocks;  // parts, K stages per part
+    uint64_t split_stride;            // floats between the partial outputs of consecutive parts
     int *error_flag;           // set non-zero when a bounded wait runs out
 };
 
@@ -264,21 +269,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t k_blocks = p.k / kTileK;
-    const uint32_t total_tiles = p.tiles_n * p.tiles_m;
+    const uint32_t k_blocks_all = p.k / kTileK;
+    const uint32_t out_tiles = p.tiles_n * p.tiles_m;
+    const uint32_t total_tiles = out_tiles * p.k_splits;  // work items: (K part, output tile), parts outermost
+    // K stages [kb_lo, kb_lo + k_blocks) of work item `item`
+    auto part_of = [&](uint32_t item) { return item / out_tiles; };
+    auto stages_of = [&](uint32_t item) {
+        const uint32_t lo = part_of(item) * p.split_blocks;
+        return k_blocks_all - lo < p.split_blocks ? k_blocks_all - lo : p.split_blocks;
+    };
 
     if (warp == 0) {
         // ---- TMA producer: activation tiles ----
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const uint32_t tile = item % out_tiles, kb_lo = part_of(item) * p.split_blocks, k_blocks = stages_of(item);
                 const uint32_t m0 = (tile % p.tiles_m) * BN;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
                     if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(full_x(s), L::kBTileBytes);
-                    tma_load_2d(smem_base + s * L::kStageBytes + kATileBytes, &tmap_x, full_x(s), (int32_t)(kb * kTileK), (int32_t)m0);
+                    tma_load_2d(smem_base + s * L::kStageBytes + kATileBytes, &tmap_x, full_x(s), (int32_t)((kb_lo + kb) * kTileK), (int32_t)m0);
                 }
             }
         }
@@ -288,7 +301,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+            for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tcount) {
+                const uint32_t k_blocks = stages_of(item);
                 const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
@@ -312,16 +326,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
     } else if (warp == 6) {
         // ---- TMA producer: packed weight tiles ----
         if (lane == 0) {
-            const uint32_t w_tiles = (k_blocks + w_stages - 1) / w_stages;
             uint32_t wb = 0, ph = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const uint32_t tile = item % out_tiles, kb_lo = part_of(item) * p.split_blocks;
+                const uint32_t w_tiles = (stages_of(item) + w_stages - 1) / w_stages;
                 const uint32_t n0 = (tile / p.tiles_m) * kTileN;
                 for (uint32_t wt = 0; wt < w_tiles; ++wt) {
                     if (!mbar_wait(staged_empty(wb), ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(staged_full(wb), w_bytes);
                     // x is a byte offset from the (rounded-down) tensor base: a multiple of 16 in both forms
-                    tma_load_2d(smem_base + L::kWStageOffset + wb * w_bytes, &tmap_w, staged_full(wb), (int32_t)(wt * w_stages * 32u), (int32_t)n0);
+                    tma_load_2d(smem_base + L::kWStageOffset + wb * w_bytes, &tmap_w, staged_full(wb), (int32_t)((kb_lo + wt * w_stages) * 32u), (int32_t)n0);
                     if (++wb == w_bufs) {
                         wb = 0;
                         ph ^= 1u;
@@ -334,7 +349,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         const uint32_t quarter = warp & 3u;  // a warp may touch TMEM lanes 32*(warp%4) .. +31
         uint32_t tcount = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tcount) {
+            const uint32_t tile = item % out_tiles;
+            float *const out = p.out + (uint64_t)part_of(item) * p.split_stride;
             const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
             const uint32_t n0 = (tile / p.tiles_m) * kTileN, m0 = (tile % p.tiles_m) * BN;
             if (!mbar_wait(acc_full(acc), aph, abort_flag)) { ok = false; break; }
@@ -350,7 +367,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
                     for (int i = 0; i < 32; ++i) {
                         const uint32_t m = m0 + c0 + i;
                         if (m < p.m) {
-                            float *dst = p.out + (uint64_t)m * p.out_stride + n;
+                            float *dst = out + (uint64_t)m * p.out_stride + n;
                             float v = __uint_as_float(r[i]);
                             if (p.accumulate) v += *dst;
                             *dst = v;
@@ -370,11 +387,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         uint32_t s = 0, ph = 0;      // stage ring position
         uint32_t wb = 0, wph = 0;    // staging ring position
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+            const uint32_t tile = item % out_tiles, kb_lo = part_of(item) * p.split_blocks, k_blocks = stages_of(item);
             const uint32_t n0 = (tile / p.tiles_m) * kTileN;
             uint32_t grow = n0 + row;
             grow = grow < p.n ? grow : p.n - 1u;  // rows past N take a valid row's parameters and are never stored
-            const uint8_t *srow = p.s + (uint64_t)grow * groups * 2u, *brow = p.b + (uint64_t)grow * groups * 2u;
+            const uint8_t *srow = p.s + ((uint64_t)grow * groups + kb_lo) * 2u, *brow = p.b + ((uint64_t)grow * groups + kb_lo) * 2u;
             // Scales and biases of eight stages come in one 16-byte load each (any byte alignment), one period ahead,
             // so that no load is waited for in the stage loop.
             auto params = [&](const uint8_t *base, uint32_t kb) {
@@ -449,6 +467,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
     if (threadIdx.x == 0 && *abort_flag && p.error_flag) *p.error_flag = 1;
 }
 
+// out[m][n] (+)= part[0][m][n] + part[1][m][n] + ... in that order (the second step of a launch cut along K)
+__global__ void __launch_bounds__(256) q4_gemm_sum_parts_kernel(const float *__restrict__ parts, uint64_t split_stride, uint32_t k_splits,
+                                                               uint64_t elements, float *__restrict__ out, int accumulate) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= elements) return;
+    float acc = accumulate ? out[i] : 0.f;
+    for (uint32_t s = 0; s < k_splits; ++s) acc += __ldcg(parts + (uint64_t)s * split_stride + i);
+    out[i] = acc;
+}
+
 }  // namespace q4
 
 // ---------------------------------------------------------------------------------------------------------
@@ -499,10 +527,28 @@ extern "C" uint32_t q4k_gemm_tile_m(uint32_t m) {
     return 16;
 }
 
-// xp: prepared activations [m][k] bf16 (q4k_gemm_prepare_x), 16-byte aligned. One projection per launch.
+// How many parts the K range of an m x n x k projection is cut into (1: not cut): only when the output tiles fill less
+// than half of the SMs, every part at least 32 stages long and a multiple of eight stages.
+extern "C" uint32_t q4k_gemm_k_splits(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_count, uint32_t *split_blocks) {
+    const uint32_t bn = q4k_gemm_tile_m(m);
+    const uint32_t tiles = ((n + q4::kTileN - 1) / q4::kTileN) * ((m + bn - 1) / bn);
+    const uint32_t k_blocks = k / q4::kTileK;
+    uint32_t splits = tiles * 2 <= sm_count ? sm_count / tiles : 1;
+    if (splits > k_blocks / 32) splits = k_blocks / 32;
+    if (splits < 2) {
+        *split_blocks = k_blocks;
+        return 1;
+    }
+    const uint32_t per = ((k_blocks + splits - 1) / splits + 7u) & ~7u;
+    *split_blocks = per;
+    return (k_blocks + per - 1) / per;
+}
+
+// xp: prepared activations [m][k] bf16 (q4k_gemm_prepare_x), 16-byte aligned. One projection per launch. `parts`:
+// scratch for m * out_stride * q4k_gemm_k_splits(...) floats when that is more than one, else unused.
 extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_t *w, const uint8_t *s, const uint8_t *b,
                                    uint32_t n, float *out, uint32_t out_stride, int accumulate, int *error_flag, uint32_t sm_count,
-                                   cudaStream_t stream) {
+                                   float *parts, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return cudaErrorNotSupported;
     const uint32_t bn = q4k_gemm_tile_m(m);
@@ -544,13 +590,28 @@ extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, c
     p.w_misalign = w_mis;
     p.accumulate = accumulate ? 1u : 0u;
     p.error_flag = error_flag;
-    const uint32_t tiles = p.tiles_n * p.tiles_m;
-    const uint32_t ctas = tiles < sm_count ? tiles : sm_count;
-    switch (bn) {
-        case 256: return launch_gemm<256>(map, wmap, p, ctas, stream);
-        case 128: return launch_gemm<128>(map, wmap, p, ctas, stream);
-        case 64: return launch_gemm<64>(map, wmap, p, ctas, stream);
-        case 32: return launch_gemm<32>(map, wmap, p, ctas, stream);
-        default: return launch_gemm<16>(map, wmap, p, ctas, stream);
+    p.k_splits = q4k_gemm_k_splits(m, n, k, sm_count, &p.split_blocks);
+    p.split_stride = 0;
+    if (p.k_splits > 1) {
+        if (!parts) return cudaErrorInvalidValue;
+        p.out = parts;
+        p.out_stride = out_stride;
+        p.split_stride = (uint64_t)m * out_stride;
+        p.accumulate = 0;
     }
+    const uint32_t tiles = p.tiles_n * p.tiles_m * p.k_splits;
+    const uint32_t ctas = tiles < sm_count ? tiles : sm_count;
+    cudaError_t launched;
+    switch (bn) {
+        case 256: launched = launch_gemm<256>(map, wmap, p, ctas, stream); break;
+        case 128: launched = launch_gemm<128>(map, wmap, p, ctas, stream); break;
+        case 64: launched = launch_gemm<64>(map, wmap, p, ctas, stream); break;
+        case 32: launched = launch_gemm<32>(map, wmap, p, ctas, stream); break;
+        default: launched = launch_gemm<16>(map, wmap, p, ctas, stream); break;
+    }
+    if (launched != cudaSuccess || p.k_splits == 1) return launched;
+    const uint64_t elements = (uint64_t)m * out_stride;
+    q4::q4_gemm_sum_parts_kernel<<<(uint32_t)((elements + 255) / 256), 256, 0, stream>>>(parts, p.split_stride, p.k_splits, elements, out,
+                                                                                  accumulate ? 1 : 0);
+    return cudaGetLastError();
 }

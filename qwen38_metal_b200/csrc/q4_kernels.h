@@ -87,9 +87,10 @@ void q4k_stack_fill_peers(void *image, uint32_t world, uint32_t rank, void *cons
 
 cudaError_t q4k_gemm_prepare_x(const void *x, int x_is_f32, uint64_t elements, uint16_t *xp, cudaStream_t stream);
 uint32_t q4k_gemm_tile_m(uint32_t m);
+uint32_t q4k_gemm_k_splits(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_count, uint32_t *split_blocks);
 cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_t *w, const uint8_t *s, const uint8_t *b,
                         uint32_t n, float *out, uint32_t out_stride, int accumulate, int *error_flag, uint32_t sm_count,
-                        cudaStream_t stream);
+                        float *parts, cudaStream_t stream);
 
 cudaError_t q4k_synth_q4(uint64_t seed, uint64_t tensor, float sigma, uint64_t row0, uint64_t rows, uint32_t k,
                          uint8_t *w, uint8_t *s, uint8_t *b, cudaStream_t stream);

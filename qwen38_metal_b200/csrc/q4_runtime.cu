@@ -104,7 +104,7 @@ struct q4b_runtime {
     uint32_t gemv_ctas[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // [column tiles][aligned] resident warps per SM
     uint32_t max_workers = 0;
     std::vector<void *> arenas, peer_arenas;
-    Pool trace, gemm_x, error_flag;
+    Pool trace, gemm_x, gemm_parts, error_flag;
     uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
     uint32_t chain_offset_cost = 120;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
     uint64_t prof_flops = 0;
@@ -295,10 +295,13 @@ int enqueue_gemm(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, ui
              "q4_gemm_prepare_x launch");
     rt->launches++;
     for (size_t i = 0; i < jobs.size(); ++i) {
+        uint32_t split_blocks = 0;
+        const uint32_t splits = q4k_gemm_k_splits((uint32_t)m, jobs[i].n, (uint32_t)k, (uint32_t)rt->sm_count, &split_blocks);
+        if (splits > 1) Q4B_CUDA(rt->gemm_parts.ensure((size_t)splits * m * jobs[i].n * 4), "partial output scratch");
         if (int st = profile_open(rt, stream)) return st;
         Q4B_CUDA(q4k_gemm_tc((const uint16_t *)rt->gemm_x.ptr, (uint32_t)m, (uint32_t)k, jobs[i].w, jobs[i].s, jobs[i].b, jobs[i].n,
                              outs[i], jobs[i].n, (flags & Q4B_FLAG_ACCUMULATE) ? 1 : 0, (int *)rt->error_flag.ptr,
-                             (uint32_t)rt->sm_count, stream),
+                             (uint32_t)rt->sm_count, (float *)rt->gemm_parts.ptr, stream),
                  "q4_gemm_tc launch");
         rt->launches++;
         const uint64_t bytes = (uint64_t)jobs[i].n * (k / 2 + (k / 64) * 4) + m * k * 2 + m * jobs[i].n * 4;
@@ -426,7 +429,7 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
         if (s.ptr) cudaFree(s.ptr);
     for (void *p : rt->peer_arenas) cudaIpcCloseMemHandle(p);
     for (void *p : rt->arenas) cudaFree(p);
-    Pool *pools[] = {&rt->gemm_x, &rt->error_flag, &rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
+    Pool *pools[] = {&rt->gemm_x, &rt->gemm_parts, &rt->error_flag, &rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
