@@ -123,6 +123,26 @@ def secondary_metrics(torch, rt, stack, stream, capi):
             "gate_up": tf_gu, "down": tf_d, "gate_up_down": tf_all, "ms": {"gate_up": ms_gu, "down": ms_d},
             "peak_burst": burst, "peak_sustained": sustained, "peak_source": source, "peak_datasheet": 2250.0,
             "frac_of_burst": tf_all / burst, "frac_of_sustained": tf_all / sustained, "frac_of_datasheet": tf_all / 2250.0}
+        # config 0: one 5120 x 5120 matvec (14.7 MB, 2.3 us at the measured HBM peak) -- 48 distinct matrices carved out
+        # of lm_head's rows so that no launch finds its weights in L2
+        from qwen38_metal_b200.runtime import MappedQ4AffineJob
+
+        head = stack.lm_head.job
+        groups = hidden // 64
+        singles = [MappedQ4AffineJob(head.weights, head.weight_offset + r * hidden * (hidden // 2), head.scales,
+                                     head.scale_offset + r * hidden * groups * 2, head.biases,
+                                     head.bias_offset + r * hidden * groups * 2, hidden, True)
+                   for r in range(min(48, stack.lm_head.rows // hidden))]
+
+        def single(layer, m, flags):
+            rt.matmul_batch_device(xa.data_ptr(), capi.Q4B_BF16, m, hidden, [singles[layer % len(singles)]], [od.data_ptr()], flags, raw)
+
+        if singles:
+            ms_single = timed(single, 1, 0, len(singles))
+            nbytes = 0.5625 * hidden * hidden
+            out["single_matvec"] = {"workload": "config0: M=1, K=N=5120, bf16 activation, graph of launches over distinct matrices",
+                                    "unit": "GB/s", "value": nbytes / ms_single / 1e6, "us_per_call": ms_single * 1e3,
+                                    "bytes_per_call": nbytes, "frac_of_measured_hbm": nbytes / ms_single / 1e6 / measured_peaks()[0]}
         sweep = {"workload": "config3-small-M sweep: weight-stream GB/s (0.5625 B per weight) per activation rows M, aligned tensors",
                  "unit": "GB/s", "gate_up": {}, "down": {}}
         bytes_gu, bytes_d = 2 * 0.5625 * inter * hidden, 0.5625 * hidden * inter
