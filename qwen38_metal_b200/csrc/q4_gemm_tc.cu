@@ -527,14 +527,35 @@ extern "C" uint32_t q4k_gemm_tile_m(uint32_t m) {
     return 16;
 }
 
-// How many parts the K range of an m x n x k projection is cut into (1: not cut): only when the output tiles fill less
-// than half of the SMs, every part at least 32 stages long and a multiple of eight stages.
+// How many parts the K range of an m x n x k projection is cut into (1: not cut), every part at least 32 stages long
+// and a multiple of eight stages. Two cases: the output tiles fill less than half of the SMs (as many parts as fit), or
+// the last of several rounds of tiles would leave many SMs idle (2 to 4 parts, the fewest that bring the rounds to
+// 85 % occupancy; the extra pass over the partial outputs costs less than the idle round).
 extern "C" uint32_t q4k_gemm_k_splits(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_count, uint32_t *split_blocks) {
     const uint32_t bn = q4k_gemm_tile_m(m);
     const uint32_t tiles = ((n + q4::kTileN - 1) / q4::kTileN) * ((m + bn - 1) / bn);
     const uint32_t k_blocks = k / q4::kTileK;
-    uint32_t splits = tiles * 2 <= sm_count ? sm_count / tiles : 1;
-    if (splits > k_blocks / 32) splits = k_blocks / 32;
+    const uint32_t longest = k_blocks / 32;  // most parts the K range allows
+    uint32_t splits = 1;
+    if (tiles * 2 <= sm_count) {
+        splits = sm_count / tiles;
+    } else {
+        auto fill = [&](uint32_t s) {
+            const uint32_t items = tiles * s, rounds = (items + sm_count - 1) / sm_count;
+            return (double)items / ((double)rounds * sm_count);
+        };
+        if (fill(1) < 0.85) {
+            double best = fill(1);
+            for (uint32_t s = 2; s <= 4 && s <= longest; ++s) {
+                if (fill(s) > best + 0.05) {
+                    best = fill(s);
+                    splits = s;
+                    if (best >= 0.85) break;
+                }
+            }
+        }
+    }
+    if (splits > longest) splits = longest;
     if (splits < 2) {
         *split_blocks = k_blocks;
         return 1;
