@@ -197,7 +197,10 @@ __device__ __forceinline__ void build_activation(const StackStage &S, uint8_t *x
                     const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const float h = (a[i] * (1.0f / (1.0f + expf(-a[i])))) * u[i];  // qwen38_swiglu_rows
+                        // qwen38_swiglu_rows with the hardware exponential and reciprocal (as Metal's fast math does): every
+                        // block evaluates all of it, so the full-precision forms were most of this stage's rebuild time;
+                        // the result is rounded to bf16 right away
+                        const float h = __fdividef(a[i], 1.0f + __expf(-a[i])) * u[i];
                         v[it][i] = bf16_bits_to_float(float_to_bf16_bits(h));
                     }
                 } else {
