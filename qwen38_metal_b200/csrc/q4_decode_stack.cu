@@ -49,7 +49,7 @@ struct StackParams {
     const StackStage *stages;
     uint32_t n_stages;
     uint32_t x_halfs;       // capacity of the shared activation buffer in fp16 elements (largest kp)
-    unsigned int *barrier;  // [0] arrivals, [1] generation; both zero at launch
+    unsigned int *barrier;  // [0] arrivals of all blocks at all barriers of this launch; zero at launch
     int *error_flag;
     const float *logits;    // output of the last stage to reduce, or null
     uint32_t vocab, index_base;
@@ -110,25 +110,22 @@ __device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &genera
                 __nanosleep(20);
             }
         } else {
+            // one GPU: every block adds to one counter (zero at launch) and polls it until all blocks have arrived
+            // `generation` times -- no last-arriver hop
             __threadfence();
-            const unsigned int old = atomicAdd(&bar[0], 1u);
-            if (old == gridDim.x - 1) {
-                bar[0] = 0;
-                __threadfence();
-                atomicExch(&bar[1], generation);
-            } else {
-                uint32_t spins = 0;
-                while (true) {
-                    unsigned int seen;
-                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar + 1) : "memory");
-                    if (seen == generation) break;
-                    if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
-                        *error_flag = 1;
-                        ok = 0;
-                        break;
-                    }
-                    __nanosleep(20);
+            atomicAdd(&bar[0], 1u);
+            const unsigned int target = generation * gridDim.x;
+            uint32_t spins = 0;
+            while (true) {
+                unsigned int seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar) : "memory");
+                if (seen >= target) break;
+                if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
+                    *error_flag = 1;
+                    ok = 0;
+                    break;
                 }
+                __nanosleep(20);
             }
         }
         // the acquire loads above order this block's later reads behind the arrivals they observed
