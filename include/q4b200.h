@@ -182,10 +182,15 @@ int q4b_rms_unit_bf16_device(q4b_runtime *rt, const float *in_dev, uint32_t rows
 
 #define Q4B_X_BF16 0u    /* activation = bf16 vector src0[k] */
 #define Q4B_X_SWIGLU 1u  /* activation = bf16(silu(src0) * src1), fp32 vectors (qwen38_swiglu_rows) */
-#define Q4B_X_RMS 2u     /* activation = bf16(src0 / sqrt(mean(src0^2) + eps)), fp32 vector */
+#define Q4B_X_RMS 2u     /* activation = bf16(v / sqrt(mean(v^2) + eps)), v = fp32 vector src0 (or a sum of vectors) */
 
 /* One stage: build an activation of k elements from device vectors, then run n_jobs projections of it (M=1) into
- * outputs[i] (device, jobs[i].output_rows floats). Stages run in order; a stage may read what earlier stages wrote. */
+ * outputs[i] (device, jobs[i].output_rows floats). Stages run in order; a stage may read what earlier stages wrote.
+ * The chain is free to reorder work that nothing in it depends on: a projection whose output no later stage reads
+ * (Q/K/V and the DeltaNet inputs of the reference's layer, src/metal_runtime.rs:3463-3517) may run while the next
+ * stage is already in progress; every output is complete when the launch is. When a stage is the SwiGLU of two
+ * whole outputs of the stage before it, those two projections are streamed row-interleaved and the SwiGLU is
+ * applied as their rows finish (the fp32 outputs are still written). */
 typedef struct q4b_stage {
     uint32_t x_kind;
     float eps;
@@ -196,15 +201,27 @@ typedef struct q4b_stage {
     const q4b_job *jobs;
     uint32_t n_jobs;
     float *const *outputs;
-    /* Row-sharded chains only, else null: peer_outputs[i * 8 + r] is where rank r keeps the rows of job i that this
-     * rank computes (peer memory opened with q4b_arena_open), or null when that output is not needed elsewhere. */
+    /* Sharded chains only, else null: peer_outputs[i * 8 + r] is where rank r keeps its copy of the output of job i
+     * that this rank computes (peer memory opened with q4b_arena_open), or null when rank r does not need it. */
     float *const *peer_outputs;
+    /* K-slice: the jobs' tensors have rows of k_total inputs (0: k) of which this stage multiplies inputs
+     * [k_begin, k_begin + k) with its k-element activation; the tensors are read in place through strided rows.
+     * k_begin must be a multiple of 64, k of 128, k_total of 512. */
+    uint64_t k_total;
+    uint64_t k_begin;
+    /* Q4B_X_RMS only: src0 is the first of src_parts (0 = 1) fp32 vectors, src_part_stride bytes apart, that are
+     * added in order before the norm (partial outputs of a projection cut along K, one per rank). */
+    uint32_t src_parts;
+    uint32_t reserved;
+    uint64_t src_part_stride;
+    void *sum_out; /* optional (Q4B_X_RMS): the summed fp32 vector (k elements) */
 } q4b_stage;
 
-/* The ranks of a row-sharded chain (one process per GPU). flags[r] and cand[r] are two small zeroed device arrays
+/* The ranks of a sharded chain (one process per GPU). flags[r] and cand[r] are two small zeroed device arrays
  * (32 and 64 bytes, 8-byte aligned) living on rank r: entry [rank] is this GPU's own, the others are peer memory.
- * flags holds the 64-bit barrier arrival counter that every block of every rank adds to; cand holds one
- * (best logit, token id) pair per rank. All ranks must run on GPUs with the same SM count. */
+ * flags holds the 64-bit count of ranks that have arrived at cross-GPU barriers and, behind it, the count this
+ * rank's earlier launches have used up; cand holds one (best logit, token id) pair per rank.
+ * All ranks must run on GPUs with the same SM count. */
 typedef struct q4b_peers {
     uint32_t world;
     uint32_t rank;
@@ -219,22 +236,36 @@ int q4b_arena_open(q4b_runtime *rt, const uint8_t handle[64], void **peer_ptr);
 
 typedef struct q4b_chain q4b_chain;
 
-/* Compiles a list of stages into one cooperative kernel launch (one resident block per SM, grid barriers between
- * stages, next-stage weights prefetched across the barrier). Requires k % 512 == 0 and k <= q4b_chain_max_k().
+/* Compiles a list of stages into one cooperative kernel launch (one resident block per SM; barriers between
+ * dependent stages, split into an arrival and a later wait with independent projections in between; next weights
+ * requested before each wait). Requires k <= q4b_chain_max_k() except for a fused SwiGLU stage.
  * If logits is not null, the vocab floats there are reduced to *token_dev (+ index_base; ties to the lowest index)
  * and the winning value to *best_dev after the last stage.
- * With `peers` (row-sharded stack, every rank creates the same chain over its own row slices) results are also stored
- * into the other ranks' buffers with peer stores, every barrier spans all ranks, `vocab`/`index_base` describe this
+ * With `peers` (every rank creates the same chain over its own slices) outputs with peer_outputs are also stored
+ * into the other ranks' buffers, the barrier behind such a stage spans all ranks, `vocab`/`index_base` describe this
  * rank's slice and the token is the winner over all slices. All ranks must launch the chain the same number of
- * times; a multi-rank chain must not be captured in a CUDA graph (its barrier epoch is a launch argument). */
+ * times. After a wait of a multi-rank chain has run out (Q4B_COMMAND_FAILED from q4b_device_status or
+ * q4b_chain_run) the ranks' counters are out of step: q4b_chain_run[_device] then returns Q4B_POOL_POISONED until
+ * the chain is destroyed, the arena zeroed on every rank and the chain created again. */
 int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32_t n_stages, const float *logits, uint32_t vocab,
                      uint32_t index_base, uint32_t *token_dev, float *best_dev, const q4b_peers *peers, q4b_chain **out);
 int q4b_chain_run_device(q4b_chain *chain, void *stream);
+/* Host-buffer twin of the token step (src/native.rs:3250-3274, 2644-2652: host slice in, token out): copies the
+ * first stage's bf16 activation (k elements) from x_host, runs the chain, returns the token id and, if best_host
+ * is not null, the winning logit. Synchronous; serialises on the runtime lock. */
+int q4b_chain_run(q4b_chain *chain, const void *x_host, uint32_t *token_host, float *best_host);
+/* Polls after which a barrier wait of this chain gives up (default 2^21; each poll is one read of device memory). */
+int q4b_chain_set_spin_limit(q4b_chain *chain, uint32_t polls);
 void q4b_chain_destroy(q4b_chain *chain);
 uint64_t q4b_chain_max_k(void);
-/* Per-block, per-stage timeline of the last run of a chain created while tracing was enabled (q4b_trace_enable):
- * four device-clock stamps in ns -- stage start, activation built, block's work done, barrier passed. */
-int q4b_chain_trace_read(q4b_chain *chain, uint64_t *stamps, uint64_t capacity_words, uint32_t *blocks, uint32_t *stages);
+int q4b_chain_phase_count(q4b_chain *chain, uint32_t *phases);
+/* Per-block, per-phase timeline of the last run of a chain created while tracing was enabled (q4b_trace_enable):
+ * eight device-clock stamps in ns per block and phase -- wait begun, wait over, activation rebuilt, warp 0 done with
+ * its units, block arrived at the barrier, three unused; zero where a step does not exist. phase_info[p] (optional)
+ * receives stage * 4 + role, role 0 = the stage's dependent projections, 1 = its deferred projections, 2 = deferred
+ * projections of the stage before. */
+int q4b_chain_trace_read(q4b_chain *chain, uint64_t *stamps, uint64_t capacity_words, uint32_t *blocks, uint32_t *phases,
+                         uint32_t *phase_info, uint32_t phase_info_capacity);
 
 /* ---- seeded synthetic tensors, generated in HBM (benchmark inputs) ---- */
 

@@ -59,6 +59,8 @@ class Stage(C.Structure):
         ("src0", C.c_void_p), ("src1", C.c_void_p), ("x_bf16_out", C.c_void_p),
         ("jobs", C.POINTER(Job)), ("n_jobs", C.c_uint32), ("outputs", C.POINTER(C.c_void_p)),
         ("peer_outputs", C.POINTER(C.c_void_p)),
+        ("k_total", C.c_uint64), ("k_begin", C.c_uint64), ("src_parts", C.c_uint32), ("reserved", C.c_uint32),
+        ("src_part_stride", C.c_uint64), ("sum_out", C.c_void_p),
     ]
 
 
@@ -123,7 +125,10 @@ def load() -> C.CDLL:
         "q4b_arena_create": [vp, u64, P(vp), C.c_char_p],
         "q4b_arena_open": [vp, C.c_char_p, P(vp)],
         "q4b_chain_run_device": [vp, vp],
-        "q4b_chain_trace_read": [vp, vp, u64, P(u32), P(u32)],
+        "q4b_chain_trace_read": [vp, vp, u64, P(u32), P(u32), vp, u32],
+        "q4b_chain_run": [vp, vp, P(u32), P(C.c_float)],
+        "q4b_chain_set_spin_limit": [vp, u32],
+        "q4b_chain_phase_count": [vp, P(u32)],
         "q4b_matvec_noalloc": [i32, vp, u64, vp, vp, vp, u64, vp, vp],
         "q4b_shard_free": [vp, u32],
         "q4b_store_open": [C.c_char_p, P(vp)],
@@ -181,8 +186,8 @@ EXPORTS = [
     "q4b_shard_info", "q4b_offset_is_aligned", "q4b_matvec_batch", "q4b_matmul_batch", "q4b_argmax_batch",
     "q4b_mlp_batch", "q4b_matmul_add_batch", "q4b_dequantize_row", "q4b_matmul_batch_device",
     "q4b_argmax_batch_device", "q4b_swiglu_device", "q4b_rms_unit_bf16_device", "q4b_synth_q4_device",
-    "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status", "q4b_matvec_noalloc", "q4b_noalloc_last_error", "q4b_chain_create", "q4b_chain_run_device",
-    "q4b_chain_destroy", "q4b_chain_max_k", "q4b_chain_trace_read", "q4b_arena_create", "q4b_arena_open",
+    "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status", "q4b_matvec_noalloc", "q4b_noalloc_last_error", "q4b_chain_create", "q4b_chain_run_device", "q4b_chain_run",
+    "q4b_chain_set_spin_limit", "q4b_chain_phase_count", "q4b_chain_destroy", "q4b_chain_max_k", "q4b_chain_trace_read", "q4b_arena_create", "q4b_arena_open",
     "q4b_shard_free",
 ]
 

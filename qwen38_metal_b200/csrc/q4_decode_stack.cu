@@ -3,64 +3,39 @@
 // The reference encodes a token as one command buffer of many dispatches (decode_layers,
 // src/metal_runtime.rs:2022-2081; encode_decode_linear_layer :3301-3520). On B200 a launch per projection group
 // leaves the memory system idle for longer than a group takes to stream (launch gap, the first-data latency of
-// every kernel, the tail of its slowest warp). Here one block per SM stays resident for the whole token:
-//   for every stage:  build the activation in shared memory from the previous stage's outputs
-//                     (bf16 vector | SwiGLU of two vectors | weightless RMS-norm of a vector),
-//                     stream this block's share of the stage's projections (same arithmetic and work split as the
-//                     single-launch kernels in q4_gemv.cu),
-//                     start the async copies of the next stage's first weights, then cross a grid barrier.
-// Weights do not depend on earlier results, so the copies issued before the barrier keep HBM busy while the
-// barrier and the activation rebuild run. After the last stage the blocks reduce the logits to a token id.
-// Every block computes the activation itself (identical code, identical result); nothing but outputs crosses SMs.
+// every kernel, the tail of its slowest warp). Here one block per SM stays resident for the whole token and walks a
+// list of phases (q4_stack.h):
+//   [wait for the previous barrier, rebuild the activation in shared memory]
+//   stream this warp's share of the phase's projections (the arithmetic of the single-launch kernels, q4_gemv.cu)
+//   [arrive at the next barrier]
+// Arrival and wait are separate steps. Projections that feed nothing downstream (Q/K/V, the DeltaNet inputs) are
+// placed between them, reading the previous activation from a second shared-memory buffer, so the weight stream
+// continues while the barrier completes. The first weights of every phase are requested before the wait that
+// precedes it: weights do not depend on earlier results.
 //
-// All waits are bounded: a barrier that does not complete within its limit raises the error flag and the block
-// leaves the kernel.
+// Fusions: a gate/up pair is streamed as tiles of 8 gate rows + the same 8 up rows, so a lane ends up with both sums
+// of a row and stores bf16(silu(gate)*up) (qwen38_swiglu_rows, shaders/qwen38.metal:4188-4198) plus a running
+// maximum; the next phase then only converts 2 bytes per input instead of evaluating the whole vector in every block.
+// Across GPUs the down projection is cut along K (each rank consumes the slice of the hidden vector it produced) and
+// the partial outputs are pushed to every rank with peer stores; the rebuild of the next activation adds them in rank
+// order. One cross-GPU barrier per layer: blocks arrive on a counter in their own GPU's memory, the last of them
+// forwards one arrival per rank over NVLink, waiters poll their own memory.
+//
+// All waits are bounded: a barrier that does not complete within the chain's poll limit raises the error flag and the
+// block leaves the kernel.
 #include <cooperative_groups.h>
 
 #include <cstring>
 
 #include "q4_gemv_core.cuh"
+#include "q4_stack.h"
 
 namespace q4 {
 
 constexpr int kStackRingBytes = kStages * kStageBytesAligned + 2 * 1024;  // weight ring + two parameter stages of 2 windows
-constexpr int kStackMaxIters = 5;                                        // activation blocks of 8 per thread
-constexpr uint32_t kBarrierSpinLimit = 1u << 21;
-
-struct StackStage {
-    GemvParams gemv;        // jobs, k, kp, groups, cpt, units, workers, partials, counters (xp/xsum/row_inv unused)
-    uint32_t x_kind;        // 0: bf16 vector src0; 1: bf16(silu(src0) * src1), fp32 inputs; 2: bf16(src0 / rms(src0)), fp32 input
-    float eps;
-    const void *src0, *src1;
-    uint16_t *x_bf16_out;   // optional: block 0 stores the bf16 activation it built (next token's input, inspection)
-};
-
-// Cross-GPU part of a row-sharded chain. Every rank runs the same chain on its row slices; outputs that feed a
-// later stage are stored into every rank's buffers, and each grid barrier also waits for the other ranks.
-struct StackPeers {
-    uint32_t world, rank;
-    unsigned long long *arrivals_local;            // barrier arrivals of all blocks of all ranks, in this GPU's memory
-    unsigned long long *arrivals_peer[kMaxPeers];  // the same counter on every rank (every block adds to all of them)
-    float2 *cand_local;                    // [kMaxPeers] (best logit, token id) candidates, in this GPU's memory
-    float2 *cand_peer[kMaxPeers];
-};
-
-struct StackParams {
-    const StackStage *stages;
-    uint32_t n_stages;
-    uint32_t x_halfs;       // capacity of the shared activation buffer in fp16 elements (largest kp)
-    unsigned int *barrier;  // [0] arrivals of all blocks at all barriers of this launch; zero at launch
-    int *error_flag;
-    const float *logits;    // output of the last stage to reduce, or null
-    uint32_t vocab, index_base;
-    float *part_val;        // [gridDim.x]
-    uint32_t *part_idx;     // [gridDim.x]
-    uint32_t *token;
-    float *best;
-    const StackPeers *peers;    // null on one GPU
-    unsigned int epoch;         // with peers: barrier generations consumed by earlier launches (flags only grow)
-    unsigned long long *trace;  // optional [blocks][n_stages][4] device-clock stamps (stage start, activation built, work done, barrier passed)
-};
+constexpr int kStackMaxIters = 5;                                        // activation blocks of 8 per thread (register-held rebuilds)
+constexpr int kXChunkBytes = 384;                                        // activation of one chunk: three digit planes of 128 bytes
+constexpr int kXSlack = kXChunkBytes;                                    // the fragment of the chunk after the last one is read ahead
 
 __device__ __forceinline__ unsigned long long stack_ns() {
     unsigned long long t;
@@ -77,247 +52,366 @@ __device__ __forceinline__ void lds_v4_keep(uint4 &v, uint32_t addr, bool pred) 
 __device__ __forceinline__ void lds_f32_keep(float &v, uint32_t addr, bool pred) {
     asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.shared.f32 %0, [%1];\n\t}" : "+f"(v) : "r"(addr), "r"((uint32_t)pred) : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-// Grid-wide barrier with a bounded wait; with peers it is also a barrier across the GPUs of the chain.
-// Generations only grow (`generation` starts at the launch's epoch), so nothing has to be reset between launches.
-// Returns false when it gave up (error flag raised).
-//
-// Across GPUs every block announces itself directly in every rank's memory: after a system-scope fence behind its peer
-// stores it adds one to an arrival counter on each rank (remote reductions over NVLink, sent back to back) and then
-// polls the counter in its own GPU's memory until all blocks of all ranks have arrived `generation` times. There is no
-// gather-then-forward step: the critical path is one fence, one NVLink hop and a local poll. All ranks run the same
-// number of blocks. A rank that runs ahead into its next barrier only adds arrivals that the others wait for anyway.
-__device__ __forceinline__ bool grid_barrier(unsigned int *bar, uint32_t &generation, int *error_flag, const StackPeers *peers) {
-    __syncthreads();
+// ---------------------------------------------------------------------------------------------------------
+// Barriers. Every block arrives exactly once per barrier and every block makes the same sequence of arrivals, so
+// the targets are plain multiples: after its n-th arrival a block waits for n * gridDim.x arrivals on the counter in
+// its own GPU's memory (zero at launch), or for n * world arrivals of whole ranks on the cross-GPU word (which only
+// grows; `gbase` is what earlier launches left there).
+// ---------------------------------------------------------------------------------------------------------
+struct SyncState {
+    uint32_t local_gen;   // arrivals this block has made on the local counter
+    uint32_t global_gen;  // of those, arrivals at cross-GPU barriers
+    const unsigned long long *gbase;  // shared memory: what earlier launches left on the cross-GPU word
+};
+
+// Called by every warp once it has finished the phase's units. The warp's results are ordered before the arrival by
+// a fence (system scope when it stored into other GPUs' memory); the last warp of the block arrives for the block,
+// and the block that completes the local count of a cross-GPU barrier forwards one arrival to every rank.
+template <int WARPS>
+__device__ __forceinline__ void phase_arrive(const StackParams &sp, uint32_t kind, const SyncState &ss, uint32_t *arrive_smem,
+                                             bool stored_to_peers, uint32_t lane, unsigned long long *tr, unsigned int *amax_global = nullptr,
+                                             uint32_t *amax_smem = nullptr) {
+    if (stored_to_peers) __threadfence_system();
+    else if (sp.flags & kFlagWarpFenceGpu) __threadfence();
+    else __threadfence_block();  // the block's last warp fences at device scope for everyone it has seen arrive
+    __syncwarp();
+    if (lane != 0) return;
+    const uint32_t before = atomicAdd(arrive_smem, 1u);
+    if (before != WARPS - 1) return;
+    *reinterpret_cast<volatile uint32_t *>(arrive_smem) = 0;  // the next arrival follows a block barrier
+    if (amax_global) {
+        const uint32_t mx = atomicExch(amax_smem, 0u);
+        if (mx) atomicMax(amax_global, mx);
+    }
+    __threadfence();
+    const unsigned int target = (ss.local_gen + 1u) * gridDim.x;
+    const unsigned int seen = atomicAdd(sp.local_bar, 1u);
+    if (tr) tr[4] = stack_ns();
+    if (kind == kSyncGlobal && seen + 1u == target) {
+        // every block of this GPU has arrived (each behind its own fence): tell all ranks, this one included
+        __threadfence_system();
+        const StackPeers *peers = sp.peers;
+        for (uint32_t r = 0; r < peers->world; ++r)
+            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(peers->flag_peer[r]), "l"(1ull) : "memory");
+    }
+}
+
+// Block-wide wait for the latest arrival; false when it gave up (error flag raised).
+__device__ __forceinline__ bool phase_wait(const StackParams &sp, uint32_t kind, const SyncState &ss) {
     int ok = 1;
-    ++generation;
     if (threadIdx.x == 0) {
-        if (peers) {
-            __threadfence_system();  // this block's stores (peer stores included) are visible before its arrival counts
-            for (uint32_t r = 0; r < peers->world; ++r)
-                asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(peers->arrivals_peer[r]), "l"(1ull) : "memory");
-            const unsigned long long target = (unsigned long long)generation * gridDim.x * peers->world;
-            uint32_t spins = 0;
+        uint32_t spins = 0;
+        if (kind == kSyncGlobal) {
+            const unsigned long long target = *ss.gbase + (unsigned long long)ss.global_gen * sp.peers->world;
             while (true) {
                 unsigned long long seen;
-                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(peers->arrivals_local) : "memory");
+                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(sp.peers->flag_local) : "memory");
                 if (seen >= target) break;
-                if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
-                    *error_flag = 1;
+                if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
+                    *sp.error_flag = 1;
                     ok = 0;
                     break;
                 }
                 __nanosleep(20);
             }
         } else {
-            // one GPU: every block adds to one counter (zero at launch) and polls it until all blocks have arrived
-            // `generation` times -- no last-arriver hop
-            __threadfence();
-            atomicAdd(&bar[0], 1u);
-            const unsigned int target = generation * gridDim.x;
-            uint32_t spins = 0;
+            const unsigned int target = ss.local_gen * gridDim.x;
             while (true) {
                 unsigned int seen;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar) : "memory");
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sp.local_bar) : "memory");
                 if (seen >= target) break;
-                if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile int *>(error_flag)) {
-                    *error_flag = 1;
+                if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
+                    *sp.error_flag = 1;
                     ok = 0;
                     break;
                 }
                 __nanosleep(20);
             }
         }
-        // the acquire loads above order this block's later reads behind the arrivals they observed
         __threadfence();
     }
     return __syncthreads_and(ok) != 0;
 }
 
-// deterministic block-wide sum / max through shared memory (same order on every block)
-template <int WARPS>
-__device__ __forceinline__ float block_sum(float v, float *red) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    __syncthreads();
-    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float total = 0.f;
-#pragma unroll
-    for (int i = 0; i < WARPS; ++i) total += red[i];
-    return total;
-}
-template <int WARPS>
-__device__ __forceinline__ uint32_t block_max_u32(uint32_t v, uint32_t *red) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, off));
-    __syncthreads();
-    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    uint32_t total = 0;
-#pragma unroll
-    for (int i = 0; i < WARPS; ++i) total = max(total, red[i]);
-    return total;
+// ---------------------------------------------------------------------------------------------------------
+// Activation rebuilds: fp16 after an exact power-of-two scaling, fragment order (k0,k4,k1,k5,k2,k6,k3,k7 inside each
+// block of 8), per-group sums, and the inverse scale. Each ends with a block barrier.
+// ---------------------------------------------------------------------------------------------------------
+struct XBuf {
+    uint8_t *xp;   // fp16 fragments
+    float *xsum;   // per-group sums
+    float *inv;    // inverse of the power-of-two scaling
+};
+
+// The activation is held as 23-bit fixed point: x' = round(x * 2^e) with 2^e putting the largest magnitude into
+// [2^21, 2^22). A bf16 value within 2^14 of the maximum is represented exactly, smaller ones to 2^-22 of the maximum.
+// e = 0 for an all-zero vector.
+__device__ __forceinline__ int scale_exponent(uint32_t amax_bits) {
+    const int e = 21 - ((int)((amax_bits >> 23) & 0xffu) - 127);
+    return amax_bits == 0 ? 0 : max(-100, min(100, e));
 }
 
-// Build the stage's activation in shared memory: fp16 after an exact power-of-two scaling, fragment order,
-// per-group sums, and the inverse scale. Ends with a block barrier.
+// x' is stored as three signed 8-bit digits, x' = d0 + 256 d1 + 65536 d2 with every digit in [-128, 127], one 128-byte
+// plane per digit and chunk. Inside a plane the byte order is the one the tensor-core B fragment of the integer MMA
+// (m16n8k32) wants, given that lane t of a quad feeds its own 32 consecutive nibbles of a weight row as A operand:
+// byte [t][r][i] (t: quad lane, r: one of the 8 B registers of the chunk's four MMAs, i: byte) holds input
+//   k = 32 t + 16 (r >> 2) + 8 (r & 1) + ((r >> 1) & 1) + 2 i.
+// One thread converts 8 consecutive inputs (k = 8b .. 8b+7): the even ones fill register r, the odd ones r + 2.
+__device__ __forceinline__ void emit_block(const float (&v)[8], float scale, uint32_t b, bool in_range, const XBuf &X) {
+    int xi[8];
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        xi[i] = __float2int_rn(v[i] * scale);
+        sum += xi[i];
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    uint32_t even[3] = {0, 0, 0}, odd[3] = {0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d0 = (xi[i] << 24) >> 24;
+        const int x1 = (xi[i] - d0) >> 8;
+        const int d1 = (x1 << 24) >> 24;
+        const int d2 = (x1 - d1) >> 8;
+        const uint32_t sh = 8u * (uint32_t)(i >> 1);
+        if (i & 1) {
+            odd[0] |= ((uint32_t)d0 & 0xffu) << sh;
+            odd[1] |= ((uint32_t)d1 & 0xffu) << sh;
+            odd[2] |= ((uint32_t)d2 & 0xffu) << sh;
+        } else {
+            even[0] |= ((uint32_t)d0 & 0xffu) << sh;
+            even[1] |= ((uint32_t)d1 & 0xffu) << sh;
+            even[2] |= ((uint32_t)d2 & 0xffu) << sh;
+        }
+    }
+    if (in_range) {
+        const uint32_t chunk = b >> 4, bb = b & 15u;
+        const uint32_t r = ((bb & 2u) << 1) | (bb & 1u);  // inputs 8 (bb & 3) + {0,2,4,6}: register r, the odd ones r + 2
+        uint8_t *dst = X.xp + (size_t)chunk * kXChunkBytes + (bb >> 2) * 32u + r * 4u;
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            *reinterpret_cast<uint32_t *>(dst + c * 128) = even[c];
+            *reinterpret_cast<uint32_t *>(dst + c * 128 + 8) = odd[c];
+        }
+        if ((threadIdx.x & 7u) == 0) X.xsum[b / 8] = (float)sum;
+    }
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
+    uint32_t bb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bb[i] = float_to_bf16_bits(v[i]);
+    uint4 plain;
+    plain.x = bb[0] | (bb[1] << 16);
+    plain.y = bb[2] | (bb[3] << 16);
+    plain.z = bb[4] | (bb[5] << 16);
+    plain.w = bb[6] | (bb[7] << 16);
+    return plain;
+}
+
+// sum and maximum over the block in one exchange, the same order on every block
 template <int WARPS>
-__device__ __forceinline__ void build_activation(const StackStage &S, uint8_t *xp_smem, float *xsum_smem, float *inv_smem,
-                                                 float *red) {
+__device__ __forceinline__ void block_sum_max(float &sum, uint32_t &mx, float *red) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31u) == 0) {
+        red[threadIdx.x >> 5] = sum;
+        reinterpret_cast<uint32_t *>(red)[32 + (threadIdx.x >> 5)] = mx;
+    }
+    __syncthreads();
+    float total = 0.f;
+    uint32_t top = 0;
+#pragma unroll
+    for (int i = 0; i < WARPS; ++i) {
+        total += red[i];
+        top = max(top, reinterpret_cast<uint32_t *>(red)[32 + i]);
+    }
+    sum = total;
+    mx = top;
+}
+
+// The hidden vector as the gate/up epilogue left it: bf16 values and their maximum magnitude. No reduction, no
+// transcendental: 2 bytes per input.
+template <int WARPS>
+__device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &X) {
     constexpr uint32_t T = WARPS * 32;
-    const uint32_t k = S.gemv.k, kp = S.gemv.kp;
-    const uint32_t blocks = k / 8, blocks_p = kp / 8;
+    const uint32_t blocks = P.k / 8, blocks_p = P.kp / 8;
+    const uint32_t amax = __ldcg(static_cast<const unsigned int *>(P.src1));
+    const int e = scale_exponent(amax);
+    const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
+    if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
+    const uint16_t *h = static_cast<const uint16_t *>(P.src0);
+    for (uint32_t b0 = (threadIdx.x & ~31u); b0 < blocks_p; b0 += T) {
+        const uint32_t b = b0 + (threadIdx.x & 31u);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (b < blocks) {
+            raw = __ldcg(reinterpret_cast<const uint4 *>(h + (size_t)b * 8));
+            const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
+                v[2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
+            }
+        }
+        emit_block(v, scale, b, b < blocks_p, X);
+        if (blockIdx.x == 0 && P.x_bf16_out && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = raw;
+    }
+    __syncthreads();
+}
+
+// bf16 vector | bf16(silu(gate)*up) of two fp32 vectors | weightless RMS-norm of an fp32 vector given as the sum of
+// src_parts vectors. Values are held in registers between the reduction and the conversion.
+template <int WARPS>
+__device__ __forceinline__ void rebuild_general(const StackPhase &P, const XBuf &X, float *red) {
+    constexpr uint32_t T = WARPS * 32;
+    const uint32_t k = P.k;
+    const uint32_t blocks = k / 8, blocks_p = P.kp / 8;
     float v[kStackMaxIters][8];
     float ss = 0.f;
+    uint32_t amax = 0;
 #pragma unroll
     for (int it = 0; it < kStackMaxIters; ++it) {
         const uint32_t b = threadIdx.x + it * T;
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[it][i] = 0.f;
+        if (it * T >= blocks_p) continue;  // (uniform) nothing left for any thread
         if (b < blocks) {
-            if (S.x_kind == 0) {
-                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(S.src0) + b * 8));
+            if (P.x_kind == kRebuildBf16) {
+                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(P.src0) + (size_t)b * 8));
                 const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     v[it][2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
                     v[it][2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
                 }
-            } else {
-                const float4 *p0 = reinterpret_cast<const float4 *>(static_cast<const float *>(S.src0) + b * 8);
-                const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1);
+            } else if (P.x_kind == kRebuildSwiglu) {
+                const float4 *p0 = reinterpret_cast<const float4 *>(static_cast<const float *>(P.src0) + (size_t)b * 8);
+                const float4 *p1 = reinterpret_cast<const float4 *>(static_cast<const float *>(P.src1) + (size_t)b * 8);
+                const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1), u0 = __ldcg(p1), u1 = __ldcg(p1 + 1);
                 const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                if (S.x_kind == 1) {
-                    const float4 *p1 = reinterpret_cast<const float4 *>(static_cast<const float *>(S.src1) + b * 8);
-                    const float4 u0 = __ldcg(p1), u1 = __ldcg(p1 + 1);
-                    const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        // qwen38_swiglu_rows with the hardware exponential and reciprocal (as Metal's fast math does): every
-                        // block evaluates all of it, so the full-precision forms were most of this stage's rebuild time;
-                        // the result is rounded to bf16 right away
-                        const float h = __fdividef(a[i], 1.0f + __expf(-a[i])) * u[i];
-                        v[it][i] = bf16_bits_to_float(float_to_bf16_bits(h));
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        v[it][i] = a[i];
-                        ss += a[i] * a[i];
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    const float h = (a[i] * (1.0f / (1.0f + expf(-a[i])))) * u[i];  // qwen38_swiglu_rows
+                    v[it][i] = bf16_bits_to_float(float_to_bf16_bits(h));
                 }
+            } else {
+                for (uint32_t part = 0; part < P.src_parts; ++part) {
+                    const float4 *p0 = reinterpret_cast<const float4 *>(
+                        reinterpret_cast<const uint8_t *>(P.src0) + (size_t)part * P.src_part_stride + (size_t)b * 32);
+                    const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1);
+                    v[it][0] += a0.x; v[it][1] += a0.y; v[it][2] += a0.z; v[it][3] += a0.w;
+                    v[it][4] += a1.x; v[it][5] += a1.y; v[it][6] += a1.z; v[it][7] += a1.w;
+                }
+                if (blockIdx.x == 0 && P.sum_out) {
+                    float4 *dst = reinterpret_cast<float4 *>(P.sum_out + (size_t)b * 8);
+                    dst[0] = make_float4(v[it][0], v[it][1], v[it][2], v[it][3]);
+                    dst[1] = make_float4(v[it][4], v[it][5], v[it][6], v[it][7]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss += v[it][i] * v[it][i];
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = max(amax, __float_as_uint(v[it][i]) & 0x7fffffffu);
         }
     }
-    if (S.x_kind == 2) {
-        const float inv = rsqrtf(block_sum<WARPS>(ss, red) / (float)k + S.eps);
+    block_sum_max<WARPS>(ss, amax, red);
+    if (P.x_kind == kRebuildRms) {
+        const float inv = rsqrtf(ss / (float)k + P.eps);
+        // rounding is monotonic, so the largest rounded magnitude is the rounded largest magnitude
+        amax = float_to_bf16_bits(__uint_as_float(amax) * inv) << 16;
 #pragma unroll
-        for (int it = 0; it < kStackMaxIters; ++it)
+        for (int it = 0; it < kStackMaxIters; ++it) {
+            if (it * T >= blocks_p) continue;
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[it][i] = bf16_bits_to_float(float_to_bf16_bits(v[it][i] * inv));
+        }
     }
-    uint32_t amax = 0;
-#pragma unroll
-    for (int it = 0; it < kStackMaxIters; ++it)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = max(amax, __float_as_uint(v[it][i]) & 0x7fffffffu);
-    amax = block_max_u32<WARPS>(amax, reinterpret_cast<uint32_t *>(red));
-    int e = 14 - ((int)((amax >> 23) & 0xffu) - 127);
-    e = amax == 0 ? 0 : max(-100, min(100, e));
+    const int e = scale_exponent(amax);
     const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
-    if (threadIdx.x == 0) *inv_smem = __uint_as_float((uint32_t)(127 - e) << 23);
+    if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
 #pragma unroll
     for (int it = 0; it < kStackMaxIters; ++it) {
         const uint32_t b = threadIdx.x + it * T;
-        uint32_t bits[8];
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const __half h = __float2half_rn(v[it][i] * scale);
-            bits[i] = (uint32_t)__half_as_ushort(h);
-            sum += __half2float(h);
-        }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if (b < blocks_p) {
-            uint4 out;
-            out.x = bits[0] | (bits[4] << 16);
-            out.y = bits[1] | (bits[5] << 16);
-            out.z = bits[2] | (bits[6] << 16);
-            out.w = bits[3] | (bits[7] << 16);
-            *reinterpret_cast<uint4 *>(xp_smem + b * 16) = out;
-            if ((threadIdx.x & 7u) == 0) xsum_smem[b / 8] = sum;
-            if (blockIdx.x == 0 && S.x_bf16_out && b < blocks) {
-                uint4 plain;
-                uint32_t bb[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) bb[i] = float_to_bf16_bits(v[it][i]);
-                plain.x = bb[0] | (bb[1] << 16);
-                plain.y = bb[2] | (bb[3] << 16);
-                plain.z = bb[4] | (bb[5] << 16);
-                plain.w = bb[6] | (bb[7] << 16);
-                *reinterpret_cast<uint4 *>(S.x_bf16_out + b * 8) = plain;
-            }
-        }
+        if (it * T >= blocks_p) continue;
+        emit_block(v[it], scale, b, b < blocks_p, X);
+        if (blockIdx.x == 0 && P.x_bf16_out && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = pack_bf16x8(v[it]);
     }
     __syncthreads();
 }
 
-// One contiguous run of chunks of one tile, as seen by one lane.
+// ---------------------------------------------------------------------------------------------------------
+// Work: one contiguous run of chunks of one tile, as seen by one lane.
+// ---------------------------------------------------------------------------------------------------------
 struct Segment {
-    uint32_t tile, c0, c1, cbase, job_index;
-    uint32_t c0v, c1v;               // the run in the job's virtual chunk numbering (c0, c1 are clamped to real chunks)
-    uint32_t mis_w, mis_s, mis_b;   // byte misalignment (address & 15) of the job's three tensors
-    uint32_t pmis;                   // misalignment of the parameter array this lane copies
-    const uint8_t *wa, *wb, *pp;     // cursors at chunk cbase (weights: this lane's aligned window)
+    uint32_t job;                   // index into the chain's job array
+    uint32_t tile_local, tile_row;  // tile within the job, its first side-a row
+    uint32_t c0, c1, cbase;         // real chunks [c0, c1); cbase = c0 rounded down to four
+    uint32_t c0v, c1v;              // the run in the job's virtual chunk numbering
+    uint32_t mis_wa, mis_wb;        // byte misalignment (address & 15) of the two sides' weights
+    uint32_t mis_p;                 // and of their scale / bias arrays, four bits each: scales a, scales b, biases a, biases b
+    uint32_t pmis;                  // misalignment of the parameter row this lane copies
+    const uint8_t *wa, *wb, *pp;    // cursors at chunk cbase (this lane's aligned window)
 };
 
-__device__ __forceinline__ void segment_setup(const GemvParams &P, uint64_t u, uint64_t u1, uint32_t &job_index, uint32_t lane,
-                                              Segment &sg) {
+__device__ __forceinline__ void segment_setup(const StackPhase &P, const StackJob *jobs, uint32_t u, uint32_t u1, uint32_t &job_rel,
+                                              uint32_t lane, Segment &sg) {
     const uint32_t g = lane >> 2, t = lane & 3u, cpt = P.cpt;
-    while (job_index + 1 < P.n_jobs && u >= P.jobs[job_index + 1].unit_begin) ++job_index;
-    sg.job_index = job_index;
-    const GemvJob &job = P.jobs[job_index];
-    const uint32_t rel = (uint32_t)(u - job.unit_begin), vcpt = job.vcpt;
-    const uint32_t tile_local = rel / vcpt;
-    sg.tile = job.tile_begin + tile_local;
-    sg.c0v = rel - tile_local * vcpt;
-    const uint64_t left = u1 - u;
-    sg.c1v = (left < (uint64_t)(vcpt - sg.c0v)) ? sg.c0v + (uint32_t)left : vcpt;
+    while (job_rel + 1 < P.n_jobs && u >= jobs[P.job_begin + job_rel + 1].unit_begin) ++job_rel;
+    sg.job = P.job_begin + job_rel;
+    const StackJob &J = jobs[sg.job];
+    const uint32_t rel = u - J.unit_begin, vcpt = J.vcpt;
+    sg.tile_local = rel / vcpt;
+    sg.tile_row = sg.tile_local * J.rows_per_tile;
+    sg.c0v = rel - sg.tile_local * vcpt;
+    const uint32_t left = u1 - u;
+    sg.c1v = (left < vcpt - sg.c0v) ? sg.c0v + left : vcpt;
     sg.c0 = sg.c0v < cpt ? sg.c0v : cpt;
     sg.c1 = sg.c1v < cpt ? sg.c1v : cpt;
     sg.cbase = sg.c0 & ~3u;
-    sg.mis_w = job.w_misalign;
-    sg.mis_s = (uint32_t)((uintptr_t)job.s & 15u);
-    sg.mis_b = (uint32_t)((uintptr_t)job.b & 15u);
-    const uint32_t row0 = (sg.tile - job.tile_begin) * 16u, prow = lane & 15u;
-    uint32_t row_a = row0 + g, row_b = row0 + g + 8u, row_p = row0 + prow;
-    row_a = row_a < job.n ? row_a : job.n - 1u;  // rows past N read a valid row and are never stored
-    row_b = row_b < job.n ? row_b : job.n - 1u;
-    row_p = row_p < job.n ? row_p : job.n - 1u;
-    const uint64_t row_bytes = (uint64_t)P.k >> 1;
-    sg.wa = job.w + (uint64_t)row_a * row_bytes + t * 16u + sg.cbase * 64u - sg.mis_w;
-    sg.wb = job.w + (uint64_t)row_b * row_bytes + t * 16u + sg.cbase * 64u - sg.mis_w;
-    const bool is_bias = (lane >> 4) != 0;
-    sg.pmis = is_bias ? sg.mis_b : sg.mis_s;
-    sg.pp = (is_bias ? job.b : job.s) + ((uint64_t)row_p * P.groups) * 2u + sg.cbase * 4u - sg.pmis;
+    sg.mis_wa = (uint32_t)((uintptr_t)J.w[0] & 15u);
+    sg.mis_wb = (uint32_t)((uintptr_t)J.w[1] & 15u);
+    sg.mis_p = (uint32_t)((uintptr_t)J.s[0] & 15u) | ((uint32_t)((uintptr_t)J.s[1] & 15u) << 4) |
+               ((uint32_t)((uintptr_t)J.b[0] & 15u) << 8) | ((uint32_t)((uintptr_t)J.b[1] & 15u) << 12);
+    const uint32_t last = J.n - 1u;
+    uint32_t row_a = sg.tile_row + g, row_b = sg.tile_row + g + J.b_row_offset;
+    row_a = row_a < last ? row_a : last;  // rows past N read a valid row and are never stored
+    row_b = row_b < last ? row_b : last;
+    sg.wa = J.w[0] + (uint64_t)row_a * J.w_stride + t * 16u + sg.cbase * 64u - sg.mis_wa;
+    sg.wb = J.w[1] + (uint64_t)row_b * J.w_stride + t * 16u + sg.cbase * 64u - sg.mis_wb;
+    // parameter copies: lane l moves 16 bytes of tile row (l & 15) of array (l >> 4: scales, biases)
+    const uint32_t prow = lane & 15u, side = prow >> 3;
+    uint32_t row_p = sg.tile_row + (prow & 7u) + (side ? J.b_row_offset : 0u);
+    row_p = row_p < last ? row_p : last;
+    const uint8_t *pbase = (lane >> 4) ? J.b[side] : J.s[side];
+    sg.pmis = (uint32_t)((uintptr_t)pbase & 15u);
+    sg.pp = pbase + (uint64_t)row_p * J.p_stride + sg.cbase * 4u - sg.pmis;
 }
 
 // Async copies of the first two groups of four chunks. With misaligned weights the chunk after the segment is
 // copied as well: the last lane of a quad completes its 16 bytes from the next chunk's first window.
 __device__ __forceinline__ void segment_prologue(const Segment &sg, uint32_t ring, uint32_t pring, uint32_t lane) {
-    const uint32_t wend = sg.c1 + ((sg.mis_w && sg.c1 > sg.c0) ? 1u : 0u);
+    const uint32_t live = sg.c1 > sg.c0 ? 1u : 0u;
+    const uint32_t wend_a = sg.c1 + (sg.mis_wa ? live : 0u), wend_b = sg.c1 + (sg.mis_wb ? live : 0u);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
             const uint32_t c = sg.cbase + 4 * h + s;
             const uint32_t stage = ring + (4 * h + s) * kStageBytesAligned + lane * 16u;
-            const bool in = c >= sg.c0 && c < wend;
-            cp_async_16_pred(stage, sg.wa + (4 * h + s) * 64, in);
-            cp_async_16_pred(stage + 512u, sg.wb + (4 * h + s) * 64, in);
+            cp_async_16_pred(stage, sg.wa + (4 * h + s) * 64, c >= sg.c0 && c < wend_a);
+            cp_async_16_pred(stage + 512u, sg.wb + (4 * h + s) * 64, c >= sg.c0 && c < wend_b);
         }
         const bool pin = sg.cbase + 4 * h < sg.c1;
         cp_async_16_pred(pring + h * 1024u + lane * 16u, sg.pp + h * 16, pin);
@@ -326,69 +420,254 @@ __device__ __forceinline__ void segment_prologue(const Segment &sg, uint32_t rin
     }
 }
 
+// What is needed to finish a tile after the lane's cursors have moved on to the next run of chunks.
+struct TileEnd {
+    uint32_t job, tile_local, tile_row, c0v, c1v;
+};
+
+// End of a tile for one activation row. A lane holds two sums: side a (tile row g) and side b. A whole tile is stored
+// at once. A tile split between warps is owned by the warp that computed its first chunks (the last thing that warp
+// does in the phase, while the other contributors met the tile at the start of their ranges): every other contributor
+// posts its sums in its partial slot as 8-byte {value, tag} words -- value and tag travel in one store, so no fence and
+// no counter are needed -- and the owner adds them to its own in worker order once their tags show this launch and
+// phase. The wait for a late contributor is bounded. Returns true when this warp stored into other GPUs' memory.
+__device__ __forceinline__ bool finish_tile_m1(const StackParams &sp, const StackPhase &P, const StackJob &J, uint32_t worker,
+                                               const TileEnd &te, float acc_a, float acc_b, float inv, uint32_t tag,
+                                               uint32_t *amax_smem, uint32_t lane, uint32_t g, uint32_t t) {
+    const bool whole = te.c0v == 0 && te.c1v == J.vcpt;
+    if (!whole) {
+        const Q4Split split{P.units, P.cpt, P.workers};
+        const uint64_t u0 = (uint64_t)J.unit_begin + (uint64_t)te.tile_local * J.vcpt;
+        uint32_t first, last;
+        q4_split_span_contributors(split, u0, J.vcpt, &first, &last);
+        uint4 *slots = sp.partials + (size_t)P.slot_set * sp.max_workers * 32u;
+        if (worker != first) {
+            uint4 *dst = slots + (size_t)worker * 32u + lane;
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(acc_a)), "r"(tag),
+                         "r"(__float_as_uint(acc_b)), "r"(tag)
+                         : "memory");
+            return false;
+        }
+        // the other contributors' sums, four slots at a time (independent loads in flight), added in worker order
+        for (uint32_t w0 = first + 1; w0 <= last; w0 += 4) {
+            uint4 pv[4];
+            uint32_t spins = 0;
+            while (true) {
+                bool ok = true;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t w = w0 + i <= last ? w0 + i : last;
+                    const uint4 *src = slots + (size_t)w * 32u + lane;
+                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(pv[i].x), "=r"(pv[i].y), "=r"(pv[i].z), "=r"(pv[i].w) : "l"(src) : "memory");
+                    ok = ok && pv[i].y == tag && pv[i].w == tag;
+                }
+                if (__all_sync(0xffffffffu, ok)) break;
+                if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
+                    *sp.error_flag = 1;  // the next barrier wait of every block sees it and leaves
+                    return false;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (w0 + i <= last) {
+                    acc_a += __uint_as_float(pv[i].x);
+                    acc_b += __uint_as_float(pv[i].z);
+                }
+            }
+        }
+    }
+    // a row's sum is spread over the four lanes of its quad: digits (0,1) and digit 2 of group A in lanes 0 and 1,
+    // those of group B in lanes 2 and 3
+    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
+    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+    const float ya = (acc_a + __shfl_xor_sync(0xffffffffu, acc_a, 2)) * inv;  // inv is a power of two: exact
+    const float yb = (acc_b + __shfl_xor_sync(0xffffffffu, acc_b, 2)) * inv;
+    const uint32_t row_a = te.tile_row + g, row_b = row_a + J.b_row_offset;
+    if (J.pair) {
+        const bool valid = t == 0 && row_a < J.n;
+        const float h = (ya * (1.0f / (1.0f + expf(-ya)))) * yb;  // qwen38_swiglu_rows, shaders/qwen38.metal:4188-4198
+        const uint32_t hb = float_to_bf16_bits(h);
+        const uint32_t mag = __reduce_max_sync(0xffffffffu, valid ? ((hb << 16) & 0x7fffffffu) : 0u);
+        if (valid) {
+            J.h_out[row_a] = (uint16_t)hb;
+            if (J.out[0]) J.out[0][row_a] = ya;
+            if (J.out[1]) J.out[1][row_a] = yb;
+        }
+        // the block's maximum goes to device memory once, with the block's arrival: thousands of tiles adding to one
+        // word would queue up behind each other
+        if (lane == 0) atomicMax(amax_smem, mag);
+        return false;
+    }
+    if (t != 0) return J.has_peers != 0;
+    if (row_a < J.n) J.out[0][row_a] = ya;
+    if (row_b < J.n) J.out[0][row_b] = yb;
+    if (J.has_peers) {
+        // the other ranks' copies of this output (peer stores over NVLink)
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            float *peer = J.peer_out[r];
+            if (peer) {
+                if (row_a < J.n) peer[row_a] = ya;
+                if (row_b < J.n) peer[row_b] = yb;
+            }
+        }
+    }
+    return J.has_peers != 0;
+}
+
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One chunk on the integer tensor-core path: d = sum over the chunk of q * digit for rows g (d[0], d[1]) and g+8 (d[2],
+// d[3]) and the lane's two result columns. A packed word becomes two byte registers with three logic instructions
+// (even nibbles: w & 0x0f0f0f0f, odd nibbles: (w >> 4) & 0x0f0f0f0f); the products are exact integers.
+__device__ __forceinline__ void chunk_mma_i8(const uint4 &cwa, const uint4 &cwb, const uint4 (&xr)[2], int (&d)[4]) {
+    const uint32_t wa[4] = {cwa.x, cwa.y, cwa.z, cwa.w}, wb[4] = {cwb.x, cwb.y, cwb.z, cwb.w};
+    const uint32_t m = 0x0f0f0f0fu;
+    uint32_t la[4], ha[4], lb[4], hb[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        la[w] = wa[w] & m;
+        ha[w] = (wa[w] >> 4) & m;
+        lb[w] = wb[w] & m;
+        hb[w] = (wb[w] >> 4) & m;
+    }
+    d[0] = d[1] = d[2] = d[3] = 0;
+    mma_u8s8_16832(d, la[0], lb[0], la[1], lb[1], xr[0].x, xr[0].y);
+    mma_u8s8_16832(d, ha[0], hb[0], ha[1], hb[1], xr[0].z, xr[0].w);
+    mma_u8s8_16832(d, la[2], lb[2], la[3], lb[3], xr[1].x, xr[1].y);
+    mma_u8s8_16832(d, ha[2], hb[2], ha[3], hb[3], xr[1].z, xr[1].w);
+}
+
+// exact for |i| < 2^22
+__device__ __forceinline__ float small_int_to_float(int i) { return __int_as_float(i + 0x4B400000) - 12582912.0f; }
+
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_constant__ StackParams sp) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t worker = blockIdx.x * WARPS + warp;
-    uint8_t *xp_smem = smem + WARPS * kStackRingBytes;
-    float *xsum_smem = reinterpret_cast<float *>(xp_smem + sp.x_halfs * 2);
-    float *inv_smem = xsum_smem + sp.x_halfs / 64;
-    float *red = inv_smem + 4;
+    // shared memory: per-warp rings | activation buffer 0 | activation buffer 1 | group sums 0 | group sums 1 | misc
+    uint8_t *xp0 = smem + WARPS * kStackRingBytes;
+    uint8_t *xp1 = xp0 + sp.halfs[0] * 3 + kXSlack;
+    float *xsum0 = reinterpret_cast<float *>(xp1 + sp.halfs[1] * 3 + kXSlack);
+    float *xsum1 = xsum0 + sp.halfs[0] / 64 + 4;
+    float *misc = xsum1 + sp.halfs[1] / 64 + 4;
+    uint32_t *arrive_smem = reinterpret_cast<uint32_t *>(misc + 2);
+    uint32_t *amax_smem = reinterpret_cast<uint32_t *>(misc + 70);
+    float *red = misc + 4;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * kStackRingBytes;
     const uint32_t pring = ring + kStages * kStageBytesAligned;
-    const uint32_t xp_addr = (uint32_t)__cvta_generic_to_shared(xp_smem) + t * 64u;
-    const uint32_t xsum_addr = (uint32_t)__cvta_generic_to_shared(xsum_smem) + (t >> 1) * 4u;
-    // one activation row: MMA column 0 carries group A (lanes g==0, t<2), column 4 group B (lanes g==4, t>=2)
-    const bool has_x = (g == 0 && t < 2u) || (g == 4 && t >= 2u);
-    const bool has_sum = (t & 1u) == 0;  // lanes whose MMA result columns include column 0 / 4
+    // One activation row as three digit columns per affine group: MMA columns 0,1,2 carry the digits of group A (fed by
+    // lanes g = 0,1,2 with t < 2, which hold group A's k slots), columns 4,5,6 those of group B (lanes g = 4,5,6, t >= 2);
+    // every other B lane supplies zeros. A lane's results are columns 2t and 2t+1.
+    const bool has_x = (g & 3u) < 3u && ((g < 4u) == (t < 2u));
+    const bool has_sum = (t & 1u) == 0;  // lanes whose result columns include digit 0 of a group (column 0 / 4)
     const uint32_t half_sel = (t >> 1) ? 0x3244u : 0x1044u;
-    const Magic mg = make_magic();
-    uint4 xf[2][1][4];
+    uint4 xf[2][2];  // B registers of the chunk in use and the next one
 #pragma unroll
-    for (int b = 0; b < 2; ++b)
-#pragma unroll
-        for (int w = 0; w < 4; ++w) xf[b][0][w] = make_uint4(0, 0, 0, 0);
+    for (int b = 0; b < 2; ++b) xf[b][0] = xf[b][1] = make_uint4(0, 0, 0, 0);
 
-    uint32_t generation = sp.peers ? sp.epoch : 0;
+    unsigned long long *gbase_smem = reinterpret_cast<unsigned long long *>(misc + 68);
+    SyncState sync{0u, 0u, gbase_smem};
+    if (threadIdx.x == 0) {
+        *arrive_smem = 0;
+        *amax_smem = 0;
+        *gbase_smem = sp.peers ? *reinterpret_cast<volatile unsigned long long *>(sp.peers->consumed) : 0ull;
+        reinterpret_cast<uint32_t *>(misc)[3] = *reinterpret_cast<volatile unsigned int *>(sp.launch_seq);
+    }
+    __syncthreads();
+    // tags of the split-tile partial slots: unique per launch and phase, never zero
+    const uint32_t tag_base = reinterpret_cast<uint32_t *>(misc)[3] * kMaxPhases + 1u;
+
     bool prefetched = false;
     Segment sg;
-    uint32_t job_index = 0;
+    uint32_t job_rel = 0;
 
-    for (uint32_t st = 0; st < sp.n_stages; ++st) {
-        const StackStage &S = sp.stages[st];
-        const GemvParams &P = S.gemv;
-        unsigned long long *tr = sp.trace ? sp.trace + ((size_t)blockIdx.x * sp.n_stages + st) * 4 : nullptr;
-        if (tr && threadIdx.x == 0) tr[0] = stack_ns();
-        build_activation<WARPS>(S, xp_smem, xsum_smem, inv_smem, red);
-        if (tr && threadIdx.x == 0) tr[1] = stack_ns();
+    for (uint32_t ph = 0; ph < sp.n_phases; ++ph) {
+        const StackPhase &P = sp.phases[ph];
+        // trace slot of this block and phase for lane 0 of any warp, null otherwise
+        auto trace_slot = [&]() -> unsigned long long * {
+            return (sp.trace && lane == 0) ? sp.trace + ((size_t)blockIdx.x * sp.n_phases + ph) * kTraceStamps : nullptr;
+        };
+        const bool second = P.x_buf != 0;
+        const XBuf X{second ? xp1 : xp0, second ? xsum1 : xsum0, misc + (second ? 1 : 0)};
+        // descriptors of the phase after this one: bring them into L2 while this one runs
+        if (warp == 1 && ph + 2 < sp.n_phases) {
+            const StackPhase &N = sp.phases[ph + 2];
+            if (lane == 0) prefetch_l2(&N);
+            const uint32_t lines = (N.n_jobs * (uint32_t)sizeof(StackJob) + 127u) / 128u;
+            if (lane >= 1 && lane <= lines) prefetch_l2(reinterpret_cast<const uint8_t *>(sp.jobs + N.job_begin) + (lane - 1u) * 128u);
+        }
+        if (P.wait_kind != kSyncNone || P.x_kind != kRebuildNone) {
+            if (sp.trace && threadIdx.x == 0) trace_slot()[0] = stack_ns();
+            if (P.wait_kind != kSyncNone) {
+                if (!phase_wait(sp, P.wait_kind, sync)) return;
+            } else {
+                __syncthreads();  // everyone is done with the buffer that is about to be rewritten
+            }
+            if (sp.trace && threadIdx.x == 0) trace_slot()[1] = stack_ns();
+            if (P.x_kind == kRebuildH) rebuild_from_h<WARPS>(P, X);
+            else if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(P, X, red);
+            if (sp.trace && threadIdx.x == 0) trace_slot()[2] = stack_ns();
+        }
 
+        bool stored_to_peers = false;
+        uint32_t dbg_i = 0;
+        uint32_t u = 0, u1 = 0;  // this warp's units of the phase (a phase has fewer than 2^32)
         if (worker < P.workers) {
             const Q4Split split{P.units, P.cpt, P.workers};
-            uint64_t u = q4_split_begin(split, worker);
-            const uint64_t u1 = q4_split_begin(split, worker + 1);
-            bool first = true;
-            if (!prefetched) job_index = 0;
-            while (u < u1) {
-                if (!(first && prefetched)) {
-                    segment_setup(P, u, u1, job_index, lane, sg);
-                    segment_prologue(sg, ring, pring, lane);
+            u = (uint32_t)q4_split_begin(split, worker);
+            u1 = (uint32_t)q4_split_begin(split, worker + 1);
+        }
+        bool more = u < u1;
+        if (more && !prefetched) {
+            job_rel = 0;
+            segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
+            segment_prologue(sg, ring, pring, lane);
+        }
+        // weights of the next phase's first run of chunks: they depend on nothing, so they are requested as soon as the
+        // ring is free -- before this phase's last tile is finished and before any barrier
+        auto request_next_phase = [&]() {
+            prefetched = false;
+            if (ph + 1 < sp.n_phases) {
+                const StackPhase &N = sp.phases[ph + 1];
+                if (worker < N.workers) {
+                    const Q4Split nsplit{N.units, N.cpt, N.workers};
+                    const uint32_t nu = (uint32_t)q4_split_begin(nsplit, worker), nu1 = (uint32_t)q4_split_begin(nsplit, worker + 1);
+                    if (nu < nu1) {
+                        job_rel = 0;
+                        segment_setup(N, sp.jobs, nu, nu1, job_rel, lane, sg);
+                        segment_prologue(sg, ring, pring, lane);
+                        prefetched = true;
+                    }
                 }
-                first = false;
+            }
+        };
+        if (!more) request_next_phase();
+        const uint32_t xp_addr = (uint32_t)__cvta_generic_to_shared(X.xp) + (g & 3u) * 128u + t * 32u;
+        const uint32_t xsum_addr = (uint32_t)__cvta_generic_to_shared(X.xsum) + (t >> 1) * 4u;
+        while (more) {
+            {
                 const uint32_t c0 = sg.c0, c1 = sg.c1;
-                const uint32_t mis_w = sg.mis_w, mis_s = sg.mis_s, mis_b = sg.mis_b;
-                const uint32_t wend = c1 + ((mis_w && c1 > c0) ? 1u : 0u);
+                const uint32_t mis_wa = sg.mis_wa, mis_wb = sg.mis_wb;
+                const bool mis_any = (mis_wa | mis_wb) != 0;
+                const uint32_t live = c1 > c0 ? 1u : 0u;
+                const uint32_t wend_a = c1 + (mis_wa ? live : 0u), wend_b = c1 + (mis_wb ? live : 0u);
                 const uint8_t *wa = sg.wa, *wb = sg.wb, *pp = sg.pp;
-                uint32_t xa = xp_addr + sg.cbase * 256u;           // this lane's fragment of chunk cbase
-                uint32_t xs = xsum_addr + sg.cbase * 8u;           // group sum of this lane's group in chunk cbase
-                float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+                uint32_t xa = xp_addr + sg.cbase * kXChunkBytes;  // this lane's fragment of chunk cbase
+                uint32_t xs = xsum_addr + sg.cbase * 8u;  // group sum of this lane's group in chunk cbase
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 if (c0 & 1u) {
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) lds_v4_keep(xf[1][0][w], xa + (c0 - sg.cbase) * 256u + w * 16u, has_x);
+                    lds_v4_keep(xf[1][0], xa + (c0 - sg.cbase) * kXChunkBytes, has_x);
+                    lds_v4_keep(xf[1][1], xa + (c0 - sg.cbase) * kXChunkBytes + 16u, has_x);
                 } else {
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) lds_v4_keep(xf[0][0][w], xa + (c0 - sg.cbase) * 256u + w * 16u, has_x);
+                    lds_v4_keep(xf[0][0], xa + (c0 - sg.cbase) * kXChunkBytes, has_x);
+                    lds_v4_keep(xf[0][1], xa + (c0 - sg.cbase) * kXChunkBytes + 16u, has_x);
                 }
 
                 uint32_t half = 0;
@@ -396,17 +675,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                     const uint32_t stage0 = ring + half * (4 * kStageBytesAligned) + lane * 16u;
                     const uint32_t other0 = ring + (half ^ 1u) * (4 * kStageBytesAligned) + lane * 16u;
                     const uint32_t pstage = pring + half * 1024u;
+                    if (sp.dbg && ph == sp.dbg_phase && lane == 0 && dbg_i < 30) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 2 * dbg_i] = stack_ns();
                     cp_async_wait<1>();  // this half's group has landed; the other half's may be pending
                     __syncwarp();        // parameters (and neighbouring weight windows) were copied by other lanes
+                    if (sp.dbg && ph == sp.dbg_phase && lane == 0 && dbg_i < 30) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 2 * dbg_i++ + 1] = stack_ns();
                     uint4 psa = lds_v4(pstage + g * 16u), psb = lds_v4(pstage + (g + 8u) * 16u);
                     uint4 pba = lds_v4(pstage + 256u + g * 16u), pbb = lds_v4(pstage + 256u + (g + 8u) * 16u);
-                    if (mis_s) {
-                        psa = realign_16(psa, lds_v4(pstage + 512u + g * 16u), mis_s);
-                        psb = realign_16(psb, lds_v4(pstage + 512u + (g + 8u) * 16u), mis_s);
-                    }
-                    if (mis_b) {
-                        pba = realign_16(pba, lds_v4(pstage + 768u + g * 16u), mis_b);
-                        pbb = realign_16(pbb, lds_v4(pstage + 768u + (g + 8u) * 16u), mis_b);
+                    if (sg.mis_p) {
+                        const uint32_t mp = sg.mis_p;
+                        if (mp & 0x000fu) psa = realign_16(psa, lds_v4(pstage + 512u + g * 16u), mp & 15u);
+                        if (mp & 0x00f0u) psb = realign_16(psb, lds_v4(pstage + 512u + (g + 8u) * 16u), (mp >> 4) & 15u);
+                        if (mp & 0x0f00u) pba = realign_16(pba, lds_v4(pstage + 768u + g * 16u), (mp >> 8) & 15u);
+                        if (mp & 0xf000u) pbb = realign_16(pbb, lds_v4(pstage + 768u + (g + 8u) * 16u), (mp >> 12) & 15u);
                     }
                     const uint32_t wsa[4] = {psa.x, psa.y, psa.z, psa.w}, wsb[4] = {psb.x, psb.y, psb.z, psb.w};
                     const uint32_t wba[4] = {pba.x, pba.y, pba.z, pba.w}, wbb[4] = {pbb.x, pbb.y, pbb.z, pbb.w};
@@ -417,7 +697,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                             const int b = s & 1;
                             const uint32_t stage = stage0 + s * kStageBytesAligned;
                             uint4 cwa = lds_v4(stage), cwb = lds_v4(stage + 512u);
-                            if (mis_w) {
+                            if (mis_any) {
                                 // the 16 bytes end in the next window: the next lane's slot, or for the quad's last
                                 // lane the first window of the next chunk (next stage; after the fourth chunk of a
                                 // half that is the other half, which must have landed)
@@ -429,27 +709,30 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                                 } else if (t == 3u) {
                                     next = stage + kStageBytesAligned - 48u;
                                 }
-                                cwa = realign_16(cwa, lds_v4(next), mis_w);
-                                cwb = realign_16(cwb, lds_v4(next + 512u), mis_w);
+                                if (mis_wa) cwa = realign_16(cwa, lds_v4(next), mis_wa);
+                                if (mis_wb) cwb = realign_16(cwb, lds_v4(next + 512u), mis_wb);
                             }
-#pragma unroll
-                            for (int w = 0; w < 4; ++w) lds_v4_keep(xf[b ^ 1][0][w], xa + (s + 1) * 256u + w * 16u, has_x);
+                            lds_v4_keep(xf[b ^ 1][0], xa + (s + 1) * kXChunkBytes, has_x);
+                            lds_v4_keep(xf[b ^ 1][1], xa + (s + 1) * kXChunkBytes + 16u, has_x);
                             float xsv = 0.f;
                             lds_f32_keep(xsv, xs + s * 8u, has_sum);
-                            float d[1][4];
-                            chunk_mma<1>(cwa, cwb, xf[b], mg, d);
+                            int d[4];
+                            chunk_mma_i8(cwa, cwb, xf[b], d);
                             const float sa = param_of(wsa[s], half_sel), sb = param_of(wsb[s], half_sel);
                             const float ba = param_of(wba[s], half_sel), bb = param_of(wbb[s], half_sel);
-                            acc[0][0] = fmaf(d[0][0], sa, fmaf(xsv, ba, acc[0][0]));
-                            acc[0][2] = fmaf(d[0][2], sb, fmaf(xsv, bb, acc[0][2]));
+                            // per result column: the digit's integer sum times the group's scale; the bias term rides
+                            // on digit 0 (weight 1)
+                            acc[0] = fmaf(small_int_to_float(d[0]), sa, fmaf(xsv, ba, acc[0]));
+                            acc[1] = fmaf(small_int_to_float(d[1]), sa, acc[1]);
+                            acc[2] = fmaf(small_int_to_float(d[2]), sb, fmaf(xsv, bb, acc[2]));
+                            acc[3] = fmaf(small_int_to_float(d[3]), sb, acc[3]);
                         }
                     }
                     __syncwarp();  // every lane is done with this half before it is refilled
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        const bool more = cg + 8 + s < wend;
-                        cp_async_16_pred(stage0 + s * kStageBytesAligned, wa + (8 + s) * 64, more);
-                        cp_async_16_pred(stage0 + s * kStageBytesAligned + 512u, wb + (8 + s) * 64, more);
+                        cp_async_16_pred(stage0 + s * kStageBytesAligned, wa + (8 + s) * 64, cg + 8 + s < wend_a);
+                        cp_async_16_pred(stage0 + s * kStageBytesAligned + 512u, wb + (8 + s) * 64, cg + 8 + s < wend_b);
                     }
                     cp_async_16_pred(pstage + lane * 16u, pp + 32, cg + 8 < c1);
                     cp_async_16_pred(pstage + 512u + lane * 16u, pp + 48, cg + 8 < c1 && sg.pmis != 0);
@@ -457,46 +740,47 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                     wa += 4 * 64;
                     wb += 4 * 64;
                     pp += 16;
-                    xa += 4 * 256u;
+                    xa += 4 * kXChunkBytes;
                     xs += 4 * 8u;
                     half ^= 1u;
                 }
                 cp_async_wait<0>();
                 __syncwarp();
-                {
-                    const GemvJob &job = P.jobs[sg.job_index];
-                    finish_tile<1>(P, inv_smem, split, worker, sg.tile, sg.c0v == 0 && sg.c1v == job.vcpt, acc, lane, g, t, sg.job_index,
-                                   (uint64_t)job.unit_begin + (uint64_t)(sg.tile - job.tile_begin) * job.vcpt, job.vcpt);
-                }
+                // the ring is free: request the next run of chunks before this tile is finished, so that the finish
+                // (a round trip to the other contributors' slots for a split tile) overlaps the load latency
+                const TileEnd te{sg.job, sg.tile_local, sg.tile_row, sg.c0v, sg.c1v};
                 u += sg.c1v - sg.c0v;
+                more = u < u1;
+                if (more) {
+                    segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
+                    segment_prologue(sg, ring, pring, lane);
+                } else {
+                    request_next_phase();
+                }
+                // digits back together: a lane's columns are digits (0, 1) of its group for even t, (2, none) for odd t
+                const float w0 = (t & 1u) ? 65536.f : 1.f, w1 = (t & 1u) ? 0.f : 256.f;
+                const float part_a = fmaf(acc[1], w1, acc[0] * w0), part_b = fmaf(acc[3], w1, acc[2] * w0);
+                stored_to_peers |= finish_tile_m1(sp, P, sp.jobs[te.job], worker, te, part_a, part_b, *X.inv, tag_base + ph, amax_smem, lane, g, t);
             }
+        }
+        if (sp.trace && threadIdx.x == 0) trace_slot()[3] = stack_ns();
+        if (sp.dbg && ph == sp.dbg_phase && lane == 0) {
+            sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 62] = stack_ns();
+            sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 63] = dbg_i;
         }
 
-        // weights of the next stage's first segment start streaming before the barrier
-        prefetched = false;
-        if (st + 1 < sp.n_stages) {
-            const GemvParams &N = sp.stages[st + 1].gemv;
-            if (worker < N.workers) {
-                const Q4Split nsplit{N.units, N.cpt, N.workers};
-                const uint64_t nu = q4_split_begin(nsplit, worker), nu1 = q4_split_begin(nsplit, worker + 1);
-                if (nu < nu1) {
-                    job_index = 0;
-                    segment_setup(N, nu, nu1, job_index, lane, sg);
-                    segment_prologue(sg, ring, pring, lane);
-                    prefetched = true;
-                }
-            }
+        if (P.arrive_kind != kSyncNone) {
+            const StackJob &J0 = sp.jobs[P.job_begin];
+            phase_arrive<WARPS>(sp, P.arrive_kind, sync, arrive_smem, stored_to_peers, lane, trace_slot(), J0.pair ? J0.amax : nullptr, amax_smem);
+            ++sync.local_gen;
+            if (P.arrive_kind == kSyncGlobal) ++sync.global_gen;
         }
-        if (tr) {
-            __syncthreads();
-            if (threadIdx.x == 0) tr[2] = stack_ns();
-        }
-        if (!grid_barrier(sp.barrier, generation, sp.error_flag, sp.peers)) return;
-        if (tr && threadIdx.x == 0) tr[3] = stack_ns();
     }
 
     // ---- logits -> token: per-block candidates, barrier, block 0 picks (ties to the lowest index) ----
     if (sp.logits) {
+        const uint32_t last_kind = sp.phases[sp.n_phases - 1].arrive_kind;  // the last phase arrived for the logits
+        if (!phase_wait(sp, last_kind, sync)) return;
         const uint32_t per = (sp.vocab + gridDim.x - 1) / gridDim.x;
         const uint32_t lo = blockIdx.x * per, hi = min(sp.vocab, lo + per);
         float bv = -INFINITY;
@@ -522,7 +806,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             sp.part_val[blockIdx.x] = bv;
             sp.part_idx[blockIdx.x] = bi;
         }
-        if (!grid_barrier(sp.barrier, generation, sp.error_flag, sp.peers)) return;
+        phase_arrive<WARPS>(sp, kSyncLocal, sync, arrive_smem, false, lane, nullptr);
+        ++sync.local_gen;
+        if (!phase_wait(sp, kSyncLocal, sync)) return;
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             float fv = -INFINITY;
             uint32_t fi = 0xffffffffu;
@@ -542,7 +828,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             }
         }
         if (sp.peers) {
-            if (!grid_barrier(sp.barrier, generation, sp.error_flag, sp.peers)) return;
+            phase_arrive<WARPS>(sp, kSyncGlobal, sync, arrive_smem, blockIdx.x == 0 && warp == 0, lane, nullptr);
+            ++sync.local_gen;
+            ++sync.global_gen;
+            if (!phase_wait(sp, kSyncGlobal, sync)) return;
             if (blockIdx.x == 0 && threadIdx.x == 0) {
                 float fv = -INFINITY;
                 uint32_t fi = 0xffffffffu;
@@ -556,6 +845,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             }
         }
     }
+    // The launch is over once every block has got here: only then may the words that the next launch reads at its start
+    // change (every block read them before its first arrival).
+    phase_arrive<WARPS>(sp, kSyncLocal, sync, arrive_smem, false, lane, nullptr);
+    ++sync.local_gen;
+    if (blockIdx.x == 0) {
+        if (!phase_wait(sp, kSyncLocal, sync)) return;
+        if (threadIdx.x == 0) {
+            *sp.launch_seq = reinterpret_cast<uint32_t *>(misc)[3] + 1u;
+            if (sp.peers) *sp.peers->consumed = *gbase_smem + (unsigned long long)sync.global_gen * sp.peers->world;
+        }
+    }
 }
 
 }  // namespace q4
@@ -566,44 +866,19 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
 
 namespace {
 constexpr int kStackWarps = 16;
-
-size_t stack_smem_bytes(uint32_t x_halfs) {
-    return (size_t)kStackWarps * q4::kStackRingBytes + (size_t)x_halfs * 2 + (size_t)(x_halfs / 64) * 4 + 16 + 64 * 4 + 128;
-}
 }  // namespace
 
-extern "C" size_t q4k_stack_peers_bytes(void) { return sizeof(q4::StackPeers); }
-extern "C" void q4k_stack_fill_peers(void *image, uint32_t world, uint32_t rank, void *const *flags, void *const *cand) {
-    q4::StackPeers *p = static_cast<q4::StackPeers *>(image);
-    memset(p, 0, sizeof *p);
-    p->world = world;
-    p->rank = rank;
-    p->arrivals_local = static_cast<unsigned long long *>(flags[rank]);
-    p->cand_local = static_cast<float2 *>(cand[rank]);
-    for (uint32_t r = 0; r < world; ++r) {
-        p->arrivals_peer[r] = static_cast<unsigned long long *>(flags[r]);
-        p->cand_peer[r] = static_cast<float2 *>(cand[r]);
-    }
-}
-extern "C" size_t q4k_stack_stage_bytes(void) { return sizeof(q4::StackStage); }
 extern "C" uint32_t q4k_stack_warps(void) { return kStackWarps; }
 extern "C" uint32_t q4k_stack_max_k(void) { return q4::kStackMaxIters * kStackWarps * 32 * 8; }
 
-// Fills one stage image (host memory) for upload; `gemv` carries jobs and shape, workers/partials/counters included.
-extern "C" void q4k_stack_fill_stage(void *stage_image, const q4::GemvParams *gemv, uint32_t x_kind, float eps, const void *src0,
-                                     const void *src1, uint16_t *x_bf16_out) {
-    q4::StackStage *s = static_cast<q4::StackStage *>(stage_image);
-    s->gemv = *gemv;
-    s->x_kind = x_kind;
-    s->eps = eps;
-    s->src0 = src0;
-    s->src1 = src1;
-    s->x_bf16_out = x_bf16_out;
+extern "C" size_t q4k_stack_smem_bytes(uint32_t halfs0, uint32_t halfs1) {
+    return (size_t)kStackWarps * q4::kStackRingBytes + (size_t)(halfs0 + halfs1) * 3 + 2 * q4::kXSlack +
+           (size_t)(halfs0 / 64 + halfs1 / 64 + 8) * 4 + 4 * 4 + 64 * 4 + 32 + 128;
 }
 
-// 0 when the kernel cannot be made resident with one block per SM for this activation size
-extern "C" int q4k_stack_supported(uint32_t x_halfs, int sm_count) {
-    const size_t smem = stack_smem_bytes(x_halfs);
+// 0 when the kernel cannot be made resident with one block per SM for these activation sizes
+extern "C" int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1) {
+    const size_t smem = q4k_stack_smem_bytes(halfs0, halfs1);
     if (cudaFuncSetAttribute(q4::q4_stack_kernel<kStackWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
@@ -613,36 +888,16 @@ extern "C" int q4k_stack_supported(uint32_t x_halfs, int sm_count) {
         cudaGetLastError();
         return 0;
     }
-    (void)sm_count;
     return blocks >= 1 ? 1 : 0;
 }
 
-extern "C" cudaError_t q4k_stack_launch(const void *stages_dev, uint32_t n_stages, uint32_t x_halfs, unsigned int *barrier,
-                                        int *error_flag, const float *logits, uint32_t vocab, uint32_t index_base, float *part_val,
-                                        uint32_t *part_idx, uint32_t *token, float *best, unsigned long long *trace, const void *peers,
-                                        unsigned int epoch, int sm_count, cudaStream_t stream) {
-    q4::StackParams sp;
-    sp.stages = static_cast<const q4::StackStage *>(stages_dev);
-    sp.n_stages = n_stages;
-    sp.x_halfs = x_halfs;
-    sp.barrier = barrier;
-    sp.error_flag = error_flag;
-    sp.logits = logits;
-    sp.vocab = vocab;
-    sp.index_base = index_base;
-    sp.part_val = part_val;
-    sp.part_idx = part_idx;
-    sp.token = token;
-    sp.best = best;
-    sp.trace = trace;
-    sp.peers = static_cast<const q4::StackPeers *>(peers);
-    sp.epoch = epoch;
-    cudaError_t e = cudaSuccess;
-    if (!peers) {  // with peers generations only grow; on one GPU the two words restart at zero
-        e = cudaMemsetAsync(barrier, 0, 8, stream);
-        if (e != cudaSuccess) return e;
-    }
+// `reset_region`: the words that must be zero when the kernel starts (local arrival counter, running maxima).
+extern "C" cudaError_t q4k_stack_launch(const q4::StackParams *params, void *reset_region, size_t reset_bytes, int sm_count,
+                                        cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(reset_region, 0, reset_bytes, stream);
+    if (e != cudaSuccess) return e;
+    q4::StackParams sp = *params;
     void *args[] = {&sp};
     return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(q4::q4_stack_kernel<kStackWarps>), dim3(sm_count), dim3(kStackWarps * 32),
-                                       args, stack_smem_bytes(x_halfs), stream);
+                                       args, q4k_stack_smem_bytes(sp.halfs[0], sp.halfs[1]), stream);
 }

@@ -47,3 +47,19 @@ Q4_HD uint32_t q4_split_slot(const Q4Split &s, uint32_t w, uint32_t tile) {
     uint32_t head_tile = (uint32_t)(q4_split_begin(s, w) / s.cpt);
     return 2u * w + (tile == head_tile ? 0u : 1u);
 }
+
+// Byte-addressed variant of the streaming kernel: which aligned 16-byte windows it asks for. A chunk is 64 packed
+// bytes of a row: lanes t = 0,1 of a quad hold affine group A (bytes 0..31), lanes 2,3 group B (bytes 32..63), and
+// the lane's window is the aligned 16 bytes that start `mis` bytes before its share ([16t - mis, 16t - mis + 16)); a
+// lane completes its 16 bytes from the window after its own, so the quad needs a fifth window when mis != 0. Every
+// window the kernel asks for holds at least one byte of the row, so nothing outside the 16-byte blocks that the
+// tensor itself touches is ever read. `has_b`: group B of this chunk exists (the last chunk of a row with an odd
+// number of groups has only group A).
+Q4_HD bool q4_window_wanted(uint32_t t, uint32_t mis, bool has_b) {
+    if (t < 2u) return true;
+    if (t == 2u) return has_b || mis != 0u;  // its first `mis` bytes complete lane 1's share
+    return has_b;
+}
+Q4_HD bool q4_fifth_window_wanted(uint32_t mis, bool has_b) { return has_b && mis != 0u; }
+// chunks of a row in which lane t (0..3) of a quad has an affine group: group 2*chunk + (t >> 1) < groups
+Q4_HD uint32_t q4_lane_chunks(uint32_t groups, uint32_t t) { return (groups + 1u - (t >> 1)) >> 1; }

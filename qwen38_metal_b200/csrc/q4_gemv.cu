@@ -139,7 +139,6 @@ __global__ void __launch_bounds__(256) q4_prepare_x_kernel(const void *__restric
 template <int NT>
 __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_generic_kernel(const __grid_constant__ GemvParams p) {
     constexpr bool ALIGNED = false;
-    const bool ODD = (p.groups & 1u) != 0;
     extern __shared__ __align__(128) uint8_t ring_bytes[];
     const uint32_t lane = threadIdx.x;
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -159,7 +158,7 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_generic_kernel(
     const float *xs0 = p.xsum + (size_t)(t >> 1) * p.vpad + 2u * (t & 1u);
     const uint32_t xs_step = 2u * p.vpad;
     // chunks whose group exists for this lane: group = 2*chunk + (t>>1) < groups
-    const uint32_t lane_chunks = (groups + 1u - (t >> 1)) >> 1;
+    const uint32_t lane_chunks = q4_lane_chunks(groups, t);
     const Magic mg = make_magic();
     constexpr uint32_t kStageBytes = ALIGNED ? kStageBytesAligned : kStageBytesWindowed;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_bytes);
@@ -205,19 +204,19 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_generic_kernel(
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
-        // prologue: weights of the first kStages chunks, parameters of the first two, activations of the first
+        // prologue: weights of the first kStages chunks, parameters of the first two, activations of the first.
+        // Parameters are only read for chunks of this segment in which the lane has a group: no byte outside the three
+        // tensors' own 16-byte blocks is touched, so caller-supplied tensors need no padding.
+        const uint32_t full_chunks = groups >> 1;  // chunks with both affine groups
+        const uint32_t param_n = live_n < n ? live_n : n;
 #pragma unroll
         for (int i = 0; i < kStages; ++i) {
-            issue_weights<ALIGNED>(ring + i * kStageBytes, wa + i * 64, wb + i * 64, lane, t, (uint32_t)i < n);
+            issue_weights<ALIGNED>(ring + i * kStageBytes, wa + i * 64, wb + i * 64, lane, t, (uint32_t)i < n, mis, c0 + i < full_chunks);
             if (i == 3 || i == 7) cp_async_commit();  // one group per half of the ring
         }
         ParamRegs prm[2];
-        load_params<ALIGNED>(prm[0], sa, sb, ba, bb);
-        load_params<ALIGNED>(prm[1], sa + 4, sb + 4, ba + 4, bb + 4);
-        if (ODD) {
-            if (0 >= live_n) prm[0].sa = prm[0].sb = prm[0].ba = prm[0].bb = 0;
-            if (1 >= live_n) prm[1].sa = prm[1].sb = prm[1].ba = prm[1].bb = 0;
-        }
+        load_params<ALIGNED>(prm[0], sa, sb, ba, bb, 0 < param_n);
+        load_params<ALIGNED>(prm[1], sa + 4, sb + 4, ba + 4, bb + 4, 1 < param_n);
         load_x<NT>(xf[0], xsrc, x_mask, p.kp);
 
         // Four chunks are consumed, then their four stages are refilled in one burst (chunks 8..11 ahead):
@@ -239,17 +238,14 @@ __global__ void __launch_bounds__(32, NT == 1 ? 20 : 16) q4_gemv_generic_kernel(
                     load_x<NT>(xf[b ^ 1], xsrc + (s + 1) * 128, x_mask, p.kp);  // reads past the segment are harmless
                     consume_chunk<NT>(cwa, cwb, bf16_bits_to_float(prm[b].sa), bf16_bits_to_float(prm[b].sb),
                                       bf16_bits_to_float(prm[b].ba), bf16_bits_to_float(prm[b].bb), xf[b], xs + s * xs_step, mg, acc);
-                    load_params<ALIGNED>(prm[b], sa + (s + 2) * 4, sb + (s + 2) * 4, ba + (s + 2) * 4, bb + (s + 2) * 4);
-                    if (ODD) {
-                        if (ci + s + 2 >= live_n) prm[b].sa = prm[b].sb = prm[b].ba = prm[b].bb = 0;
-                    }
+                    load_params<ALIGNED>(prm[b], sa + (s + 2) * 4, sb + (s + 2) * 4, ba + (s + 2) * 4, bb + (s + 2) * 4, ci + s + 2 < param_n);
                 }
             }
             if (!ALIGNED) __syncwarp();  // everyone has read before the stages are refilled
 #pragma unroll
             for (int s = 0; s < 4; ++s)
                 issue_weights<ALIGNED>(stage0 + s * kStageBytes, wa + (s + kStages) * 64, wb + (s + kStages) * 64, lane, t,
-                                       ci + s + kStages < n);
+                                       ci + s + kStages < n, mis, c0 + ci + s + kStages < full_chunks);
             cp_async_commit();
             wa += 4 * 64;
             wb += 4 * 64;

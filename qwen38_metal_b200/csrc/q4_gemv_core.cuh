@@ -28,19 +28,23 @@ struct ParamRegs {
     uint32_t sb, bb;  // same for row g+8
 };
 
+// `mis`: byte misalignment of the weights; `has_b`: the chunk's second affine group exists (byte-addressed variant)
 template <bool ALIGNED>
 __device__ __forceinline__ void issue_weights(uint32_t stage_addr, const uint8_t *wa, const uint8_t *wb, uint32_t lane,
-                                              uint32_t t, bool pred) {
+                                              uint32_t t, bool pred, uint32_t mis = 0, bool has_b = true) {
     if (ALIGNED) {
         cp_async_16_pred(stage_addr + lane * 16u, wa, pred);
         cp_async_16_pred(stage_addr + 512u + lane * 16u, wb, pred);
     } else {
-        // quad q = lane>>2 owns 80 bytes per row half: windows 0..3 from its four lanes, window 4 from lane 3
+        // quad q = lane>>2 owns 80 bytes per row half: windows 0..3 from its four lanes, window 4 from lane 3.
+        // Only windows that hold bytes of the row are requested (q4_decomp.h).
         const uint32_t a = stage_addr + (lane >> 2) * 80u + t * 16u, b = a + 640u;
-        cp_async_16_pred(a, wa, pred);
-        cp_async_16_pred(b, wb, pred);
-        cp_async_16_pred(a + 16u, wa + 16, pred && t == 3u);
-        cp_async_16_pred(b + 16u, wb + 16, pred && t == 3u);
+        const bool own = pred && q4_window_wanted(t, mis, has_b);
+        const bool fifth = pred && t == 3u && q4_fifth_window_wanted(mis, has_b);
+        cp_async_16_pred(a, wa, own);
+        cp_async_16_pred(b, wb, own);
+        cp_async_16_pred(a + 16u, wa + 16, fifth);
+        cp_async_16_pred(b + 16u, wb + 16, fifth);
     }
 }
 
@@ -57,9 +61,12 @@ __device__ __forceinline__ void read_weights(uint32_t stage_addr, uint32_t lane,
     }
 }
 
+// parameters of one chunk for this lane's group; zeros (and no load) when `pred` is false
 template <bool ALIGNED>
 __device__ __forceinline__ void load_params(ParamRegs &c, const uint8_t *sa, const uint8_t *sb, const uint8_t *ba,
-                                            const uint8_t *bb) {
+                                            const uint8_t *bb, bool pred = true) {
+    c.sa = c.sb = c.ba = c.bb = 0;
+    if (!pred) return;
     if (ALIGNED) {
         c.sa = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(sa));
         c.sb = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(sb));

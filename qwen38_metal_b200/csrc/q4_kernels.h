@@ -1,5 +1,5 @@
 // Kernel-side parameter blocks and launcher prototypes shared between the .cu files and the
-// host runtime (runtime.cpp). Plain C structs: no CUDA types beyond cudaStream_t/cudaError_t.
+// host runtime (q4_runtime.cu). Plain C structs: no CUDA types beyond cudaStream_t/cudaError_t.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -71,19 +71,6 @@ cudaError_t q4k_argmax_rows(const float *logits, uint32_t m, uint32_t n, uint32_
 cudaError_t q4k_rms_unit_bf16(const float *in, uint32_t rows, uint32_t n, float eps, uint16_t *out, cudaStream_t stream);
 cudaError_t q4k_dequantize_row(const uint8_t *w, const uint8_t *s, const uint8_t *b, uint32_t k, uint32_t row, float *out,
                                cudaStream_t stream);
-
-size_t q4k_stack_stage_bytes(void);
-uint32_t q4k_stack_warps(void);
-uint32_t q4k_stack_max_k(void);
-void q4k_stack_fill_stage(void *stage_image, const q4::GemvParams *gemv, uint32_t x_kind, float eps, const void *src0,
-                          const void *src1, uint16_t *x_bf16_out);
-int q4k_stack_supported(uint32_t x_halfs, int sm_count);
-cudaError_t q4k_stack_launch(const void *stages_dev, uint32_t n_stages, uint32_t x_halfs, unsigned int *barrier, int *error_flag,
-                             const float *logits, uint32_t vocab, uint32_t index_base, float *part_val, uint32_t *part_idx,
-                             uint32_t *token, float *best, unsigned long long *trace, const void *peers, unsigned int epoch,
-                             int sm_count, cudaStream_t stream);
-size_t q4k_stack_peers_bytes(void);
-void q4k_stack_fill_peers(void *image, uint32_t world, uint32_t rank, void *const *flags, void *const *cand);
 
 cudaError_t q4k_gemm_prepare_x(const void *x, int x_is_f32, uint64_t elements, uint16_t *xp, cudaStream_t stream);
 uint32_t q4k_gemm_tile_m(uint32_t m);

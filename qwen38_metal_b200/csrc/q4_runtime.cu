@@ -9,13 +9,16 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <new>
 #include <string>
 #include <vector>
 
 #include "q4_kernels.h"
+#include "q4_stack.h"
 
 namespace {
 
@@ -77,6 +80,30 @@ struct Pool {
     }
 };
 
+// Grow-only pinned host buffer: results are downloaded here first and handed to the caller only after the device
+// reported success, so that caller buffers stay untouched when a call fails.
+struct HostPool {
+    void *ptr = nullptr;
+    size_t capacity = 0;
+    cudaError_t ensure(size_t bytes) {
+        if (bytes <= capacity) return cudaSuccess;
+        size_t want = 4096;
+        while (want < bytes) want <<= 1;
+        void *fresh = nullptr;
+        cudaError_t e = cudaHostAlloc(&fresh, want, cudaHostAllocDefault);
+        if (e != cudaSuccess) return e;
+        if (ptr) cudaFreeHost(ptr);
+        ptr = fresh;
+        capacity = want;
+        return cudaSuccess;
+    }
+    void release() {
+        if (ptr) cudaFreeHost(ptr);
+        ptr = nullptr;
+        capacity = 0;
+    }
+};
+
 struct Shard {
     uint8_t *ptr = nullptr;
     uint64_t bytes = 0;
@@ -97,7 +124,7 @@ struct q4b_runtime {
     uint64_t total_bytes = 0;
     char name[128] = {0};
     cudaStream_t stream = nullptr;
-    std::mutex mu;
+    std::recursive_mutex mu;  // host-side state (shard table, pools, counters); recursive: host entry points call the _device twins
     std::vector<Shard> shards;
     void *stage[2] = {nullptr, nullptr};  // pinned staging for uploads from pageable (mmap'd) memory
     cudaEvent_t stage_done[2] = {nullptr, nullptr};
@@ -107,11 +134,18 @@ struct q4b_runtime {
     Pool trace, gemm_x, gemm_parts, error_flag;
     uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
     uint32_t chain_offset_cost = 120;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
+    uint32_t chain_defer_split = 50;   // per cent of a stage's deferred rows that run behind its own barrier (the rest behind the next one)
+    uint32_t chain_spin_limit = 1u << 21;  // polls before a chain's barrier wait gives up
+    bool chain_no_fusion = false, chain_no_deferral = false;
+    bool chain_split_tiles = true;     // a phase with fewer tiles than warps gives every tile the same number of warps
+    uint32_t chain_flags = 0;
+    uint64_t failures = 0;             // bounded waits that ran out (finish() saw the error flag)
     uint64_t prof_flops = 0;
     bool tracing = false;
     uint32_t trace_workers = 0;
     Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
     Pool outs[q4::kMaxJobs];
+    HostPool results;  // staging for downloads (host-buffer entry points)
     uint64_t launches = 0;
     std::string force_variant;
     // per-kernel timing window (q4b_profile_begin/end)
@@ -344,6 +378,7 @@ int finish(q4b_runtime *rt, cudaStream_t stream) {
     if (e != cudaSuccess) return fail(Q4B_COMMAND_FAILED, "CUDA command failed: %s", cudaGetErrorString(e));
     if (flag) {
         cudaMemset(rt->error_flag.ptr, 0, sizeof flag);
+        rt->failures++;
         return fail(Q4B_COMMAND_FAILED, "a kernel gave up on a bounded wait (pipeline stalled); results are invalid");
     }
     return Q4B_OK;
@@ -381,6 +416,17 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     if (const char *cost = getenv("Q4B_CHAIN_OFFSET_COST")) {
         const long v = strtol(cost, nullptr, 10);
         if (v >= 100 && v <= 300) rt->chain_offset_cost = (uint32_t)v;
+    }
+    if (const char *split = getenv("Q4B_CHAIN_DEFER_SPLIT")) {
+        const long v = strtol(split, nullptr, 10);
+        if (v >= 0 && v <= 100) rt->chain_defer_split = (uint32_t)v;
+    }
+    if (const char *mode = getenv("Q4B_CHAIN_SPLIT")) rt->chain_split_tiles = strcmp(mode, "equal") != 0;
+    if (const char *fl = getenv("Q4B_CHAIN_FLAGS")) rt->chain_flags = (uint32_t)strtol(fl, nullptr, 10);
+    if (const char *plain = getenv("Q4B_CHAIN_PLAIN")) {  // 1: no gate/up fusion, 2: no deferred projections, 3: neither
+        const long v = strtol(plain, nullptr, 10);
+        rt->chain_no_fusion = (v & 1) != 0;
+        rt->chain_no_deferral = (v & 2) != 0;
     }
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
     if (rt->force_variant == "stream") rt->gemm_min_m = 0xffffffffu;   // never use the tensor-core GEMM
@@ -433,6 +479,7 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
+    rt->results.release();
     for (cudaEvent_t ev : rt->prof_events) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) {
         if (rt->stage[i]) cudaFreeHost(rt->stage[i]);
@@ -554,7 +601,7 @@ static cudaError_t staged_h2d(q4b_runtime *rt, uint8_t *dst, const uint8_t *src,
 extern "C" int q4b_shard_upload(q4b_runtime *rt, const void *host_bytes, uint64_t bytes, uint32_t *shard_id) {
     if (int st = check_rt(rt)) return st;
     if (!host_bytes && bytes) return fail(Q4B_INVALID_ARGUMENT, "host pointer is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     uint32_t id = 0;
     if (int st = shard_new(rt, bytes, &id)) return st;
@@ -572,7 +619,7 @@ extern "C" int q4b_shard_upload(q4b_runtime *rt, const void *host_bytes, uint64_
 // later use of it reports Q4B_MISSING_SHARD.
 extern "C" int q4b_shard_free(q4b_runtime *rt, uint32_t shard_id) {
     if (int st = check_rt(rt)) return st;
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     if (shard_id >= rt->shards.size() || !rt->shards[shard_id].ptr)
         return fail(Q4B_MISSING_SHARD, "mapped safetensors shard %u is absent", shard_id);
@@ -585,7 +632,7 @@ extern "C" int q4b_shard_free(q4b_runtime *rt, uint32_t shard_id) {
 
 extern "C" int q4b_shard_alloc(q4b_runtime *rt, uint64_t bytes, uint32_t *shard_id) {
     if (int st = check_rt(rt)) return st;
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     return shard_new(rt, bytes, shard_id);
 }
@@ -602,7 +649,7 @@ static int shard_range(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, uint
 extern "C" int q4b_shard_write(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, const void *host_bytes,
                                uint64_t bytes) {
     if (int st = check_rt(rt)) return st;
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     if (int st = shard_range(rt, shard_id, offset, bytes)) return st;
     if (bytes == 0) return Q4B_OK;
@@ -613,7 +660,7 @@ extern "C" int q4b_shard_write(q4b_runtime *rt, uint32_t shard_id, uint64_t offs
 
 extern "C" int q4b_shard_read(q4b_runtime *rt, uint32_t shard_id, uint64_t offset, void *host_bytes, uint64_t bytes) {
     if (int st = check_rt(rt)) return st;
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     if (int st = shard_range(rt, shard_id, offset, bytes)) return st;
     if (bytes == 0) return Q4B_OK;
@@ -626,14 +673,14 @@ extern "C" int q4b_shard_read(q4b_runtime *rt, uint32_t shard_id, uint64_t offse
 extern "C" int q4b_shard_count(q4b_runtime *rt, uint32_t *count) {
     if (int st = check_rt(rt)) return st;
     if (!count) return fail(Q4B_INVALID_ARGUMENT, "count pointer is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     *count = (uint32_t)rt->shards.size();
     return Q4B_OK;
 }
 
 extern "C" int q4b_shard_info(q4b_runtime *rt, uint32_t shard_id, void **device_ptr, uint64_t *bytes) {
     if (int st = check_rt(rt)) return st;
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     if (int st = shard_range(rt, shard_id, 0, 0)) return st;
     if (device_ptr) *device_ptr = rt->shards[shard_id].ptr;
     if (bytes) *bytes = rt->shards[shard_id].bytes;
@@ -644,7 +691,7 @@ extern "C" int q4b_offset_is_aligned(q4b_runtime *rt, uint32_t shard_id, uint64_
                                      int *aligned) {
     if (int st = check_rt(rt)) return st;
     if (!aligned || alignment == 0) return fail(Q4B_INVALID_ARGUMENT, "alignment must be positive and the result pointer non-null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     if (int st = shard_range(rt, shard_id, 0, 0)) return st;
     *aligned = (((uintptr_t)rt->shards[shard_id].ptr + byte_offset) % alignment) == 0 ? 1 : 0;
     return Q4B_OK;
@@ -661,6 +708,7 @@ extern "C" int q4b_matmul_batch_device(q4b_runtime *rt, const void *x_dev, int x
     if (int st = check_dtype(x_dtype)) return st;
     if (!x_dev || !outputs_dev) return fail(Q4B_INVALID_ARGUMENT, "activation or output pointer is null");
     if ((uintptr_t)x_dev & 15u) return fail(Q4B_INVALID_ARGUMENT, "device activations must be 16-byte aligned");
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     std::vector<Resolved> resolved;
     if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
@@ -675,6 +723,7 @@ extern "C" int q4b_argmax_batch_device(q4b_runtime *rt, const void *x_dev, int x
     if (int st = check_rt(rt)) return st;
     if (int st = check_dtype(x_dtype)) return st;
     if (!x_dev || !tokens_dev || !job) return fail(Q4B_INVALID_ARGUMENT, "activation, job or token pointer is null");
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     std::vector<Resolved> resolved;
     if (int st = resolve_jobs(rt, job, 1, m, k, &resolved)) return st;
@@ -697,6 +746,7 @@ extern "C" int q4b_swiglu_device(q4b_runtime *rt, const float *gate_dev, const f
     if (int st = check_rt(rt)) return st;
     if (!gate_dev || !up_dev || (!out_f32_dev && !out_bf16_dev)) return fail(Q4B_INVALID_ARGUMENT, "swiglu pointer is null");
     if (count == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     Q4B_CUDA(q4k_swiglu(gate_dev, up_dev, count, out_f32_dev, out_bf16_dev, (cudaStream_t)stream), "swiglu launch");
     rt->launches++;
@@ -708,6 +758,7 @@ extern "C" int q4b_rms_unit_bf16_device(q4b_runtime *rt, const float *in_dev, ui
     if (int st = check_rt(rt)) return st;
     if (!in_dev || !out_bf16_dev) return fail(Q4B_INVALID_ARGUMENT, "rms pointer is null");
     if (rows == 0 || n == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     Q4B_CUDA(q4k_rms_unit_bf16(in_dev, rows, n, eps, out_bf16_dev, (cudaStream_t)stream), "rms launch");
     rt->launches++;
@@ -723,7 +774,7 @@ static int host_matmul(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, 
     if (int st = check_rt(rt)) return st;
     if (int st = check_dtype(x_dtype)) return st;
     if (!x || !outputs) return fail(Q4B_INVALID_ARGUMENT, "activation or output pointer is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     std::vector<Resolved> resolved;
     if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
@@ -752,11 +803,15 @@ static int host_matmul(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, 
         cudaStreamSynchronize(s);
         return st;
     }
-    // results land in a private copy first so that caller buffers stay untouched on failure
+    // results are downloaded into the runtime's staging buffer and copied to the caller only after the device
+    // reported success: caller buffers stay untouched on failure
+    Q4B_CUDA(rt->results.ensure(total), "result staging");
     for (uint32_t i = 0; i < n_jobs; ++i)
-        Q4B_CUDA(cudaMemcpyAsync(outputs[i], outs_dev[i], (size_t)m * resolved[i].n * 4, cudaMemcpyDeviceToHost, s),
+        Q4B_CUDA(cudaMemcpyAsync((uint8_t *)rt->results.ptr + offs[i], outs_dev[i], (size_t)m * resolved[i].n * 4, cudaMemcpyDeviceToHost, s),
                  "result download");
-    return finish(rt, s);
+    if (int st = finish(rt, s)) return st;
+    for (uint32_t i = 0; i < n_jobs; ++i) memcpy(outputs[i], (uint8_t *)rt->results.ptr + offs[i], (size_t)m * resolved[i].n * 4);
+    return Q4B_OK;
 }
 
 extern "C" int q4b_matvec_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t k, const q4b_job *jobs,
@@ -780,7 +835,7 @@ extern "C" int q4b_argmax_batch(q4b_runtime *rt, const void *x, int x_dtype, uin
     if (int st = check_dtype(x_dtype)) return st;
     if (!x || !tokens || !job) return fail(Q4B_INVALID_ARGUMENT, "activation, job or token pointer is null");
     if (m == 0 || k == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
     Q4B_CUDA(rt->x_in.ensure((size_t)m * k * esize), "activation buffer");
@@ -808,7 +863,7 @@ extern "C" int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64
     if (gate->output_rows != up->output_rows)
         return fail(Q4B_WRONG_LENGTH, "up projection rows has %llu elements, expected %llu",
                     (unsigned long long)up->output_rows, (unsigned long long)gate->output_rows);
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     const uint64_t inter = gate->output_rows;
     std::vector<Resolved> gu, dn;
@@ -837,14 +892,17 @@ extern "C" int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64
         cudaStreamSynchronize(s);
         return st;
     }
-    Q4B_CUDA(cudaMemcpyAsync(out, dn_out, (size_t)m * dn[0].n * 4, cudaMemcpyDeviceToHost, s), "result download");
-    return finish(rt, s);
+    Q4B_CUDA(rt->results.ensure((size_t)m * dn[0].n * 4), "result staging");
+    Q4B_CUDA(cudaMemcpyAsync(rt->results.ptr, dn_out, (size_t)m * dn[0].n * 4, cudaMemcpyDeviceToHost, s), "result download");
+    if (int fst = finish(rt, s)) return fst;
+    memcpy(out, rt->results.ptr, (size_t)m * dn[0].n * 4);
+    return Q4B_OK;
 }
 
 extern "C" int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t k, uint64_t row, float *out) {
     if (int st = check_rt(rt)) return st;
     if (!job || !out) return fail(Q4B_INVALID_ARGUMENT, "job or output pointer is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     Resolved r;
     if (int st = resolve_job(rt, *job, k, &r)) return st;
@@ -853,8 +911,11 @@ extern "C" int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t 
     cudaStream_t s = rt->stream;
     Q4B_CUDA(q4k_dequantize_row(r.w, r.s, r.b, (uint32_t)k, (uint32_t)row, (float *)rt->outs[0].ptr, s), "dequantize launch");
     rt->launches++;
-    Q4B_CUDA(cudaMemcpyAsync(out, rt->outs[0].ptr, (size_t)k * 4, cudaMemcpyDeviceToHost, s), "result download");
-    return finish(rt, s);
+    Q4B_CUDA(rt->results.ensure((size_t)k * 4), "result staging");
+    Q4B_CUDA(cudaMemcpyAsync(rt->results.ptr, rt->outs[0].ptr, (size_t)k * 4, cudaMemcpyDeviceToHost, s), "result download");
+    if (int st = finish(rt, s)) return st;
+    memcpy(out, rt->results.ptr, (size_t)k * 4);
+    return Q4B_OK;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -863,20 +924,19 @@ extern "C" int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t 
 
 struct q4b_chain {
     q4b_runtime *rt = nullptr;
-    void *stages_dev = nullptr;
-    uint32_t n_stages = 0;
-    uint32_t x_halfs = 0;
-    unsigned int *barrier = nullptr;  // 2 words, then per-block argmax candidates
-    float *part_val = nullptr;
-    uint32_t *part_idx = nullptr;
-    const float *logits = nullptr;
-    uint32_t vocab = 0, index_base = 0;
+    q4::StackParams params;               // kernel arguments (device pointers)
+    std::vector<void *> owned;            // device allocations of this chain
+    void *reset_region = nullptr;         // local arrival counter + running maxima: zeroed before every launch
+    size_t reset_bytes = 0;
+    uint32_t n_phases = 0, n_stages = 0;
+    void *first_x = nullptr;              // first stage's bf16 activation (host twin of run copies into it)
+    uint64_t first_x_bytes = 0;
     uint32_t *token = nullptr;
     float *best = nullptr;
-    unsigned long long *trace = nullptr;  // [blocks][stages][4] when tracing was on at creation
-    void *peers_dev = nullptr;            // StackPeers image, multi-rank chains
-    std::vector<void *> mirror_tables;    // per-stage device tables of peer output pointers
-    unsigned int epoch = 0, barriers_per_run = 0;
+    bool multi_rank = false;
+    uint64_t failures_seen = 0;           // rt->failures when the chain was created / last repaired
+    std::vector<uint32_t> phase_stage;    // stage each phase belongs to (trace read-out)
+    std::vector<uint32_t> phase_role;     // 0 main, 1 deferred jobs of the same stage, 2 deferred jobs of the stage before
 };
 
 extern "C" int q4b_arena_create(q4b_runtime *rt, uint64_t bytes, void **device_ptr, uint8_t handle[64]) {
@@ -884,7 +944,7 @@ extern "C" int q4b_arena_create(q4b_runtime *rt, uint64_t bytes, void **device_p
     if (!device_ptr || !handle) return fail(Q4B_INVALID_ARGUMENT, "output pointer is null");
     if (bytes == 0) return fail(Q4B_EMPTY_BUFFER, "CUDA buffers cannot be empty");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     void *p = nullptr;
     Q4B_CUDA(cudaMalloc(&p, bytes), "arena allocation");
@@ -904,7 +964,7 @@ extern "C" int q4b_arena_create(q4b_runtime *rt, uint64_t bytes, void **device_p
 extern "C" int q4b_arena_open(q4b_runtime *rt, const uint8_t handle[64], void **peer_ptr) {
     if (int st = check_rt(rt)) return st;
     if (!peer_ptr || !handle) return fail(Q4B_INVALID_ARGUMENT, "output pointer is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     cudaIpcMemHandle_t h;
     memcpy(&h, handle, 64);
@@ -917,6 +977,42 @@ extern "C" int q4b_arena_open(q4b_runtime *rt, const uint8_t handle[64], void **
 
 extern "C" uint64_t q4b_chain_max_k(void) { return q4k_stack_max_k(); }
 
+namespace {
+
+struct ByteRange {
+    uintptr_t lo, hi;
+    bool overlaps(uintptr_t a, uintptr_t b) const { return a < hi && lo < b; }
+};
+
+// what one stage reads to build its activation
+void stage_sources(const q4b_stage &S, std::vector<ByteRange> *out) {
+    const uintptr_t s0 = (uintptr_t)S.src0, s1 = (uintptr_t)S.src1;
+    if (S.x_kind == Q4B_X_BF16) out->push_back({s0, s0 + S.k * 2});
+    if (S.x_kind == Q4B_X_SWIGLU) {
+        out->push_back({s0, s0 + S.k * 4});
+        out->push_back({s1, s1 + S.k * 4});
+    }
+    if (S.x_kind == Q4B_X_RMS) {
+        const uint64_t parts = S.src_parts ? S.src_parts : 1;
+        out->push_back({s0, s0 + (parts - 1) * S.src_part_stride + S.k * 4});
+    }
+}
+
+struct ChainBuild {
+    std::vector<void *> owned;
+    ~ChainBuild() {
+        for (void *p : owned) cudaFree(p);
+    }
+    cudaError_t alloc(void **p, size_t bytes, bool zero) {
+        cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+        if (e != cudaSuccess) return e;
+        owned.push_back(*p);
+        return zero ? cudaMemset(*p, 0, bytes ? bytes : 16) : cudaSuccess;
+    }
+};
+
+}  // namespace
+
 extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32_t n_stages, const float *logits, uint32_t vocab,
                                 uint32_t index_base, uint32_t *token_dev, float *best_dev, const q4b_peers *peers, q4b_chain **out) {
     if (int st = check_rt(rt)) return st;
@@ -924,154 +1020,439 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     if (logits && (!token_dev || vocab == 0)) return fail(Q4B_INVALID_ARGUMENT, "token pointer is null or vocabulary empty");
     if (peers && (peers->world < 2 || peers->world > (uint32_t)q4::kMaxPeers || peers->rank >= peers->world))
         return fail(Q4B_INVALID_ARGUMENT, "a multi-rank chain needs 2..%d ranks and a rank below the world size", q4::kMaxPeers);
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
-    std::vector<void *> mirror_tables;
     const uint32_t warps = q4k_stack_warps();
-    const size_t stage_bytes = q4k_stack_stage_bytes();
-    std::vector<uint8_t> image(stage_bytes * n_stages);
-    uint32_t x_halfs = 0;
+    const uint32_t grid_warps = (uint32_t)rt->sm_count * warps;
+
+    // ---- validate and resolve every stage ----
+    struct StageJobs {
+        std::vector<Resolved> res;
+        uint32_t k, k_total, k_begin;
+        int pair_a = -1, pair_b = -1;  // jobs fused with the SwiGLU of the next stage
+        std::vector<int> deferred;     // jobs nothing later reads
+    };
+    std::vector<StageJobs> sj(n_stages);
+    uint32_t halfs[2] = {0, 0};
     for (uint32_t si = 0; si < n_stages; ++si) {
         const q4b_stage &S = stages[si];
         if (S.x_kind > Q4B_X_RMS) return fail(Q4B_INVALID_ARGUMENT, "unknown activation kind %u in stage %u", S.x_kind, si);
-        if (!S.src0 || (S.x_kind == Q4B_X_SWIGLU && !S.src1) || !S.outputs) return fail(Q4B_INVALID_ARGUMENT, "stage %u has a null pointer", si);
+        if (!S.src0 || (S.x_kind == Q4B_X_SWIGLU && !S.src1) || !S.outputs || !S.jobs || S.n_jobs == 0)
+            return fail(Q4B_INVALID_ARGUMENT, "stage %u has a null pointer or no projection", si);
         if (((uintptr_t)S.src0 | (uintptr_t)S.src1) & 15u) return fail(Q4B_INVALID_ARGUMENT, "stage %u: source vectors must be 16-byte aligned", si);
         if (S.n_jobs > (uint32_t)q4::kMaxJobs) return fail(Q4B_UNSUPPORTED, "stage %u has more than %d projections", si, q4::kMaxJobs);
-        std::vector<Resolved> resolved;
-        if (int st = resolve_jobs(rt, S.jobs, S.n_jobs, 1, S.k, &resolved)) return st;
-        if (S.k % 512 != 0 || S.k > q4k_stack_max_k())
-            return fail(Q4B_UNSUPPORTED, "stage %u: the decode chain needs k %% 512 == 0 and k <= %u", si, q4k_stack_max_k());
-        const uint32_t k = (uint32_t)S.k, groups = k / 64, kp = (k + 127u) & ~127u;
-        x_halfs = kp > x_halfs ? kp : x_halfs;
-        q4::GemvParams p;
-        memset(&p, 0, sizeof p);
-        // A chunk of a projection whose weights sit at a byte offset costs more instructions than an aligned one. The
-        // stage's work is cut into equal unit ranges, so such a projection's tiles are given `vcpt` > cpt units each
-        // (the extra ones empty): its warps get fewer real chunks and all warps finish together.
-        const uint32_t cpt = (groups + 1u) / 2u;
-        const uint32_t vcpt_offset = (cpt * rt->chain_offset_cost + 50u) / 100u;
+        const uint64_t k_total = S.k_total ? S.k_total : S.k;
+        if (S.k == 0 || S.k % 128 != 0 || k_total % 512 != 0 || S.k_begin % 64 != 0 || S.k_begin + S.k > k_total)
+            return fail(Q4B_UNSUPPORTED, "stage %u: the decode chain needs k %% 128 == 0, a row length that is a multiple of 512 and a slice inside the row", si);
+        if (S.x_kind != Q4B_X_SWIGLU && S.k > q4k_stack_max_k())
+            return fail(Q4B_UNSUPPORTED, "stage %u: k exceeds %u", si, q4k_stack_max_k());
+        if (S.x_kind == Q4B_X_RMS && S.src_parts > 1 && (S.src_part_stride % 16 != 0 || S.src_part_stride < S.k * 4))
+            return fail(Q4B_INVALID_ARGUMENT, "stage %u: partial vectors must be 16-byte aligned and must not overlap", si);
+        if (int st = resolve_jobs(rt, S.jobs, S.n_jobs, 1, k_total, &sj[si].res)) return st;
+        for (uint32_t i = 0; i < S.n_jobs; ++i)
+            if (!S.outputs[i]) return fail(Q4B_INVALID_ARGUMENT, "stage %u output %u is null", si, i);
+        sj[si].k = (uint32_t)S.k;
+        sj[si].k_total = (uint32_t)k_total;
+        sj[si].k_begin = (uint32_t)S.k_begin;
+        const uint32_t kp = ((uint32_t)S.k + 127u) & ~127u;
+        halfs[si & 1u] = kp > halfs[si & 1u] ? kp : halfs[si & 1u];
+    }
+    if (n_stages * 3u >= q4::kMaxPhases) return fail(Q4B_UNSUPPORTED, "the decode chain takes fewer than %u stages", q4::kMaxPhases / 3u);
+    // Two activation buffers (stages alternate between them, so that deferred projections can still read the previous
+    // activation) when shared memory allows, else one buffer and no deferral.
+    bool single_buffer = rt->chain_no_deferral;
+    if (!single_buffer && !q4k_stack_supported(halfs[0], halfs[1])) single_buffer = true;
+    if (single_buffer) {
+        halfs[0] = halfs[0] > halfs[1] ? halfs[0] : halfs[1];
+        halfs[1] = 0;
+    }
+    if (!q4k_stack_supported(halfs[0], halfs[1]))
+        return fail(Q4B_UNSUPPORTED, "the decode chain kernel cannot be resident with an activation of %u inputs on this device", halfs[0]);
+
+    auto has_peer_out = [&](uint32_t si, uint32_t i) {
+        if (!peers || !stages[si].peer_outputs) return false;
+        for (uint32_t r = 0; r < peers->world; ++r)
+            if (r != peers->rank && stages[si].peer_outputs[(size_t)i * 8 + r]) return true;
+        return false;
+    };
+
+    // ---- fusion and deferral ----
+    std::vector<std::vector<ByteRange>> reads(n_stages);
+    for (uint32_t si = 0; si < n_stages; ++si) stage_sources(stages[si], &reads[si]);
+    for (uint32_t si = 0; si + 1 < n_stages; ++si) {
+        const q4b_stage &S = stages[si], &N = stages[si + 1];
+        // gate/up pair: the next stage is the SwiGLU of two of this stage's outputs, whole
+        if (N.x_kind == Q4B_X_SWIGLU && !rt->chain_no_fusion) {
+            int ga = -1, ub = -1;
+            for (uint32_t i = 0; i < S.n_jobs; ++i) {
+                if ((const void *)S.outputs[i] == N.src0) ga = (int)i;
+                if ((const void *)S.outputs[i] == N.src1) ub = (int)i;
+            }
+            if (ga >= 0 && ub >= 0 && ga != ub && sj[si].res[ga].n == N.k && sj[si].res[ub].n == N.k && !has_peer_out(si, ga) &&
+                !has_peer_out(si, ub)) {
+                sj[si].pair_a = ga;
+                sj[si].pair_b = ub;
+            }
+        }
+        // deferral: outputs that no later stage (and not the token reduction) reads
+        if (single_buffer) continue;
+        for (uint32_t i = 0; i < S.n_jobs; ++i) {
+            if ((int)i == sj[si].pair_a || (int)i == sj[si].pair_b || has_peer_out(si, i)) continue;
+            const uintptr_t lo = (uintptr_t)S.outputs[i], hi = lo + (uint64_t)sj[si].res[i].n * 4;
+            bool read_later = logits && ByteRange{(uintptr_t)logits, (uintptr_t)logits + (uint64_t)vocab * 4}.overlaps(lo, hi);
+            for (uint32_t later = si + 1; later < n_stages && !read_later; ++later)
+                for (const ByteRange &r : reads[later]) read_later = read_later || r.overlaps(lo, hi);
+            if (!read_later) sj[si].deferred.push_back((int)i);
+        }
+        if (sj[si].deferred.size() == S.n_jobs) sj[si].deferred.clear();  // a stage keeps at least one job in its main phase
+    }
+    for (uint32_t si = 0; si < n_stages; ++si) {
+        const bool fused = si > 0 && sj[si - 1].pair_a >= 0;
+        if (stages[si].x_kind == Q4B_X_SWIGLU && !fused && stages[si].k > q4k_stack_max_k())
+            return fail(Q4B_UNSUPPORTED, "stage %u: a SwiGLU stage that cannot be fused with the projections before it needs k <= %u", si, q4k_stack_max_k());
+    }
+
+    // ---- phases ----
+    ChainBuild build;
+    std::vector<q4::StackPhase> phases;
+    std::vector<q4::StackJob> jobs;
+    std::vector<uint32_t> phase_stage, phase_role;
+    std::vector<std::pair<size_t, size_t>> pair_fixups;  // (job index, pair ordinal): h buffer and amax word assigned below
+    std::vector<uint32_t> pair_k;
+    std::vector<uint32_t> pair_of_stage(n_stages, 0xffffffffu);
+
+    auto add_phase = [&](uint32_t si, uint32_t role, const std::vector<int> &list, bool with_pair) -> int {
+        const q4b_stage &S = stages[si];
+        const StageJobs &J = sj[si];
+        q4::StackPhase P;
+        memset(&P, 0, sizeof P);
+        P.job_begin = (uint32_t)jobs.size();
+        P.k = J.k;
+        P.kp = (J.k + 127u) & ~127u;
+        P.groups = J.k / 64;
+        P.cpt = (P.groups + 1u) / 2u;
+        P.x_buf = single_buffer ? 0u : (si & 1u);
+        P.slot_set = (uint32_t)(phases.size() % q4::kPartialSets);
+        const uint32_t cpt = P.cpt;
+        const uint32_t extra = rt->chain_offset_cost - 100u;  // per cent a byte-offset chunk costs more than an aligned one
         uint32_t tiles = 0, vcpt_max = cpt;
         uint64_t units = 0;
-        for (uint32_t i = 0; i < S.n_jobs; ++i) {
-            if (!S.outputs[i]) return fail(Q4B_INVALID_ARGUMENT, "stage %u output %u is null", si, i);
-            q4::GemvJob &j = p.jobs[i];
-            j.w = resolved[i].w;
-            j.s = resolved[i].s;
-            j.b = resolved[i].b;
-            j.out = S.outputs[i];
-            j.n = resolved[i].n;
-            j.out_stride = resolved[i].n;
+        auto push = [&](const Resolved &a, const Resolved &b, float *out_a, float *out_b, bool pair, uint32_t stage_job) -> int {
+            q4::StackJob j;
+            memset(&j, 0, sizeof j);
+            const Resolved *side[2] = {&a, &b};
+            for (int sdx = 0; sdx < 2; ++sdx) {
+                j.w[sdx] = side[sdx]->w + J.k_begin / 2;
+                j.s[sdx] = side[sdx]->s + (J.k_begin / 64) * 2;
+                j.b[sdx] = side[sdx]->b + (J.k_begin / 64) * 2;
+            }
+            j.out[0] = out_a;
+            j.out[1] = out_b;
+            j.n = a.n;
+            j.rows_per_tile = pair ? 8u : 16u;
+            j.b_row_offset = pair ? 0u : 8u;
+            j.w_stride = J.k_total / 2;
+            j.p_stride = (J.k_total / 64) * 2;
             j.tile_begin = tiles;
-            j.w_misalign = (uint32_t)((uintptr_t)resolved[i].w & 15u);
-            j.vcpt = j.w_misalign ? vcpt_offset : cpt;
+            j.pair = pair ? 1u : 0u;
+            const uint32_t off_sides = (((uintptr_t)j.w[0] & 15u) ? 1u : 0u) + (((uintptr_t)j.w[1] & 15u) ? 1u : 0u);
+            j.vcpt = (cpt * (200u + extra * off_sides) + 100u) / 200u;
             if (units > 0xffffffffull) return fail(Q4B_UNSUPPORTED, "stage %u is too large for the decode chain", si);
             j.unit_begin = (uint32_t)units;
-            const uint32_t job_tiles = (resolved[i].n + 15u) / 16u;
+            const uint32_t job_tiles = (a.n + j.rows_per_tile - 1u) / j.rows_per_tile;
             tiles += job_tiles;
             units += (uint64_t)job_tiles * j.vcpt;
             vcpt_max = j.vcpt > vcpt_max ? j.vcpt : vcpt_max;
+            if (!pair && has_peer_out(si, stage_job)) {
+                j.has_peers = 1;
+                for (uint32_t r = 0; r < peers->world; ++r)
+                    j.peer_out[r] = r == peers->rank ? nullptr : S.peer_outputs[(size_t)stage_job * 8 + r];
+            }
+            jobs.push_back(j);
+            return Q4B_OK;
+        };
+        if (with_pair) {
+            pair_fixups.push_back({jobs.size(), pair_k.size()});
+            pair_of_stage[si] = (uint32_t)pair_k.size();
+            pair_k.push_back(J.res[J.pair_a].n);
+            if (int st = push(J.res[J.pair_a], J.res[J.pair_b], S.outputs[J.pair_a], S.outputs[J.pair_b], true, 0)) return st;
         }
-        p.n_jobs = S.n_jobs;
-        p.v_cols = 1;
-        p.vpad = 4;
-        p.m_rows = 1;
-        p.k = k;
-        p.kp = kp;
-        p.groups = groups;
-        p.cpt = cpt;
-        p.units = units;
-        uint64_t workers = (uint64_t)rt->sm_count * warps;
+        for (int i : list)
+            if (int st = push(J.res[i], J.res[i], S.outputs[i], S.outputs[i], false, (uint32_t)i)) return st;
+        P.n_jobs = (uint32_t)jobs.size() - P.job_begin;
+        uint64_t workers = grid_warps;
+        // at most 32 warps share a tile: the warp that combines a split tile reads their partials four at a time
         const uint64_t min_chunks = (vcpt_max + 31u) / 32u;
-        if (workers > p.units / min_chunks) workers = p.units / min_chunks;
-        if (workers == 0) workers = 1;
-        p.workers = (uint32_t)workers;
-        p.partials = (float *)rt->partials.ptr;
-        p.counters = (unsigned int *)rt->counters.ptr;
-        if (peers && S.peer_outputs) {
-            void *table = nullptr;
-            const size_t tb = (size_t)q4::kMaxJobs * q4::kMaxPeers * sizeof(float *);
-            std::vector<float *> host_table((size_t)q4::kMaxJobs * q4::kMaxPeers, nullptr);
-            for (uint32_t i = 0; i < S.n_jobs; ++i)
-                for (uint32_t rr = 0; rr < peers->world; ++rr) host_table[(size_t)i * q4::kMaxPeers + rr] = S.peer_outputs[(size_t)i * 8 + rr];
-            Q4B_CUDA(cudaMalloc(&table, tb), "mirror table allocation");
-            mirror_tables.push_back(table);
-            Q4B_CUDA(cudaMemcpy(table, host_table.data(), tb, cudaMemcpyHostToDevice), "mirror table upload");
-            p.mirror = (float *const *)table;
-            p.world = peers->world;
-            p.rank = peers->rank;
+        if (rt->chain_split_tiles && tiles <= grid_warps) {
+            // Fewer tiles than warps: every tile is cut into the same number of equal parts, one per warp, so a warp
+            // has exactly one run of chunks (one pipeline ramp, at most one partial-sum exchange) per phase. The equal
+            // split of units yields this when all tiles count the same and the warps are a multiple of the tiles.
+            uint32_t parts = grid_warps / tiles;
+            if (parts > cpt / (uint32_t)min_chunks) parts = cpt / (uint32_t)min_chunks;
+            if (parts > 32u) parts = 32u;
+            if (parts == 0) parts = 1;
+            units = 0;
+            for (uint32_t i = P.job_begin; i < jobs.size(); ++i) {
+                jobs[i].vcpt = cpt;
+                jobs[i].unit_begin = (uint32_t)units;
+                units += (uint64_t)((jobs[i].n + jobs[i].rows_per_tile - 1u) / jobs[i].rows_per_tile) * cpt;
+            }
+            workers = (uint64_t)tiles * parts;
+        } else {
+            if (workers > units / min_chunks) workers = units / min_chunks;
+            if (workers == 0) workers = 1;
         }
-        q4k_stack_fill_stage(image.data() + stage_bytes * si, &p, S.x_kind, S.eps, S.src0, S.src1, (uint16_t *)S.x_bf16_out);
+        P.units = units;
+        P.workers = (uint32_t)workers;
+        phases.push_back(P);
+        phase_stage.push_back(si);
+        phase_role.push_back(role);
+        return Q4B_OK;
+    };
+
+    std::vector<int> carried;  // deferred jobs of the previous stage that run behind this stage's arrival
+    uint32_t carried_stage = 0;
+    bool any_global = false;
+    uint32_t prev_arrive = q4::kSyncNone;
+    for (uint32_t si = 0; si < n_stages; ++si) {
+        const q4b_stage &S = stages[si];
+        const StageJobs &J = sj[si];
+        std::vector<int> main_list;
+        for (uint32_t i = 0; i < S.n_jobs; ++i) {
+            const bool is_def = std::find(J.deferred.begin(), J.deferred.end(), (int)i) != J.deferred.end();
+            if (!is_def && (int)i != J.pair_a && (int)i != J.pair_b) main_list.push_back((int)i);
+        }
+        if (int st = add_phase(si, 0, main_list, J.pair_a >= 0)) return st;
+        q4::StackPhase &M = phases.back();
+        // the main phase waits for the stage before it and rebuilds the activation
+        M.wait_kind = si > 0 ? prev_arrive : (uint32_t)q4::kSyncNone;
+        const bool fused_in = si > 0 && sj[si - 1].pair_a >= 0;
+        M.x_kind = fused_in ? q4::kRebuildH : S.x_kind == Q4B_X_BF16 ? q4::kRebuildBf16 : S.x_kind == Q4B_X_SWIGLU ? q4::kRebuildSwiglu : q4::kRebuildRms;
+        M.src0 = S.src0;
+        M.src1 = S.src1;
+        M.src_parts = S.src_parts ? S.src_parts : 1u;
+        M.src_part_stride = (uint32_t)S.src_part_stride;
+        M.eps = S.eps;
+        M.x_bf16_out = (uint16_t *)S.x_bf16_out;
+        M.sum_out = (float *)S.sum_out;
+        bool global = false;
+        for (uint32_t i = 0; i < S.n_jobs; ++i) global = global || has_peer_out(si, i);
+        // the last stage's arrival publishes the logits; without a token reduction only peers would need it
+        const bool last = si + 1 == n_stages;
+        M.arrive_kind = global ? q4::kSyncGlobal : (last && !logits) ? q4::kSyncNone : q4::kSyncLocal;
+        prev_arrive = M.arrive_kind;
+        any_global = any_global || global;
+        // behind this stage's arrival: the carried half of the previous stage's deferred jobs, then the first part of
+        // this stage's own
+        if (!carried.empty()) {
+            if (int st = add_phase(carried_stage, 2, carried, false)) return st;
+            carried.clear();
+        }
+        if (!J.deferred.empty()) {
+            std::vector<int> now = J.deferred, later;
+            if (si + 2 < n_stages) {
+                // split by rows (all of a stage's jobs share k); the share that stays is rt->chain_defer_split per cent
+                uint64_t total = 0, run = 0;
+                for (int i : J.deferred) total += J.res[i].n;
+                now.clear();
+                for (int i : J.deferred) {
+                    if (run * 100 < total * rt->chain_defer_split || now.empty()) now.push_back(i);
+                    else later.push_back(i);
+                    run += J.res[i].n;
+                }
+            }
+            if (int st = add_phase(si, 1, now, false)) return st;
+            carried = later;
+            carried_stage = si;
+        }
     }
-    if (!q4k_stack_supported(x_halfs, rt->sm_count))
-        return fail(Q4B_UNSUPPORTED, "the decode chain kernel cannot be resident with k = %u on this device", x_halfs);
+    (void)any_global;
+    const size_t n_pairs = pair_k.size();
+
+    // ---- device memory of the chain ----
     q4b_chain *c = new (std::nothrow) q4b_chain();
     if (!c) return fail(Q4B_CUDA_ERROR, "out of host memory");
-    c->rt = rt;
-    c->n_stages = n_stages;
-    c->x_halfs = x_halfs;
-    c->logits = logits;
-    c->vocab = vocab;
-    c->index_base = index_base;
-    c->token = token_dev;
-    c->best = best_dev;
-    cudaError_t e = cudaMalloc(&c->stages_dev, image.size());
-    if (e == cudaSuccess) e = cudaMemcpy(c->stages_dev, image.data(), image.size(), cudaMemcpyHostToDevice);
-    void *aux = nullptr;
-    if (e == cudaSuccess) e = cudaMalloc(&aux, 256 + (size_t)rt->sm_count * 8);
-    if (e == cudaSuccess) e = cudaMemset(aux, 0, 256 + (size_t)rt->sm_count * 8);
-    if (e != cudaSuccess) {
-        if (c->stages_dev) cudaFree(c->stages_dev);
-        if (aux) cudaFree(aux);
-        delete c;
-        return fail_cuda(e, "decode chain allocation");
+    std::unique_ptr<q4b_chain> guard_chain(c);
+    uint8_t *reset = nullptr, *hbuf = nullptr;
+    const size_t reset_bytes = 256 + n_pairs * 4;
+    size_t h_total = 0;
+    std::vector<size_t> h_off(n_pairs);
+    for (size_t i = 0; i < n_pairs; ++i) {
+        h_off[i] = h_total;
+        h_total += ((size_t)pair_k[i] * 2 + 255) & ~(size_t)255;
     }
-    if (rt->tracing) {
-        const size_t tb = (size_t)rt->sm_count * n_stages * 32;
-        if (cudaMalloc((void **)&c->trace, tb) == cudaSuccess) cudaMemset(c->trace, 0, tb);
-        else c->trace = nullptr;
+    cudaError_t e = build.alloc((void **)&reset, reset_bytes, true);
+    if (e == cudaSuccess) e = build.alloc((void **)&hbuf, h_total + 256, true);
+    if (e != cudaSuccess) return fail_cuda(e, "decode chain allocation");
+    for (auto &fx : pair_fixups) {
+        jobs[fx.first].h_out = (uint16_t *)(hbuf + h_off[fx.second]);
+        jobs[fx.first].amax = (unsigned int *)(reset + 256 + fx.second * 4);
     }
-    c->mirror_tables = mirror_tables;
-    c->barriers_per_run = n_stages + (logits ? 1u : 0u) + ((logits && peers) ? 1u : 0u);
-    if (peers) {
-        std::vector<uint8_t> pimage(q4k_stack_peers_bytes());
-        q4k_stack_fill_peers(pimage.data(), peers->world, peers->rank, peers->flags, peers->cand);
-        if (cudaMalloc(&c->peers_dev, pimage.size()) != cudaSuccess ||
-            cudaMemcpy(c->peers_dev, pimage.data(), pimage.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
-            cudaGetLastError();
-            q4b_chain_destroy(c);
-            return fail(Q4B_CUDA_ERROR, "peer table allocation failed");
+    for (size_t pi = 0; pi < phases.size(); ++pi) {
+        if (phases[pi].x_kind != q4::kRebuildH) continue;
+        const uint32_t pr = pair_of_stage[phase_stage[pi] - 1];
+        phases[pi].src0 = hbuf + h_off[pr];
+        phases[pi].src1 = reset + 256 + (size_t)pr * 4;
+    }
+    void *phases_dev = nullptr, *jobs_dev = nullptr, *partials = nullptr, *counters = nullptr, *aux = nullptr, *peers_dev = nullptr, *trace = nullptr;
+    e = build.alloc(&phases_dev, phases.size() * sizeof(q4::StackPhase), false);
+    if (e == cudaSuccess) e = cudaMemcpy(phases_dev, phases.data(), phases.size() * sizeof(q4::StackPhase), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = build.alloc(&jobs_dev, jobs.size() * sizeof(q4::StackJob), false);
+    if (e == cudaSuccess) e = cudaMemcpy(jobs_dev, jobs.data(), jobs.size() * sizeof(q4::StackJob), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = build.alloc(&partials, (size_t)q4::kPartialSets * grid_warps * 32 * sizeof(uint4), true);
+    if (e == cudaSuccess) e = build.alloc(&counters, 256, true);
+    if (e == cudaSuccess) e = build.alloc(&aux, (size_t)rt->sm_count * 8, true);
+    if (e == cudaSuccess && rt->tracing) e = build.alloc(&trace, (size_t)rt->sm_count * phases.size() * q4::kTraceStamps * 8, true);
+    if (e == cudaSuccess && peers) {
+        q4::StackPeers pimage;
+        memset(&pimage, 0, sizeof pimage);
+        pimage.world = peers->world;
+        pimage.rank = peers->rank;
+        pimage.flag_local = (unsigned long long *)peers->flags[peers->rank];
+        pimage.consumed = pimage.flag_local + 1;
+        pimage.cand_local = (float2 *)peers->cand[peers->rank];
+        for (uint32_t r = 0; r < peers->world; ++r) {
+            if (!peers->flags[r] || !peers->cand[r]) return fail(Q4B_INVALID_ARGUMENT, "peer table entry %u is null", r);
+            pimage.flag_peer[r] = (unsigned long long *)peers->flags[r];
+            pimage.cand_peer[r] = (float2 *)peers->cand[r];
+        }
+        e = build.alloc(&peers_dev, sizeof pimage, false);
+        if (e == cudaSuccess) e = cudaMemcpy(peers_dev, &pimage, sizeof pimage, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) return fail_cuda(e, "decode chain allocation");
+
+    q4::StackParams &sp = c->params;
+    memset(&sp, 0, sizeof sp);
+    sp.phases = (const q4::StackPhase *)phases_dev;
+    sp.jobs = (const q4::StackJob *)jobs_dev;
+    sp.n_phases = (uint32_t)phases.size();
+    sp.halfs[0] = halfs[0];
+    sp.halfs[1] = halfs[1];
+    sp.local_bar = (unsigned int *)reset;
+    sp.error_flag = (int *)rt->error_flag.ptr;
+    sp.partials = (uint4 *)partials;
+    sp.launch_seq = (unsigned int *)counters;
+    sp.max_workers = grid_warps;
+    sp.spin_limit = rt->chain_spin_limit;
+    sp.flags = rt->chain_flags;
+    sp.logits = logits;
+    sp.vocab = vocab;
+    sp.index_base = index_base;
+    sp.part_val = (float *)aux;
+    sp.part_idx = (uint32_t *)((uint8_t *)aux + (size_t)rt->sm_count * 4);
+    sp.token = token_dev;
+    sp.best = best_dev;
+    sp.peers = (const q4::StackPeers *)peers_dev;
+    sp.trace = (unsigned long long *)trace;
+    if (rt->tracing && getenv("Q4B_CHAIN_DBG_PHASE")) {
+        void *dbg = nullptr;
+        if (build.alloc(&dbg, (size_t)grid_warps * 64 * 8, true) == cudaSuccess) {
+            sp.dbg = (unsigned long long *)dbg;
+            sp.dbg_phase = (uint32_t)strtol(getenv("Q4B_CHAIN_DBG_PHASE"), nullptr, 10);
         }
     }
-    c->barrier = (unsigned int *)aux;
-    c->part_val = (float *)((uint8_t *)aux + 256);
-    c->part_idx = (uint32_t *)((uint8_t *)aux + 256 + (size_t)rt->sm_count * 4);
-    *out = c;
+    c->rt = rt;
+    c->reset_region = reset;
+    c->reset_bytes = reset_bytes;
+    c->n_phases = sp.n_phases;
+    c->n_stages = n_stages;
+    c->token = token_dev;
+    c->best = best_dev;
+    c->multi_rank = peers != nullptr;
+    c->failures_seen = rt->failures;
+    c->phase_stage = phase_stage;
+    c->phase_role = phase_role;
+    if (stages[0].x_kind == Q4B_X_BF16) {
+        c->first_x = const_cast<void *>(stages[0].src0);
+        c->first_x_bytes = stages[0].k * 2;
+    }
+    c->owned.swap(build.owned);
+    *out = guard_chain.release();
+    return Q4B_OK;
+}
+
+extern "C" int q4b_chain_set_spin_limit(q4b_chain *chain, uint32_t polls) {
+    if (!chain || !chain->rt) return fail(Q4B_INVALID_ARGUMENT, "chain handle is null");
+    if (polls == 0) return fail(Q4B_INVALID_ARGUMENT, "the poll limit must be positive");
+    chain->params.spin_limit = polls;
     return Q4B_OK;
 }
 
 extern "C" int q4b_chain_run_device(q4b_chain *chain, void *stream) {
     if (!chain || !chain->rt) return fail(Q4B_INVALID_ARGUMENT, "chain handle is null");
     q4b_runtime *rt = chain->rt;
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
-    Q4B_CUDA(q4k_stack_launch(chain->stages_dev, chain->n_stages, chain->x_halfs, chain->barrier, (int *)rt->error_flag.ptr,
-                              chain->logits, chain->vocab, chain->index_base, chain->part_val, chain->part_idx, chain->token,
-                              chain->best, chain->trace, chain->peers_dev, chain->epoch, rt->sm_count, (cudaStream_t)stream),
-             "decode chain launch");
-    if (chain->peers_dev) chain->epoch += chain->barriers_per_run;
+    if (chain->failures_seen != rt->failures) {
+        // a bounded wait ran out on this runtime since the chain last ran. The counters of a multi-rank chain live
+        // on several GPUs and are out of step now; a single-GPU chain only needs the tags of its split-tile slots cleared (the launch count did not advance).
+        if (chain->multi_rank)
+            return fail(Q4B_POOL_POISONED, "a kernel gave up on a bounded wait: destroy this multi-rank chain, zero the arena on every rank and create it again");
+        Q4B_CUDA(cudaMemsetAsync(chain->params.partials, 0, (size_t)q4::kPartialSets * chain->params.max_workers * 32 * sizeof(uint4), (cudaStream_t)stream),
+                 "decode chain repair");
+        chain->failures_seen = rt->failures;
+    }
+    Q4B_CUDA(q4k_stack_launch(&chain->params, chain->reset_region, chain->reset_bytes, rt->sm_count, (cudaStream_t)stream), "decode chain launch");
     rt->launches++;
     return Q4B_OK;
 }
 
-extern "C" int q4b_chain_trace_read(q4b_chain *chain, uint64_t *stamps, uint64_t capacity_words, uint32_t *blocks, uint32_t *stages) {
-    if (!chain || !chain->rt || !stamps || !blocks || !stages) return fail(Q4B_INVALID_ARGUMENT, "chain handle or output pointer is null");
-    if (!chain->trace) return fail(Q4B_UNSUPPORTED, "the chain was created without tracing (q4b_trace_enable before q4b_chain_create)");
+// Host-buffer twin: the reference's token step takes a host slice and returns a token (src/native.rs:3250-3274,
+// 2644-2652). Copies the first stage's bf16 activation in, runs the chain, copies the token (and winning logit) out.
+extern "C" int q4b_chain_run(q4b_chain *chain, const void *x_host, uint32_t *token_host, float *best_host) {
+    if (!chain || !chain->rt) return fail(Q4B_INVALID_ARGUMENT, "chain handle is null");
+    if (!x_host || !token_host) return fail(Q4B_INVALID_ARGUMENT, "activation or token pointer is null");
+    if (!chain->first_x || !chain->token) return fail(Q4B_UNSUPPORTED, "the chain's first stage does not take a bf16 vector, or it produces no token");
+    q4b_runtime *rt = chain->rt;
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    cudaStream_t s = rt->stream;
+    Q4B_CUDA(cudaMemcpyAsync(chain->first_x, x_host, chain->first_x_bytes, cudaMemcpyHostToDevice, s), "activation upload");
+    if (int st = q4b_chain_run_device(chain, s)) {
+        cudaStreamSynchronize(s);
+        return st;
+    }
+    uint32_t token = 0;
+    float best = 0.f;
+    Q4B_CUDA(cudaMemcpyAsync(&token, chain->token, 4, cudaMemcpyDeviceToHost, s), "token download");
+    if (best_host && chain->best) Q4B_CUDA(cudaMemcpyAsync(&best, chain->best, 4, cudaMemcpyDeviceToHost, s), "logit download");
+    if (int st = finish(rt, s)) return st;
+    *token_host = token;
+    if (best_host && chain->best) *best_host = best;
+    return Q4B_OK;
+}
+
+// development aid: per-warp stamps around every wait for weights in one phase (Q4B_CHAIN_DBG_PHASE at creation)
+extern "C" int q4b_chain_debug_read(q4b_chain *chain, uint64_t *out, uint64_t capacity_words) {
+    if (!chain || !out || !chain->params.dbg) return fail(Q4B_UNSUPPORTED, "no debug stamps were recorded");
     DeviceGuard guard(chain->rt->device);
-    const uint64_t words = (uint64_t)chain->rt->sm_count * chain->n_stages * 4;
+    const uint64_t words = (uint64_t)chain->params.max_workers * 64;
+    if (capacity_words < words) return fail(Q4B_WRONG_LENGTH, "debug buffer has %llu elements, expected %llu", (unsigned long long)capacity_words, (unsigned long long)words);
+    Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
+    Q4B_CUDA(cudaMemcpy(out, chain->params.dbg, words * 8, cudaMemcpyDeviceToHost), "debug download");
+    return Q4B_OK;
+}
+
+extern "C" int q4b_chain_phase_count(q4b_chain *chain, uint32_t *phases) {
+    if (!chain || !phases) return fail(Q4B_INVALID_ARGUMENT, "chain handle or output pointer is null");
+    *phases = chain->n_phases;
+    return Q4B_OK;
+}
+
+extern "C" int q4b_chain_trace_read(q4b_chain *chain, uint64_t *stamps, uint64_t capacity_words, uint32_t *blocks, uint32_t *phases,
+                                    uint32_t *phase_info, uint32_t phase_info_capacity) {
+    if (!chain || !chain->rt || !stamps || !blocks || !phases) return fail(Q4B_INVALID_ARGUMENT, "chain handle or output pointer is null");
+    if (!chain->params.trace) return fail(Q4B_UNSUPPORTED, "the chain was created without tracing (q4b_trace_enable before q4b_chain_create)");
+    DeviceGuard guard(chain->rt->device);
+    const uint64_t words = (uint64_t)chain->rt->sm_count * chain->n_phases * q4::kTraceStamps;
     if (capacity_words < words) return fail(Q4B_WRONG_LENGTH, "trace buffer has %llu elements, expected %llu", (unsigned long long)capacity_words, (unsigned long long)words);
     Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
-    Q4B_CUDA(cudaMemcpy(stamps, chain->trace, words * 8, cudaMemcpyDeviceToHost), "trace download");
+    Q4B_CUDA(cudaMemcpy(stamps, chain->params.trace, words * 8, cudaMemcpyDeviceToHost), "trace download");
     *blocks = (uint32_t)chain->rt->sm_count;
-    *stages = chain->n_stages;
+    *phases = chain->n_phases;
+    if (phase_info) {
+        for (uint32_t i = 0; i < chain->n_phases && i < phase_info_capacity; ++i) phase_info[i] = chain->phase_stage[i] * 4u + chain->phase_role[i];
+    }
     return Q4B_OK;
 }
 
@@ -1080,11 +1461,7 @@ extern "C" void q4b_chain_destroy(q4b_chain *chain) {
     if (chain->rt) {
         DeviceGuard guard(chain->rt->device);
         cudaDeviceSynchronize();
-        if (chain->stages_dev) cudaFree(chain->stages_dev);
-        if (chain->barrier) cudaFree(chain->barrier);
-        if (chain->trace) cudaFree(chain->trace);
-        if (chain->peers_dev) cudaFree(chain->peers_dev);
-        for (void *t : chain->mirror_tables) cudaFree(t);
+        for (void *p : chain->owned) cudaFree(p);
     }
     delete chain;
 }
@@ -1097,7 +1474,7 @@ extern "C" int q4b_synth_q4_device(q4b_runtime *rt, uint64_t seed, uint64_t tens
                                    uint64_t rows, uint64_t k, const q4b_job *destination) {
     if (int st = check_rt(rt)) return st;
     if (!destination) return fail(Q4B_INVALID_ARGUMENT, "destination job is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
     Resolved r;
     q4b_job job = *destination;
@@ -1123,7 +1500,7 @@ extern "C" int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, u
     if (int st = check_rt(rt)) return st;
     if (int st = check_dtype(x_dtype)) return st;
     if (!text || text_len == 0) return fail(Q4B_INVALID_ARGUMENT, "text buffer is null");
-    std::lock_guard<std::mutex> lock(rt->mu);
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
     std::vector<Resolved> resolved;
     if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
     uint32_t fast = 0;

@@ -1,0 +1,112 @@
+// Program format of the persistent decode kernel (q4_decode_stack.cu), shared with the host code that compiles a
+// stage list into it (q4_runtime.cu). Plain structs, uploaded to device memory once per chain.
+//
+// A chain is a flat list of PHASES that every block walks in order. A phase is a set of projections over one
+// activation held in shared memory, optionally preceded by a wait on the previous barrier plus the rebuild of that
+// activation, and optionally followed by an arrival at the next barrier. Arrival and wait are separate steps: the
+// phases between them are projections whose results nothing later in the chain reads (Q/K/V and the DeltaNet inputs
+// of the reference's layer, src/metal_runtime.rs:3463-3517), so the weight stream keeps running while the barrier
+// completes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "q4_kernels.h"
+
+namespace q4 {
+
+constexpr uint32_t kPartialSets = 8;   // split-tile scratch sets, used round robin by consecutive phases
+constexpr uint32_t kMaxPhases = 4096;  // phases per chain (the tag of a partial slot is launch * kMaxPhases + phase + 1)
+
+// One projection of a phase. A tile is 16 accumulator rows: rows 0..7 ("side a") and rows 8..15 ("side b").
+//   ordinary job: both sides come from one tensor, side b is 8 rows further down (rows_per_tile 16, b_row_offset 8);
+//   gate/up pair: side a is a row of the gate tensor, side b the same row of the up tensor (rows_per_tile 8,
+//                 b_row_offset 0); the epilogue forms bf16(silu(gate) * up) from the two sums of a lane.
+// Rows may be strided views (w_stride, p_stride): a K-slice of a wider matrix is read in place.
+struct StackJob {
+    const uint8_t *w[2];   // packed weights at the first input of the slice, per side
+    const uint8_t *s[2];   // scales
+    const uint8_t *b[2];   // biases
+    float *out[2];         // fp32 results per side, indexed by row; pair: either may be null
+    float *peer_out[kMaxPeers];  // other ranks' copies of out[0] (ordinary jobs), null where not wanted
+    uint16_t *h_out;       // pair: bf16(silu(a) * b), indexed by row
+    unsigned int *amax;    // pair: running maximum of |h| as fp32 bits (zero at launch)
+    uint32_t n;            // rows per side
+    uint32_t rows_per_tile, b_row_offset;
+    uint32_t w_stride, p_stride;  // bytes between rows of the weight / parameter arrays (multiples of 16)
+    uint32_t tile_begin;   // first tile of this job in the phase
+    uint32_t unit_begin;   // first unit of this job in the phase
+    uint32_t vcpt;         // units a tile counts for when the phase is cut into equal ranges (>= cpt; the extra ones are
+                           // empty, so a job whose chunks cost more -- weights at a byte offset -- gets fewer per warp)
+    uint32_t pair;
+    uint32_t has_peers;
+};
+
+enum : uint32_t { kRebuildNone = 0, kRebuildBf16 = 1, kRebuildSwiglu = 2, kRebuildRms = 3, kRebuildH = 4 };
+enum : uint32_t { kSyncNone = 0, kSyncLocal = 1, kSyncGlobal = 2 };
+
+struct StackPhase {
+    uint32_t job_begin, n_jobs;
+    uint32_t k, kp, groups, cpt;  // inputs of this phase's activation (a K-slice counts its own inputs)
+    uint32_t workers;             // warps that take part
+    uint32_t x_buf;               // which of the two shared-memory activation buffers the phase reads
+    uint64_t units;
+    uint32_t wait_kind;           // wait for the latest arrival (this GPU's blocks / all ranks) before the phase
+    uint32_t x_kind;              // how the activation is rebuilt after the wait (kRebuild*)
+    const void *src0, *src1;      // Bf16: bf16[k]; Swiglu: fp32 gate[k], up[k]; Rms: fp32 [src_parts][k]; H: bf16[k], amax word
+    uint32_t src_parts, src_part_stride;  // Rms: the vector is the sum, in order, of src_parts vectors this many bytes apart
+    uint16_t *x_bf16_out;         // optional: block 0 stores the bf16 activation it built
+    float *sum_out;               // optional (Rms): block 0 stores the summed fp32 vector
+    float eps;
+    uint32_t arrive_kind;         // arrival after the phase's units
+    uint32_t slot_set;            // split-tile scratch set
+    uint32_t pad;
+};
+
+// Cross-GPU part of a sharded chain: every rank runs the same program on its own slices.
+struct StackPeers {
+    uint32_t world, rank;
+    unsigned long long *flag_local;            // arrivals of whole ranks at cross-GPU barriers, in this GPU's memory
+    unsigned long long *flag_peer[kMaxPeers];  // the same word on every rank (this rank's included)
+    unsigned long long *consumed;              // arrivals already accounted for by earlier launches (this GPU's memory)
+    float2 *cand_local;                        // [kMaxPeers] (best logit, token id) per vocabulary slice
+    float2 *cand_peer[kMaxPeers];
+};
+
+struct StackParams {
+    const StackPhase *phases;
+    const StackJob *jobs;
+    uint32_t n_phases;
+    uint32_t halfs[2];        // capacity of the two activation buffers in inputs (3 bytes each); the second may be 0
+    unsigned int *local_bar;  // arrivals of this GPU's blocks; zero at launch
+    int *error_flag;
+    uint4 *partials;          // [kPartialSets][max_workers][32 lanes] of {sum a, tag, sum b, tag}
+    unsigned int *launch_seq; // launches of this chain so far (read at the start, advanced at the end of the kernel)
+    uint32_t max_workers;
+    uint32_t spin_limit;      // polls before a wait gives up
+    uint32_t flags;           // kFlag*
+    const float *logits;      // output of the last phase to reduce to a token, or null
+    uint32_t vocab, index_base;
+    float *part_val;          // [gridDim.x]
+    uint32_t *part_idx;       // [gridDim.x]
+    uint32_t *token;
+    float *best;
+    const StackPeers *peers;  // null on one GPU
+    unsigned long long *trace;  // optional [blocks][n_phases][8] device-clock stamps
+    unsigned long long *dbg;    // optional [warps of the grid][64]: stamps around every wait for weights in phase dbg_phase
+    uint32_t dbg_phase;
+};
+
+constexpr uint32_t kFlagWarpFenceGpu = 1u;  // every warp fences at device scope before it arrives (default: block scope)
+
+constexpr uint32_t kTraceStamps = 8;  // wait begin, wait end, rebuild end, warp 0 units end, block's arrival, -, -, -
+
+}  // namespace q4
+
+extern "C" {
+uint32_t q4k_stack_warps(void);
+uint32_t q4k_stack_max_k(void);       // longest activation the Bf16/Swiglu/Rms rebuilds handle
+size_t q4k_stack_smem_bytes(uint32_t halfs0, uint32_t halfs1);
+int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1);
+cudaError_t q4k_stack_launch(const q4::StackParams *params, void *reset_region, size_t reset_bytes, int sm_count, cudaStream_t stream);
+}

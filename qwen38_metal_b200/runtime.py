@@ -262,8 +262,9 @@ class CudaRuntime:
 
     def chain_create(self, stages, logits_ptr: int = 0, vocab: int = 0, index_base: int = 0, token_ptr: int = 0,
                      best_ptr: int = 0, peers=None) -> "DecodeChain":
-        """stages: list of dicts {x_kind, k, src0, src1, x_bf16_out, jobs, outputs, eps[, peer_outputs]} with raw
-        device pointers; peers: None or {world, rank, flags: [ptr]*world, cand: [ptr]*world}."""
+        """stages: list of dicts {x_kind, k, src0, src1, x_bf16_out, jobs, outputs, eps[, peer_outputs, k_total,
+        k_begin, src_parts, src_part_stride, sum_out]} with raw device pointers (see q4b_stage);
+        peers: None or {world, rank, flags: [ptr]*world, cand: [ptr]*world}."""
         arr = (capi.Stage * len(stages))()
         keep = []
         for i, s in enumerate(stages):
@@ -276,7 +277,9 @@ class CudaRuntime:
                 mirrors = (C.c_void_p * len(flat))(*flat)
                 keep.append(mirrors)
             arr[i] = capi.Stage(s["x_kind"], s.get("eps", 1e-6), s["k"], s["src0"], s.get("src1") or None,
-                                s.get("x_bf16_out") or None, jobs, len(s["jobs"]), outs, mirrors)
+                                s.get("x_bf16_out") or None, jobs, len(s["jobs"]), outs, mirrors,
+                                s.get("k_total", 0), s.get("k_begin", 0), s.get("src_parts", 0), 0,
+                                s.get("src_part_stride", 0), s.get("sum_out") or None)
         cpeers = None
         if peers is not None:
             cpeers = capi.Peers(peers["world"], peers["rank"])
@@ -312,6 +315,9 @@ class CudaRuntime:
         _check(self._lib.q4b_profile_end(self._h, C.byref(n), C.byref(ms), C.byref(nbytes), C.byref(flops)))
         return {"launches": n.value, "ms": ms.value, "bytes": nbytes.value, "flops": flops.value}
 
+    def trace_enable(self, on: bool = True) -> None:
+        _check(self._lib.q4b_trace_enable(self._h, 1 if on else 0))
+
     def device_status(self) -> None:
         """Synchronise and raise if a device-resident call failed asynchronously."""
         _check(self._lib.q4b_device_status(self._h))
@@ -330,6 +336,34 @@ class DecodeChain:
 
     def run(self, stream: int = 0) -> None:
         _check(self._rt._lib.q4b_chain_run_device(self._h, stream))
+
+    def run_host(self, x_bits) -> tuple[int, float]:
+        """Host slice in, token out (q4b_chain_run): x_bits is the first stage's bf16 activation as uint16 (a numpy
+        array, or an integer address of k pinned uint16 values). Returns (token id, winning logit)."""
+        token, best = C.c_uint32(), C.c_float()
+        ptr = x_bits if isinstance(x_bits, int) else np.ascontiguousarray(x_bits, dtype=np.uint16).ctypes.data
+        _check(self._rt._lib.q4b_chain_run(self._h, ptr, C.byref(token), C.byref(best)))
+        return token.value, best.value
+
+    def set_spin_limit(self, polls: int) -> None:
+        _check(self._rt._lib.q4b_chain_set_spin_limit(self._h, polls))
+
+    def phase_count(self) -> int:
+        n = C.c_uint32()
+        _check(self._rt._lib.q4b_chain_phase_count(self._h, C.byref(n)))
+        return n.value
+
+    def trace_read(self):
+        """(stamps [blocks][phases][8] uint64 ns, phase_info [phases]) of the last run; the chain must have been
+        created after CudaRuntime.trace_enable(True)."""
+        phases = self.phase_count()
+        sms = self._rt.device_info()["sm_count"]
+        stamps = np.zeros(sms * phases * 8, dtype=np.uint64)
+        info = np.zeros(phases, dtype=np.uint32)
+        nb, nph = C.c_uint32(), C.c_uint32()
+        _check(self._rt._lib.q4b_chain_trace_read(self._h, stamps.ctypes.data_as(C.c_void_p), stamps.size, C.byref(nb),
+                                                  C.byref(nph), info.ctypes.data_as(C.c_void_p), phases))
+        return stamps.reshape(nb.value, nph.value, 8), info
 
     def close(self) -> None:
         if self._h:

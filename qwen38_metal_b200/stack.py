@@ -91,6 +91,7 @@ class SyntheticStack:
         self.rt, self.layers, self.hidden, self.inter, self.vocab = rt, layers, hidden, inter, vocab
         self.layer_rows, self.seed, self.rank, self.world = tuple(layer_rows), seed, rank, world
         self.device = torch.device("cuda", device)
+        self.misalign = misalign
         self.gate_i, self.up_i = len(layer_rows) - 2, len(layer_rows) - 1
         self.bytes_local = 0
         tensor = 0
@@ -117,8 +118,8 @@ class SyntheticStack:
         self.best = torch.zeros(1, dtype=f32, device=dev)
         self.checksum = torch.zeros(len(self.layer_rows) - 2, dtype=f32, device=dev)
 
-    def _make(self, tensor: int, n: int, k: int, offset: int) -> Projection:
-        r0, r1 = shard_rows(n, self.rank, self.world)
+    def _make(self, tensor: int, n: int, k: int, offset: int, whole: bool = False) -> Projection:
+        r0, r1 = (0, n) if whole else shard_rows(n, self.rank, self.world)
         rows = r1 - r0
         if rows == 0:
             return Projection(None, 0, r0, n)
@@ -128,7 +129,8 @@ class SyntheticStack:
         bb = self.rt.alloc_shard(rows * groups * 2 + offset)
         job = MappedQ4AffineJob(wb, offset, sb, offset, bb, offset, rows, offset % 4 == 0)
         self.rt.synth_q4(self.seed, tensor, 0.02, r0, rows, k, job)
-        self.bytes_local += weight_bytes(rows, k)
+        if not whole:
+            self.bytes_local += weight_bytes(rows, k)
         return Projection(job, rows, r0, n)
 
     def reset_input(self, stream: int = 0) -> None:
@@ -164,62 +166,74 @@ class SyntheticStack:
         return self.rt.chain_create(stages, self.logits.data_ptr(), self.vocab, 0, self.token.data_ptr(),
                                     self.best.data_ptr())
 
-    def build_chain_sharded(self, dist):
-        """The whole token as one persistent kernel per rank of a row-sharded stack. Outputs that feed a later stage
-        (gate, up, down) live in an exchange arena that every rank maps; each rank stores its rows into every
-        arena with peer stores and the chain's barriers span all ranks -- no collective library on the data path.
-        `dist` (torch.distributed) only carries the 64-byte IPC handles at set-up."""
+    def sharded_arena_bytes(self) -> int:
+        """Size of the exchange arena of `build_chain_sharded`: one partial down output per rank, the barrier words
+        and the token candidates."""
+        return self.world * ((self.hidden * 4 + 255) & ~255) + 512
+
+    def build_chain_sharded(self, dist, arenas=None):
+        """The whole token as one persistent kernel per rank. Projections of the hidden activation are row-sharded;
+        gate and up are fused into the slice of the SwiGLU vector this rank owns, and the down projection is cut
+        along K so that each rank consumes exactly that slice: it multiplies inputs [r0, r1) of the whole down
+        matrix (read in place through strided rows) and stores its partial output into every rank's exchange arena
+        with peer stores. The next activation is the RMS-norm of the partial outputs added in rank order -- one
+        cross-GPU barrier per layer and no collective library on the data path. Summation order differs from the
+        single-GPU chain (fp32 partial sums per rank), so results agree to fp32 rounding, not bit for bit.
+        `dist` (torch.distributed) only carries the 64-byte IPC handles at set-up. `arenas` (tests): exchange arenas
+        already mapped here, one base pointer per rank, in place of the IPC exchange."""
         world, rank, rt = self.world, self.rank, self.rt
 
         def align(n):
             return (n + 255) & ~255
 
-        off_gate, off_up = 0, align(self.inter * 4)
-        off_d = off_up + align(self.inter * 4)
-        off_flags = off_d + align(self.hidden * 4)
+        part_stride = align(self.hidden * 4)
+        off_parts, off_flags = 0, world * part_stride
         off_cand = off_flags + 256
         size = off_cand + 256
-        base, handle = rt.arena_create(size)
-        handles = [None] * world
-        dist.all_gather_object(handles, handle)
-        arena = [base if r == rank else rt.arena_open(handles[r]) for r in range(world)]
-        self.arena_base, self.arena_offsets = base, {"gate": off_gate, "up": off_up, "d": off_d}
-
-        def stage_jobs(projs, outs_local, shared):
-            """shared[i]: arena offset of job i's output buffer, or None when the output stays local."""
-            jobs, outs, mirrors = [], [], []
-            for p, o, sh in zip(projs, outs_local, shared):
-                if p.job is None:
-                    continue
-                jobs.append(p.job)
-                if sh is None:
-                    outs.append(o.data_ptr() + 4 * p.row0)
-                    mirrors.append([0] * 8)
-                else:
-                    outs.append(base + sh + 4 * p.row0)
-                    mirrors.append([0 if r == rank else arena[r] + sh + 4 * p.row0 for r in range(world)] + [0] * (8 - world))
-            return jobs, outs, mirrors
-
+        assert size == self.sharded_arena_bytes()
+        if arenas is None:
+            base, handle = rt.arena_create(size)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            arena = [base if r == rank else rt.arena_open(handles[r]) for r in range(world)]
+        else:
+            arena, base = list(arenas), arenas[rank]
+        self.arena_base = base
+        if not hasattr(self, "down_whole"):
+            # the whole down matrices (the per-stage path keeps its row slices in self.down)
+            first = len(self.layer_rows)
+            per_layer = first + 1
+            self.down_whole = [self._make(layer * per_layer + first, self.hidden, self.inter,
+                                          self.misalign if layer % 2 else 0, whole=True) for layer in range(self.layers)]
+        g, u = self.proj[0][self.gate_i], self.proj[0][self.up_i]
+        k0, k1 = g.row0, g.row0 + g.rows
+        if g.rows != u.rows or g.rows % 128 or k0 % 64:
+            raise ValueError("the K-sharded down projection needs gate/up slices that are multiples of 128 rows")
+        rms_src = {"src0": base + off_parts, "src_parts": world, "src_part_stride": part_stride, "sum_out": self.d.data_ptr()}
         stages = []
         for layer in range(self.layers):
-            shared = [None] * len(self.layer_rows)
-            shared[self.gate_i], shared[self.up_i] = off_gate, off_up
-            jobs, outs, mirrors = stage_jobs(self.proj[layer], self.outs, shared)
+            jobs, outs = [], []
+            for p, o in zip(self.proj[layer], self.outs):
+                if p.job is not None:
+                    jobs.append(p.job)
+                    outs.append(o.data_ptr() + 4 * p.row0)
             first = layer == 0
-            stages.append({"x_kind": capi.X_BF16 if first else capi.X_RMS, "k": self.hidden,
-                           "src0": self.x.data_ptr() if first else base + off_d, "eps": 1e-6,
-                           "x_bf16_out": 0 if first else self.x.data_ptr(), "jobs": jobs, "outputs": outs,
-                           "peer_outputs": mirrors})
-            jobs, outs, mirrors = stage_jobs([self.down[layer]], [self.d], [off_d])
-            stages.append({"x_kind": capi.X_SWIGLU, "k": self.inter, "src0": base + off_gate, "src1": base + off_up,
-                           "x_bf16_out": self.h.data_ptr(), "jobs": jobs, "outputs": outs, "peer_outputs": mirrors})
+            head = {"x_kind": capi.X_BF16, "src0": self.x.data_ptr()} if first else {"x_kind": capi.X_RMS, **rms_src}
+            stages.append({**head, "k": self.hidden, "eps": 1e-6, "x_bf16_out": 0 if first else self.x.data_ptr(),
+                           "jobs": jobs, "outputs": outs})
+            mine = off_parts + rank * part_stride
+            stages.append({"x_kind": capi.X_SWIGLU, "k": k1 - k0, "k_total": self.inter, "k_begin": k0,
+                           "src0": self.outs[self.gate_i].data_ptr() + 4 * k0, "src1": self.outs[self.up_i].data_ptr() + 4 * k0,
+                           "x_bf16_out": self.h.data_ptr() + 2 * k0, "jobs": [self.down_whole[layer].job],
+                           "outputs": [base + mine],
+                           "peer_outputs": [[0 if r == rank else arena[r] + mine for r in range(world)] + [0] * (8 - world)]})
         p = self.lm_head
         self.logits = torch.zeros(max(p.rows, 1), dtype=torch.float32, device=self.device)
-        stages.append({"x_kind": capi.X_RMS, "k": self.hidden, "src0": base + off_d, "eps": 1e-6,
-                       "x_bf16_out": self.x.data_ptr(), "jobs": [p.job], "outputs": [self.logits.data_ptr()],
-                       "peer_outputs": [[0] * 8]})
+        stages.append({"x_kind": capi.X_RMS, **rms_src, "k": self.hidden, "eps": 1e-6,
+                       "x_bf16_out": self.x.data_ptr(), "jobs": [p.job], "outputs": [self.logits.data_ptr()]})
         peers = {"world": world, "rank": rank, "flags": [a + off_flags for a in arena], "cand": [a + off_cand for a in arena]}
-        dist.barrier()  # every arena is mapped everywhere before the first launch
+        if arenas is None:
+            dist.barrier()  # every arena is mapped everywhere before the first launch
         return rt.chain_create(stages, self.logits.data_ptr(), p.rows, p.row0, self.token.data_ptr(), self.best.data_ptr(), peers)
 
     def decode_token(self, stream: int = 0, gather=None) -> None:

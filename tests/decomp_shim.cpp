@@ -6,5 +6,8 @@ uint32_t shim_owner(uint64_t units, uint32_t cpt, uint32_t workers, uint64_t u) 
 void shim_contributors(uint64_t units, uint32_t cpt, uint32_t workers, uint32_t tile, uint32_t *first, uint32_t *last) {
     q4_split_contributors(Q4Split{units, cpt, workers}, tile, first, last);
 }
+int shim_window_wanted(uint32_t t, uint32_t mis, int has_b) { return q4_window_wanted(t, mis, has_b != 0) ? 1 : 0; }
+int shim_fifth_window_wanted(uint32_t mis, int has_b) { return q4_fifth_window_wanted(mis, has_b != 0) ? 1 : 0; }
+uint32_t shim_lane_chunks(uint32_t groups, uint32_t t) { return q4_lane_chunks(groups, t); }
 uint32_t shim_slot(uint64_t units, uint32_t cpt, uint32_t workers, uint32_t w, uint32_t tile) { return q4_split_slot(Q4Split{units, cpt, workers}, w, tile); }
 }

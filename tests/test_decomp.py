@@ -21,6 +21,7 @@ def shim():
     lib.shim_owner.restype = C.c_uint32
     lib.shim_owner.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64]
     lib.shim_contributors.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
+    lib.shim_lane_chunks.restype = C.c_uint32
     lib.shim_slot.restype = C.c_uint32
     lib.shim_slot.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
     return lib
@@ -66,3 +67,46 @@ def test_split_is_a_partition_with_consistent_bookkeeping(shim, tiles, cpt, work
         split = [t for t in mine if len(set(owner[t * cpt:(t + 1) * cpt])) > 1]
         assert len(split) <= 2
         assert len({shim.shim_slot(units, cpt, workers, w, t) for t in split}) == len(split)
+
+
+@pytest.mark.parametrize("k", [64, 128, 192, 640, 1024])
+@pytest.mark.parametrize("mis", [0, 1, 2, 4, 7, 15])
+def test_byte_addressed_variant_never_reads_outside_the_tensors(shim, k, mis):
+    """Address arithmetic of the byte-addressed streaming kernel, on the CPU: every aligned 16-byte window it asks for
+    holds at least one byte of the weight row it belongs to, and every parameter it loads is a group of that row. A
+    caller's tensors (q4b_matvec_noalloc) therefore need no padding: only 16-byte blocks that the tensors themselves
+    touch are read, whatever the byte alignment and for odd group counts too."""
+    groups, row_bytes = k // 64, k // 2
+    cpt = (groups + 1) // 2
+    full_chunks = groups // 2
+    for rows in (1, 3):
+        base = 4096 + mis  # the tensor starts `mis` bytes past a 16-byte boundary
+        lo, hi = base, base + rows * row_bytes
+        first_block, last_block = lo // 16, (hi - 1) // 16
+        for r in range(rows):
+            row_lo, row_hi = base + r * row_bytes, base + (r + 1) * row_bytes
+            for c in range(cpt):
+                has_b = c < full_chunks
+                for t in range(4):
+                    window = row_lo + c * 64 + t * 16 - mis  # what the kernel computes: aligned by construction
+                    assert window % 16 == 0
+                    wanted = [window] if shim.shim_window_wanted(t, mis, int(has_b)) else []
+                    if t == 3 and shim.shim_fifth_window_wanted(mis, int(has_b)):
+                        wanted.append(window + 16)
+                    for a in wanted:
+                        assert a < row_hi and a + 16 > row_lo, (r, c, t, a)       # holds bytes of this row
+                        assert first_block <= a // 16 <= last_block
+                    # everything the lane later reads back from shared memory for an existing group was requested
+                    if t < 2 or has_b:
+                        need = {window} | ({window + 16} if mis else set())
+                        got = set()
+                        for tt in range(4):
+                            w2 = row_lo + c * 64 + tt * 16 - mis
+                            if shim.shim_window_wanted(tt, mis, int(has_b)):
+                                got.add(w2)
+                            if tt == 3 and shim.shim_fifth_window_wanted(mis, int(has_b)):
+                                got.add(w2 + 16)
+                        assert need <= got, (r, c, t)
+            for t in range(4):
+                n = shim.shim_lane_chunks(groups, t)
+                assert n == len([c for c in range(cpt) if 2 * c + (t >> 1) < groups])
