@@ -240,16 +240,19 @@ __device__ __forceinline__ void block_sum_max(float &sum, uint32_t &mx, float *r
 
 // The hidden vector as the gate/up epilogue left it: bf16 values and their maximum magnitude. No reduction, no
 // transcendental: 2 bytes per input.
+// [b_lo, b_hi): the 8-input blocks this SM holds (all of them, or the slice of a K-major phase; b_lo is a multiple of
+// 64 and X is offset so that block b_lo lands at the start of the buffer); [o_lo, o_hi): blocks this SM writes to the
+// optional bf16 copy.
 template <int WARPS>
-__device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &X) {
+__device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &X, uint32_t b_lo, uint32_t b_hi, uint32_t o_lo, uint32_t o_hi) {
     constexpr uint32_t T = WARPS * 32;
-    const uint32_t blocks = P.k / 8, blocks_p = P.kp / 8;
+    const uint32_t blocks = P.k / 8;
     const uint32_t amax = __ldcg(static_cast<const unsigned int *>(P.src1));
     const int e = scale_exponent(amax);
     const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
     if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
     const uint16_t *h = static_cast<const uint16_t *>(P.src0);
-    for (uint32_t b0 = (threadIdx.x & ~31u); b0 < blocks_p; b0 += T) {
+    for (uint32_t b0 = b_lo + (threadIdx.x & ~31u); b0 < b_hi; b0 += T) {
         const uint32_t b = b0 + (threadIdx.x & 31u);
         float v[8];
 #pragma unroll
@@ -264,8 +267,8 @@ __device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &
                 v[2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
             }
         }
-        emit_block(v, scale, b, b < blocks_p, X);
-        if (blockIdx.x == 0 && P.x_bf16_out && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = raw;
+        emit_block(v, scale, b, b < b_hi, X);
+        if (P.x_bf16_out && b >= o_lo && b < o_hi && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = raw;
     }
     __syncthreads();
 }
@@ -273,7 +276,8 @@ __device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &
 // bf16 vector | bf16(silu(gate)*up) of two fp32 vectors | weightless RMS-norm of an fp32 vector given as the sum of
 // src_parts vectors. Values are held in registers between the reduction and the conversion.
 template <int WARPS>
-__device__ __forceinline__ void rebuild_general(const StackPhase &P, const XBuf &X, float *red) {
+__device__ __forceinline__ void rebuild_general(const StackPhase &P, const XBuf &X, float *red, uint32_t b_lo, uint32_t b_hi, uint32_t o_lo,
+                                                uint32_t o_hi) {
     constexpr uint32_t T = WARPS * 32;
     const uint32_t k = P.k;
     const uint32_t blocks = k / 8, blocks_p = P.kp / 8;
@@ -345,8 +349,8 @@ __device__ __forceinline__ void rebuild_general(const StackPhase &P, const XBuf 
     for (int it = 0; it < kStackMaxIters; ++it) {
         const uint32_t b = threadIdx.x + it * T;
         if (it * T >= blocks_p) continue;
-        emit_block(v[it], scale, b, b < blocks_p, X);
-        if (blockIdx.x == 0 && P.x_bf16_out && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = pack_bf16x8(v[it]);
+        emit_block(v[it], scale, b, b >= b_lo && b < b_hi, X);
+        if (P.x_bf16_out && b >= o_lo && b < o_hi && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = pack_bf16x8(v[it]);
     }
     __syncthreads();
 }
@@ -515,6 +519,13 @@ __device__ __forceinline__ bool finish_tile_m1(const StackParams &sp, const Stac
     return J.has_peers != 0;
 }
 
+// The worker number of a warp in a phase (0xffffffff: none) -- see StackPhase::kparts.
+__device__ __forceinline__ uint32_t phase_worker(const StackPhase &P, uint32_t warp, uint32_t warps) {
+    if (P.kparts <= 1u) return blockIdx.x * warps + warp;
+    const uint32_t tile = (blockIdx.x / P.kparts) * warps + warp;
+    return tile < P.tiles ? tile * P.kparts + blockIdx.x % P.kparts : 0xffffffffu;
+}
+
 __device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
@@ -550,7 +561,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t worker = blockIdx.x * WARPS + warp;
     // shared memory: per-warp rings | activation buffer 0 | activation buffer 1 | group sums 0 | group sums 1 | misc
     uint8_t *xp0 = smem + WARPS * kStackRingBytes;
     uint8_t *xp1 = xp0 + sp.halfs[0] * 3 + kXSlack;
@@ -595,7 +605,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             return (sp.trace && lane == 0) ? sp.trace + ((size_t)blockIdx.x * sp.n_phases + ph) * kTraceStamps : nullptr;
         };
         const bool second = P.x_buf != 0;
-        const XBuf X{second ? xp1 : xp0, second ? xsum1 : xsum0, misc + (second ? 1 : 0)};
+        const uint32_t worker = phase_worker(P, warp, WARPS);
+        // chunks of the activation this SM holds: all, or the run of its part (K-major phases), from a multiple of four
+        uint32_t c_lo = 0, c_hi = P.kp / 128u;
+        if (P.kparts > 1u && P.sliced) {
+            const uint32_t part = blockIdx.x % P.kparts;
+            c_lo = P.cpt * part / P.kparts;
+            c_hi = P.cpt * (part + 1u) / P.kparts;
+        }
+        const uint32_t cs4 = c_lo & ~3u;
+        // pointers such that chunk cs4 lands at the start of the buffer
+        const XBuf X{(second ? xp1 : xp0) - (size_t)cs4 * kXChunkBytes, (second ? xsum1 : xsum0) - (size_t)cs4 * 2u, misc + (second ? 1 : 0)};
         // descriptors of the phase after this one: bring them into L2 while this one runs
         if (warp == 1 && ph + 2 < sp.n_phases) {
             const StackPhase &N = sp.phases[ph + 2];
@@ -611,8 +631,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                 __syncthreads();  // everyone is done with the buffer that is about to be rewritten
             }
             if (sp.trace && threadIdx.x == 0) trace_slot()[1] = stack_ns();
-            if (P.x_kind == kRebuildH) rebuild_from_h<WARPS>(P, X);
-            else if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(P, X, red);
+            // the bf16 copy of the activation is written by block 0, or by the first kparts blocks (one part each)
+            const bool writes = blockIdx.x < ((P.kparts > 1u && P.sliced) ? P.kparts : 1u);
+            const uint32_t o_lo = writes ? c_lo * 16u : 0u, o_hi = writes ? c_hi * 16u : 0u;
+            if (P.x_kind == kRebuildH) rebuild_from_h<WARPS>(P, X, cs4 * 16u, c_hi * 16u, o_lo, o_hi);
+            else if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi);
             if (sp.trace && threadIdx.x == 0) trace_slot()[2] = stack_ns();
         }
 
@@ -636,9 +659,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             prefetched = false;
             if (ph + 1 < sp.n_phases) {
                 const StackPhase &N = sp.phases[ph + 1];
-                if (worker < N.workers) {
+                const uint32_t nworker = phase_worker(N, warp, WARPS);
+                if (nworker < N.workers) {
                     const Q4Split nsplit{N.units, N.cpt, N.workers};
-                    const uint32_t nu = (uint32_t)q4_split_begin(nsplit, worker), nu1 = (uint32_t)q4_split_begin(nsplit, worker + 1);
+                    const uint32_t nu = (uint32_t)q4_split_begin(nsplit, nworker), nu1 = (uint32_t)q4_split_begin(nsplit, nworker + 1);
                     if (nu < nu1) {
                         job_rel = 0;
                         segment_setup(N, sp.jobs, nu, nu1, job_rel, lane, sg);

@@ -136,7 +136,9 @@ struct q4b_runtime {
     uint32_t chain_offset_cost = 120;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
     uint32_t chain_defer_split = 50;   // per cent of a stage's deferred rows that run behind its own barrier (the rest behind the next one)
     uint32_t chain_spin_limit = 1u << 21;  // polls before a chain's barrier wait gives up
-    bool chain_no_fusion = false, chain_no_deferral = false;
+    // Deferred projections (run behind a barrier's arrival) are off unless asked for: measured on B200 the extra runs
+    // of chunks they create cost more than the barrier time they cover.
+    bool chain_no_fusion = false, chain_no_deferral = true;
     bool chain_split_tiles = true;     // a phase with fewer tiles than warps gives every tile the same number of warps
     uint32_t chain_flags = 0;
     uint64_t failures = 0;             // bounded waits that ran out (finish() saw the error flag)
@@ -423,11 +425,8 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     }
     if (const char *mode = getenv("Q4B_CHAIN_SPLIT")) rt->chain_split_tiles = strcmp(mode, "equal") != 0;
     if (const char *fl = getenv("Q4B_CHAIN_FLAGS")) rt->chain_flags = (uint32_t)strtol(fl, nullptr, 10);
-    if (const char *plain = getenv("Q4B_CHAIN_PLAIN")) {  // 1: no gate/up fusion, 2: no deferred projections, 3: neither
-        const long v = strtol(plain, nullptr, 10);
-        rt->chain_no_fusion = (v & 1) != 0;
-        rt->chain_no_deferral = (v & 2) != 0;
-    }
+    if (const char *plain = getenv("Q4B_CHAIN_PLAIN")) rt->chain_no_fusion = strtol(plain, nullptr, 10) != 0;  // no gate/up fusion
+    if (const char *defer = getenv("Q4B_CHAIN_DEFER")) rt->chain_no_deferral = strtol(defer, nullptr, 10) == 0;
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
     if (rt->force_variant == "stream") rt->gemm_min_m = 0xffffffffu;   // never use the tensor-core GEMM
     if (rt->force_variant == "tensor") rt->gemm_min_m = 1;            // always use it
@@ -1054,20 +1053,8 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         sj[si].k = (uint32_t)S.k;
         sj[si].k_total = (uint32_t)k_total;
         sj[si].k_begin = (uint32_t)S.k_begin;
-        const uint32_t kp = ((uint32_t)S.k + 127u) & ~127u;
-        halfs[si & 1u] = kp > halfs[si & 1u] ? kp : halfs[si & 1u];
     }
     if (n_stages * 3u >= q4::kMaxPhases) return fail(Q4B_UNSUPPORTED, "the decode chain takes fewer than %u stages", q4::kMaxPhases / 3u);
-    // Two activation buffers (stages alternate between them, so that deferred projections can still read the previous
-    // activation) when shared memory allows, else one buffer and no deferral.
-    bool single_buffer = rt->chain_no_deferral;
-    if (!single_buffer && !q4k_stack_supported(halfs[0], halfs[1])) single_buffer = true;
-    if (single_buffer) {
-        halfs[0] = halfs[0] > halfs[1] ? halfs[0] : halfs[1];
-        halfs[1] = 0;
-    }
-    if (!q4k_stack_supported(halfs[0], halfs[1]))
-        return fail(Q4B_UNSUPPORTED, "the decode chain kernel cannot be resident with an activation of %u inputs on this device", halfs[0]);
 
     auto has_peer_out = [&](uint32_t si, uint32_t i) {
         if (!peers || !stages[si].peer_outputs) return false;
@@ -1076,9 +1063,31 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         return false;
     };
 
-    // ---- fusion and deferral ----
+    ChainBuild build;
+    std::vector<q4::StackPhase> phases;
+    std::vector<q4::StackJob> jobs;
+    std::vector<uint32_t> phase_stage, phase_role;
+    std::vector<std::pair<size_t, size_t>> pair_fixups;  // (job index, pair ordinal): h buffer and amax word assigned below
+    std::vector<uint32_t> pair_k;
+    std::vector<uint32_t> pair_of_stage;
     std::vector<std::vector<ByteRange>> reads(n_stages);
     for (uint32_t si = 0; si < n_stages; ++si) stage_sources(stages[si], &reads[si]);
+    // Two activation buffers (stages alternate between them, so that deferred projections can still read the previous
+    // activation) when shared memory allows, else one buffer and no deferral: the plan is made twice if need be.
+    bool single_buffer = rt->chain_no_deferral;
+    for (int attempt = 0;; ++attempt) {
+    phases.clear();
+    jobs.clear();
+    phase_stage.clear();
+    phase_role.clear();
+    pair_fixups.clear();
+    pair_k.clear();
+    pair_of_stage.assign(n_stages, 0xffffffffu);
+    for (StageJobs &J : sj) {
+        J.pair_a = J.pair_b = -1;
+        J.deferred.clear();
+    }
+    // ---- fusion and deferral ----
     for (uint32_t si = 0; si + 1 < n_stages; ++si) {
         const q4b_stage &S = stages[si], &N = stages[si + 1];
         // gate/up pair: the next stage is the SwiGLU of two of this stage's outputs, whole
@@ -1113,14 +1122,6 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     }
 
     // ---- phases ----
-    ChainBuild build;
-    std::vector<q4::StackPhase> phases;
-    std::vector<q4::StackJob> jobs;
-    std::vector<uint32_t> phase_stage, phase_role;
-    std::vector<std::pair<size_t, size_t>> pair_fixups;  // (job index, pair ordinal): h buffer and amax word assigned below
-    std::vector<uint32_t> pair_k;
-    std::vector<uint32_t> pair_of_stage(n_stages, 0xffffffffu);
-
     auto add_phase = [&](uint32_t si, uint32_t role, const std::vector<int> &list, bool with_pair) -> int {
         const q4b_stage &S = stages[si];
         const StageJobs &J = sj[si];
@@ -1183,11 +1184,15 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         uint64_t workers = grid_warps;
         // at most 32 warps share a tile: the warp that combines a split tile reads their partials four at a time
         const uint64_t min_chunks = (vcpt_max + 31u) / 32u;
-        if (rt->chain_split_tiles && tiles <= grid_warps) {
+        P.tiles = tiles;
+        const uint32_t tile_groups = (tiles + warps - 1u) / warps;  // blocks that hold every tile once, one tile per warp
+        if (rt->chain_split_tiles && tile_groups <= (uint32_t)rt->sm_count) {
             // Fewer tiles than warps: every tile is cut into the same number of equal parts, one per warp, so a warp
             // has exactly one run of chunks (one pipeline ramp, at most one partial-sum exchange) per phase. The equal
-            // split of units yields this when all tiles count the same and the warps are a multiple of the tiles.
-            uint32_t parts = grid_warps / tiles;
+            // split of units yields this when all tiles count the same and the warps are a multiple of the tiles. With
+            // more than one part the phase is K-major: a block takes one part of sixteen tiles and only rebuilds and
+            // holds that slice of the activation.
+            uint32_t parts = (uint32_t)rt->sm_count / tile_groups;
             if (parts > cpt / (uint32_t)min_chunks) parts = cpt / (uint32_t)min_chunks;
             if (parts > 32u) parts = 32u;
             if (parts == 0) parts = 1;
@@ -1198,6 +1203,10 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
                 units += (uint64_t)((jobs[i].n + jobs[i].rows_per_tile - 1u) / jobs[i].rows_per_tile) * cpt;
             }
             workers = (uint64_t)tiles * parts;
+            P.kparts = parts;
+            // only the stage's own dependent phase rebuilds the buffer, and it may keep a slice only when no deferred
+            // phase (whose parts differ) reads the same buffer later
+            P.sliced = (parts > 1u && role == 0 && J.deferred.empty()) ? 1u : 0u;
         } else {
             if (workers > units / min_chunks) workers = units / min_chunks;
             if (workers == 0) workers = 1;
@@ -1267,6 +1276,26 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         }
     }
     (void)any_global;
+    // what each activation buffer has to hold: the whole activation, or the longest slice of a K-major phase (from a
+    // multiple of four chunks, plus the chunk that is read ahead)
+    halfs[0] = halfs[1] = 0;
+    for (const q4::StackPhase &P : phases) {
+        uint32_t chunks = P.kp / 128u;
+        if (P.kparts > 1u && P.sliced) {
+            chunks = 0;
+            for (uint32_t part = 0; part < P.kparts; ++part) {
+                const uint32_t lo = (P.cpt * part / P.kparts) & ~3u, hi = P.cpt * (part + 1u) / P.kparts;
+                chunks = hi - lo > chunks ? hi - lo : chunks;
+            }
+            chunks += 1u;
+        }
+        halfs[P.x_buf] = chunks * 128u > halfs[P.x_buf] ? chunks * 128u : halfs[P.x_buf];
+    }
+    if (q4k_stack_supported(halfs[0], halfs[1])) break;
+    if (single_buffer || attempt > 0)
+        return fail(Q4B_UNSUPPORTED, "the decode chain kernel cannot be resident with an activation of %u inputs on this device", halfs[0]);
+    single_buffer = true;
+    }
     const size_t n_pairs = pair_k.size();
 
     // ---- device memory of the chain ----

@@ -49,6 +49,13 @@ struct StackPhase {
     uint32_t job_begin, n_jobs;
     uint32_t k, kp, groups, cpt;  // inputs of this phase's activation (a K-slice counts its own inputs)
     uint32_t workers;             // warps that take part
+    uint32_t tiles;               // 16-row tiles of all jobs
+    // K-major mapping (0 or 1: off). Every tile is cut into `kparts` equal runs of chunks and a block works on ONE of
+    // them -- part blockIdx % kparts of the 16 tiles (blockIdx / kparts) * 16 + warp -- so it rebuilds and holds only
+    // that slice of the activation. Worker numbers stay tile * kparts + part.
+    uint32_t kparts;
+    uint32_t sliced;              // the activation buffer holds only the block's part (set on the phase that rebuilds it;
+                                  // phases that reuse a buffer built whole leave it 0)
     uint32_t x_buf;               // which of the two shared-memory activation buffers the phase reads
     uint64_t units;
     uint32_t wait_kind;           // wait for the latest arrival (this GPU's blocks / all ranks) before the phase

@@ -174,3 +174,47 @@ def test_full_width_chain_every_stage_against_the_oracle(runtime, oracle):
     assert token == int(np.argmax(got_logits))  # numpy's argmax also takes the lowest index among equals
     assert float(stack.best.item()) == float(got_logits[token])
     chain.close()
+
+
+@pytest.mark.parametrize("defer", ["0", "1"])
+def test_mid_width_chain_with_and_without_deferred_projections(oracle, defer, monkeypatch):
+    """A stack wide enough that tiles are cut into many parts (K-major phases hold slices of the activation that do not
+    start at chunk 0), run with the default plan and with projections deferred behind the barriers (two activation
+    buffers, Q4B_CHAIN_DEFER=1 is latched when the runtime is created): both must match the per-stage path."""
+    import torch
+
+    from qwen38_metal_b200.runtime import CudaRuntime
+    from qwen38_metal_b200.stack import SyntheticStack
+
+    monkeypatch.setenv("Q4B_CHAIN_DEFER", defer)
+    rt = CudaRuntime(0)
+    try:
+        stack = SyntheticStack(rt, layers=3, hidden=2048, inter=4096, vocab=3000, layer_rows=(512, 256, 128, 48, 4096, 4096),
+                               seed=83, misalign=2)
+        stream = torch.cuda.current_stream().cuda_stream
+        stack.reset_input(stream)
+        torch.cuda.synchronize()
+        x0 = stack.x.clone()
+        stack.decode_token(stream)
+        rt.device_status()
+        ref_d, ref_outs, ref_token = stack.d.clone(), [o.clone() for o in stack.outs], int(stack.token.item())
+        chain = stack.build_chain()
+        for _ in range(2):
+            stack.x.copy_(x0)
+            stack.d.zero_()
+            for o in stack.outs:
+                o.zero_()
+            torch.cuda.synchronize()
+            chain.run(stream)
+            rt.device_status()
+            assert oracle.rel_l2(stack.d.cpu().numpy(), ref_d.cpu().numpy()) <= 2e-3
+            for got, ref in zip(stack.outs, ref_outs):
+                assert oracle.rel_l2(got.cpu().numpy(), ref.cpu().numpy()) <= 2e-3
+            logits = stack.logits.cpu().numpy()
+            assert int(stack.token.item()) == int(np.argmax(logits))
+            order = np.sort(logits)
+            if order[-1] - order[-2] > 1e-2 * abs(order[-1]):
+                assert int(stack.token.item()) == ref_token
+        chain.close()
+    finally:
+        rt.close()
