@@ -4,13 +4,14 @@
     python bench.py --gpus N --steps K --warmup W            # this implementation
     python bench.py --impl reference ...                      # the reference arithmetic on the host CPU
 
-Workload (config 4 of BASELINE.json; it repeats the grouped decode set of config 1 sixty-four
-times): a synthetic 64-layer projection stack, M=1 decode, plus an lm_head of 248320 rows -- 13.75 GB
-of packed Q4 weights generated in HBM from a seed. One step is one token: per layer one grouped launch
-of nine K=5120 projections sharing one activation, SwiGLU, the K=17408 down projection, a weightless
-RMS-norm; then lm_head and argmax. Half of the projections start 2 bytes off a 16-byte boundary.
-With N GPUs the output rows of every projection are sharded N ways and the outputs that feed the next
-projection are all-gathered (NCCL) -- strong scaling.
+Workload (the full-stack decode configuration; it repeats the grouped decode set sixty-four times):
+a synthetic 64-layer projection stack, M=1 decode, plus an lm_head of 248320 rows -- 13.75 GB
+of packed Q4 weights generated in HBM from a seed. One step is one token: per layer nine K=5120
+projections sharing one activation, SwiGLU, the K=17408 down projection, a weightless RMS-norm; then
+lm_head and argmax. Half of the projections start 2 bytes off a 16-byte boundary.
+With N GPUs the work of every projection is sharded N ways -- strong scaling. The timed path is the
+persistent decode chain (one kernel per token and GPU; across GPUs it exchanges partial down outputs with
+peer stores); the CUDA graph of per-stage launches with NCCL all-gathers is timed beside it.
 
 The metric is weight-stream bandwidth: algorithmic bytes of one token (packed weights + scales +
 biases) x steps / time, aggregated over all GPUs. tokens/s is the same number divided by 13.75 GB.
@@ -88,7 +89,7 @@ def secondary_metrics(torch, rt, stack, stream, capi):
 
     def timed(fn, m, flags, iters, warm=2):
         """ms per call: `iters` calls on different layers captured in one CUDA graph (no host launch cost between
-        them), replayed once untimed and once timed."""
+        them), replayed once untimed and five times timed; the median replay is reported."""
         for i in range(warm):
             fn(i % layers, m, flags)  # sizes the scratch pools before capture
         stream.synchronize()
@@ -98,13 +99,16 @@ def secondary_metrics(torch, rt, stack, stream, capi):
                 fn((warm + i) % layers, m, flags)
         graph.replay()
         stream.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        graph.replay()
-        e1.record(stream)
-        stream.synchronize()
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            times.append(e0.elapsed_time(e1) / iters)
         rt.device_status()
-        return e0.elapsed_time(e1) / iters
+        return sorted(times)[len(times) // 2]
 
     out = {}
     with torch.cuda.stream(stream):
@@ -220,48 +224,82 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+_CPU_LAYER = None
+
+
+def cpu_layer_set(oracle):
+    """One layer of the stack on the host (layer 0's ten tensors, generated once: 203.6 MB of packed weights, larger
+    than the host's last-level cache, so every pass streams them from DRAM)."""
+    global _CPU_LAYER
+    if _CPU_LAYER is None:
+        from qwen38_metal_b200.stack import HIDDEN, INTER, LAYER_ROWS
+
+        mats = [(n, HIDDEN, oracle.synth_q4(SEED, i, n, HIDDEN)) for i, n in enumerate(LAYER_ROWS)]
+        mats.append((HIDDEN, INTER, oracle.synth_q4(SEED, len(LAYER_ROWS), HIDDEN, INTER)))
+        x = oracle.bf16_to_f32(oracle.synth_bf16(SEED, 10_000, HIDDEN))
+        nbytes = sum(n * (k // 2) + 2 * n * (k // 64) * 2 for n, k, _ in mats)
+        _CPU_LAYER = (mats, x, nbytes)
+    return _CPU_LAYER
+
+
 def cpu_sample(oracle, threads: int, budget_s: float):
-    """The oracle's kernel-form arithmetic on the host cores over one gate projection (17408 x 5120),
-    repeated until about `budget_s` seconds of CPU work have been done."""
-    n, k = 17408, 5120
-    w, s, b = oracle.synth_q4(SEED, 7, n, k)
-    x = oracle.bf16_to_f32(oracle.synth_bf16(SEED, 10_000, k))
-    nbytes = n * (k // 2) + 2 * n * (k // 64) * 2
-    oracle.matmul_factored_f32(x, w, s, b, n, threads=threads)  # warm
+    """The oracle's kernel-form arithmetic on the host cores over ONE LAYER of the workload (nine K=5120 projections
+    of one activation, SwiGLU, the K=17408 down projection), repeated until about `budget_s` seconds of CPU work have
+    been done. Returns (GB/s of packed weights, description, seconds per pass, bytes per pass)."""
+    mats, x, nbytes = cpu_layer_set(oracle)
+
+    def one_pass():
+        outs = [oracle.matmul_factored_f32(x, *t, n, threads=threads)[0] for n, k, t in mats[:-1]]
+        h = oracle.bf16_to_f32(oracle.f32_to_bf16(oracle.swiglu(outs[-2], outs[-1])))
+        n, k, t = mats[-1]
+        return oracle.matmul_factored_f32(h, *t, n, threads=threads)[0]
+
+    one_pass()  # warm
     t0 = time.perf_counter()
     passes = 0
     while True:
-        oracle.matmul_factored_f32(x, w, s, b, n, threads=threads)
+        one_pass()
         passes += 1
         dt = time.perf_counter() - t0
         if dt >= budget_s or passes >= 10_000:
             break
-    return nbytes * passes / dt / 1e9, f"gate projection 17408x5120 ({nbytes / 1e6:.1f} MB), {passes} passes, {dt:.1f} s", dt / passes
+    return (nbytes * passes / dt / 1e9, f"one layer set of the stack ({nbytes / 1e6:.1f} MB of packed weights), {passes} passes in {dt:.1f} s",
+            dt / passes, nbytes)
+
+
+WORKLOAD = "config4-full-stack-decode: 64 x config1 grouped decode set + lm_head, M=1"
 
 
 def run_reference(args) -> int:
     """The reference's arithmetic for this path on the host CPU (the reference itself needs Metal and a
-    Rust toolchain, so the CPU oracle -- a restatement of its kernel, oracle/q4_oracle.c -- is timed)."""
+    Rust toolchain, so the CPU oracle -- a restatement of its kernel, oracle/q4_oracle.c -- is timed). Each step is a
+    bounded sample of the workload: whole layers of the stack, streamed from host DRAM; the time of a whole token is
+    the measured time per layer pass scaled by the token's bytes (labelled as extrapolated)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     from oracle import q4_oracle as oracle
+    from qwen38_metal_b200.stack import token_bytes
 
     threads = os.cpu_count() or 1
     per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
-    values, sample, ms = [], "", []
+    values, sample, ms, per_pass_ms, pass_bytes = [], "", [], [], 1
     for i in range(args.warmup + args.steps):
-        v, sample, per_pass = cpu_sample(oracle, threads, per_step_budget)
+        t0 = time.perf_counter()
+        v, sample, per_pass, pass_bytes = cpu_sample(oracle, threads, per_step_budget)
         if i >= args.warmup:
             values.append(v)
-            ms.append(per_step_budget * 1e3)
+            ms.append((time.perf_counter() - t0) * 1e3)
+            per_pass_ms.append(per_pass * 1e3)
     value = sum(values) / len(values)
+    pass_ms = sum(per_pass_ms) / len(per_pass_ms)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sum(ms) / len(ms), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config4-full-stack-decode (CPU: bounded sample of its weight stream)",
-                   "sample": sample},
+        "config": {"workload": WORKLOAD, "sample": sample, "ms_per_layer_pass": pass_ms,
+                   "ms_per_token_extrapolated": pass_ms * token_bytes() / pass_bytes,
+                   "note": "a step is a bounded sample: repeated passes over one layer set for ms_per_step milliseconds"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -290,6 +328,8 @@ def run_ours(args) -> int:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     build.build()
+    sampler = ClockSampler(local_rank)  # nvidia-smi needs a second or two before its first sample: start it now
+    sampler.start()
     rt = CudaRuntime(local_rank)
     stack = SyntheticStack(rt, layers=args.layers, rank=rank, world=world, seed=SEED, device=local_rank, misalign=args.misalign)
     total_bytes = token_bytes(layers=args.layers)
@@ -304,9 +344,9 @@ def run_ours(args) -> int:
     host_tok = torch.empty(2, dtype=torch.int32).pin_memory()
     with torch.cuda.stream(stream):
         stack.reset_input(stream.cuda_stream)
-        stack.decode_token(stream.cuda_stream, gather)  # sizes every scratch pool before capture
         stream.synchronize()
-        host_x.copy_(stack.x)  # any bf16 vector will do as the per-step input
+        host_x.copy_(stack.x)  # the seeded input activation: the same on every rank and for every GPU count
+        stack.decode_token(stream.cuda_stream, gather)  # sizes every scratch pool before capture
         stream.synchronize()
         launches_before = rt.launch_count()
         pairs = torch.zeros(world, 2, dtype=torch.float32, device=stack.device)
@@ -338,12 +378,40 @@ def run_ours(args) -> int:
     # row-sharded outputs with peer stores and share their barriers. The CUDA graph of per-stage launches (with
     # NCCL all-gathers between kernels when sharded) is timed beside it.
     chain = None
+    parity = {}
     if not args.no_chain:
         chain = stack.build_chain() if world == 1 else stack.build_chain_sharded(dist)
+        # Parity before anything is timed. The stack amplifies last-bit differences by about an order of magnitude per
+        # layer (bf16 re-rounding of a re-normalised activation), so two evaluation orders -- the chain and the
+        # per-stage path, or one GPU and several -- can only be compared on a shallow prefix: one layer + lm_head must
+        # give the same token and the same down output to 2e-4 (a handful of last-place flips of the bf16 SwiGLU
+        # vector, each worth about 1.5e-5; without flips the paths agree to 5e-7). That token and checksum also let lines of different
+        # GPU counts be compared with each other. The full-depth token and checksum are reported for the record.
+        probe = stack.build_chain(layers=1) if world == 1 else stack.build_chain_sharded(dist, layers=1)
         with torch.cuda.stream(stream):
+            stack.x.copy_(host_x, non_blocking=True)
+            stack.decode_token(stream.cuda_stream, gather, layers=1)
+            lm_head_pick()
+            stream.synchronize()
+            token_stages, d_stages = int(stack.token.item()), stack.d.clone()
+            stack.x.copy_(host_x, non_blocking=True)
+            stack.token.zero_()
+            probe.run(stream.cuda_stream)
+            stream.synchronize()
+            rt.device_status()
+            parity = {"depth": "1 layer + lm_head", "token": int(stack.token.item()), "token_per_stage_path": token_stages,
+                      "d_checksum": stack.d.double().sum().item(),
+                      "d_rel_l2_between_paths": ((stack.d - d_stages).double().norm() / d_stages.double().norm()).item()}
+            parity["match"] = parity["token"] == token_stages and parity["d_rel_l2_between_paths"] <= 2e-4
+            stack.x.copy_(host_x, non_blocking=True)
             chain.run(stream.cuda_stream)
             stream.synchronize()
         rt.device_status()
+        parity["full_depth"] = {"token": int(stack.token.item()), "d_checksum": stack.d.double().sum().item(),
+                                "note": "not comparable between evaluation orders (chaotic amplification over 64 layers)"}
+        if world > 1:
+            dist.barrier()
+        probe.close()
 
     def step():
         if chain is not None:
@@ -365,8 +433,6 @@ def run_ours(args) -> int:
             g1.record(stream)
             stream.synchronize()
             ms_graph = g0.elapsed_time(g1)
-        sampler = ClockSampler(local_rank)
-        sampler.start()
         for _ in range(max(3, args.warmup)):
             step()
         barrier()
@@ -382,14 +448,25 @@ def run_ours(args) -> int:
         barrier()
         e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e2.record(stream)
-        for _ in range(args.steps):
-            stack.x.copy_(host_x, non_blocking=True)
-            step()
-            host_tok[:1].copy_(stack.token, non_blocking=True)
+        if chain is not None:
+            # the plugin call: host slice in, token out (q4b_chain_run copies the activation up, runs the chain on the
+            # runtime's stream, copies the token and its logit back and synchronises)
             stream.synchronize()
+            t_host = time.perf_counter()
+            for _ in range(args.steps):
+                chain.run_host(host_x.data_ptr())
+            host_ms = (time.perf_counter() - t_host) * 1e3
+        else:
+            for _ in range(args.steps):
+                stack.x.copy_(host_x, non_blocking=True)
+                step()
+                host_tok[:1].copy_(stack.token, non_blocking=True)
+                stream.synchronize()
         e3.record(stream)
         barrier()
         ms_e2e = e2.elapsed_time(e3)
+        if chain is not None:
+            ms_e2e = host_ms  # the calls ran on the runtime's own stream: timed on the host, every call synchronous
         clocks = sampler.stop(first_sample, sampler.mark())
         if world > 1 and rank != 0:
             pass
@@ -414,7 +491,7 @@ def run_ours(args) -> int:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x u4 -> f32", "data": "synthetic",
-            "config": {"workload": "config4-full-stack-decode: 64 x config1 grouped decode set + lm_head, M=1",
+            "config": {"workload": WORKLOAD,
                        "layers": args.layers, "hidden": stack.hidden, "intermediate": stack.inter,
                        "vocab": stack.vocab, "bytes_per_token": total_bytes, "seed": SEED,
                        "row_sharding": f"{world}-way", "l2": "13.75 GB streamed per step, far larger than L2",
@@ -423,8 +500,11 @@ def run_ours(args) -> int:
             "frac_of_8TBs": value / (NOMINAL_HBM_GBS * world),
             "frac_of_measured_hbm": value / (peak * world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": stack.hidden * 2,
-                    "d2h_bytes_per_step": 4, "tokens_per_s": args.steps / (ms_e2e * 1e-3),
-                    "what": "pinned input activation -> HBM, captured token graph, token id -> host, sync per step"},
+                    "d2h_bytes_per_step": 8 if chain is not None else 4, "tokens_per_s": args.steps / (ms_e2e * 1e-3),
+                    "what": ("q4b_chain_run per step: pinned host activation -> HBM, one persistent chain launch, token id and "
+                             "logit -> host, synchronised (host clock around the calls)") if chain is not None else
+                            "pinned input activation -> HBM, captured token graph, token id -> host, sync per step"},
+            "parity": parity,
             "gpu_launches": (2 if chain is not None else launches_per_token) * args.steps,
             "path": ("persistent decode chain (one cooperative launch per token and GPU"
                      + (", peer stores + cross-GPU barriers)" if world > 1 else ")")) if chain is not None
@@ -456,9 +536,16 @@ def run_ours(args) -> int:
             from oracle import q4_oracle as oracle
 
             threads = os.cpu_count() or 1
-            v, sample, _ = cpu_sample(oracle, threads, args.cpu_seconds)
+            v, sample, _, _ = cpu_sample(oracle, threads, args.cpu_seconds)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line))
+    if parity and not parity["match"]:
+        print("bench.py: the persistent chain and the per-stage path disagree: " + json.dumps(parity), file=sys.stderr)
+        sys.stdout.flush()
+        if world > 1:
+            dist.barrier()  # rank 0 has printed its line before anyone leaves with a failure
+            os._exit(1)
+        return 1
     if world > 1:
         # A captured graph still references the communicator; tearing the process group down with it alive has
         # hung at exit, so leave together and let process exit release everything.

@@ -103,7 +103,9 @@ __device__ __forceinline__ bool phase_wait(const StackParams &sp, uint32_t kind,
     int ok = 1;
     if (threadIdx.x == 0) {
         uint32_t spins = 0;
-        if (kind == kSyncGlobal) {
+        if (*reinterpret_cast<volatile int *>(sp.error_flag)) {
+            ok = 0;  // somebody has already given up: leave instead of working on invalid data
+        } else if (kind == kSyncGlobal) {
             const unsigned long long target = *ss.gbase + (unsigned long long)ss.global_gen * sp.peers->world;
             while (true) {
                 unsigned long long seen;
@@ -276,8 +278,8 @@ __device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &
 // bf16 vector | bf16(silu(gate)*up) of two fp32 vectors | weightless RMS-norm of an fp32 vector given as the sum of
 // src_parts vectors. Values are held in registers between the reduction and the conversion.
 template <int WARPS>
-__device__ __forceinline__ void rebuild_general(const StackPhase &P, const XBuf &X, float *red, uint32_t b_lo, uint32_t b_hi, uint32_t o_lo,
-                                                uint32_t o_hi) {
+__device__ __forceinline__ void rebuild_general(const StackParams &sp, const StackPhase &P, const XBuf &X, float *red, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t o_lo, uint32_t o_hi, uint32_t src_tag) {
     constexpr uint32_t T = WARPS * 32;
     const uint32_t k = P.k;
     const uint32_t blocks = k / 8, blocks_p = P.kp / 8;
@@ -312,11 +314,37 @@ __device__ __forceinline__ void rebuild_general(const StackPhase &P, const XBuf 
                 }
             } else {
                 for (uint32_t part = 0; part < P.src_parts; ++part) {
-                    const float4 *p0 = reinterpret_cast<const float4 *>(
-                        reinterpret_cast<const uint8_t *>(P.src0) + (size_t)part * P.src_part_stride + (size_t)b * 32);
-                    const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1);
-                    v[it][0] += a0.x; v[it][1] += a0.y; v[it][2] += a0.z; v[it][3] += a0.w;
-                    v[it][4] += a1.x; v[it][5] += a1.y; v[it][6] += a1.z; v[it][7] += a1.w;
+                    const uint8_t *base = reinterpret_cast<const uint8_t *>(P.src0) + (size_t)part * P.src_part_stride;
+                    if (P.src_tagged) {
+                        // {value, tag} words: wait (bounded) until all eight carry the producing phase's tag
+                        const uint4 *p0 = reinterpret_cast<const uint4 *>(base + (size_t)b * 64);
+                        uint4 q[4];
+                        uint32_t spins = 0;
+                        while (true) {
+                            bool ok = true;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w) : "l"(p0 + i) : "memory");
+                                ok = ok && q[i].y == src_tag && q[i].w == src_tag;
+                            }
+                            if (ok) break;
+                            if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
+                                *sp.error_flag = 1;  // the values are wrong from here on; every block leaves at its next wait
+                                break;
+                            }
+                            __nanosleep(40);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            v[it][2 * i] += __uint_as_float(q[i].x);
+                            v[it][2 * i + 1] += __uint_as_float(q[i].z);
+                        }
+                    } else {
+                        const float4 *p0 = reinterpret_cast<const float4 *>(base + (size_t)b * 32);
+                        const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1);
+                        v[it][0] += a0.x; v[it][1] += a0.y; v[it][2] += a0.z; v[it][3] += a0.w;
+                        v[it][4] += a1.x; v[it][5] += a1.y; v[it][6] += a1.z; v[it][7] += a1.w;
+                    }
                 }
                 if (blockIdx.x == 0 && P.sum_out) {
                     float4 *dst = reinterpret_cast<float4 *>(P.sum_out + (size_t)b * 8);
@@ -503,8 +531,20 @@ __device__ __forceinline__ bool finish_tile_m1(const StackParams &sp, const Stac
         return false;
     }
     if (t != 0) return J.has_peers != 0;
-    if (row_a < J.n) J.out[0][row_a] = ya;
-    if (row_b < J.n) J.out[0][row_b] = yb;
+    if (J.out[0]) {
+        if (row_a < J.n) J.out[0][row_a] = ya;
+        if (row_b < J.n) J.out[0][row_b] = yb;
+    }
+    if (J.has_ll) {
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            unsigned long long *dst = J.ll_out[r];
+            if (dst) {
+                if (row_a < J.n) asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(dst + row_a), "r"(__float_as_uint(ya)), "r"(tag) : "memory");
+                if (row_b < J.n) asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(dst + row_b), "r"(__float_as_uint(yb)), "r"(tag) : "memory");
+            }
+        }
+    }
     if (J.has_peers) {
         // the other ranks' copies of this output (peer stores over NVLink)
 #pragma unroll
@@ -635,7 +675,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             const bool writes = blockIdx.x < ((P.kparts > 1u && P.sliced) ? P.kparts : 1u);
             const uint32_t o_lo = writes ? c_lo * 16u : 0u, o_hi = writes ? c_hi * 16u : 0u;
             if (P.x_kind == kRebuildH) rebuild_from_h<WARPS>(P, X, cs4 * 16u, c_hi * 16u, o_lo, o_hi);
-            else if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi);
+            else if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase);
             if (sp.trace && threadIdx.x == 0) trace_slot()[2] = stack_ns();
         }
 

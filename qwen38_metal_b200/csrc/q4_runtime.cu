@@ -139,6 +139,7 @@ struct q4b_runtime {
     // Deferred projections (run behind a barrier's arrival) are off unless asked for: measured on B200 the extra runs
     // of chunks they create cost more than the barrier time they cover.
     bool chain_no_fusion = false, chain_no_deferral = true;
+    bool chain_no_handoff = false;     // keep a barrier between a projection and the RMS-norm that consumes it
     bool chain_split_tiles = true;     // a phase with fewer tiles than warps gives every tile the same number of warps
     uint32_t chain_flags = 0;
     uint64_t failures = 0;             // bounded waits that ran out (finish() saw the error flag)
@@ -426,6 +427,7 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     if (const char *mode = getenv("Q4B_CHAIN_SPLIT")) rt->chain_split_tiles = strcmp(mode, "equal") != 0;
     if (const char *fl = getenv("Q4B_CHAIN_FLAGS")) rt->chain_flags = (uint32_t)strtol(fl, nullptr, 10);
     if (const char *plain = getenv("Q4B_CHAIN_PLAIN")) rt->chain_no_fusion = strtol(plain, nullptr, 10) != 0;  // no gate/up fusion
+    if (const char *hand = getenv("Q4B_CHAIN_HANDOFF")) rt->chain_no_handoff = strtol(hand, nullptr, 10) == 0;
     if (const char *defer = getenv("Q4B_CHAIN_DEFER")) rt->chain_no_deferral = strtol(defer, nullptr, 10) == 0;
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
     if (rt->force_variant == "stream") rt->gemm_min_m = 0xffffffffu;   // never use the tensor-core GEMM
@@ -1030,6 +1032,9 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         uint32_t k, k_total, k_begin;
         int pair_a = -1, pair_b = -1;  // jobs fused with the SwiGLU of the next stage
         std::vector<int> deferred;     // jobs nothing later reads
+        // Tagged hand-off to the next stage (its RMS-norm source is this job's output): 0 none, 1 through a buffer of
+        // the chain (one GPU, or an output that stays local), 2 through the ranks' exchange arenas
+        int ll_job = -1, ll_mode = 0;
     };
     std::vector<StageJobs> sj(n_stages);
     uint32_t halfs[2] = {0, 0};
@@ -1068,6 +1073,7 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     std::vector<q4::StackJob> jobs;
     std::vector<uint32_t> phase_stage, phase_role;
     std::vector<std::pair<size_t, size_t>> pair_fixups;  // (job index, pair ordinal): h buffer and amax word assigned below
+    std::vector<std::pair<size_t, uint32_t>> ll_fixups;  // (job index, stage): tagged hand-off buffers assigned below
     std::vector<uint32_t> pair_k;
     std::vector<uint32_t> pair_of_stage;
     std::vector<std::vector<ByteRange>> reads(n_stages);
@@ -1081,11 +1087,14 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     phase_stage.clear();
     phase_role.clear();
     pair_fixups.clear();
+    ll_fixups.clear();
     pair_k.clear();
     pair_of_stage.assign(n_stages, 0xffffffffu);
     for (StageJobs &J : sj) {
         J.pair_a = J.pair_b = -1;
         J.deferred.clear();
+        J.ll_job = -1;
+        J.ll_mode = 0;
     }
     // ---- fusion and deferral ----
     for (uint32_t si = 0; si + 1 < n_stages; ++si) {
@@ -1101,6 +1110,22 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
                 !has_peer_out(si, ub)) {
                 sj[si].pair_a = ga;
                 sj[si].pair_b = ub;
+            }
+        }
+        // tagged hand-off: the next stage is the RMS-norm of this stage's output (one job, whole) or of the ranks'
+        // partial outputs of it (arena slots wide enough for two tagged copies: 16 bytes per element)
+        if (N.x_kind == Q4B_X_RMS && !rt->chain_no_handoff) {
+            const uint64_t parts = N.src_parts ? N.src_parts : 1;
+            for (uint32_t i = 0; i < S.n_jobs; ++i) {
+                if (sj[si].res[i].n != N.k) continue;
+                if (parts == 1 && (const void *)S.outputs[i] == N.src0 && !has_peer_out(si, i)) {
+                    sj[si].ll_job = (int)i;
+                    sj[si].ll_mode = 1;
+                } else if (peers && parts == peers->world && has_peer_out(si, i) && N.src_part_stride >= 16 * N.k &&
+                           (uintptr_t)S.outputs[i] == (uintptr_t)N.src0 + (uint64_t)peers->rank * N.src_part_stride) {
+                    sj[si].ll_job = (int)i;
+                    sj[si].ll_mode = 2;
+                }
             }
         }
         // deferral: outputs that no later stage (and not the token reduction) reads
@@ -1164,7 +1189,11 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
             tiles += job_tiles;
             units += (uint64_t)job_tiles * j.vcpt;
             vcpt_max = j.vcpt > vcpt_max ? j.vcpt : vcpt_max;
-            if (!pair && has_peer_out(si, stage_job)) {
+            if (!pair && (int)stage_job == J.ll_job && role == 0) {
+                j.has_ll = 1;
+                ll_fixups.push_back({jobs.size(), si});
+                if (J.ll_mode == 2) j.out[0] = j.out[1] = nullptr;  // the arena slots hold tagged words, not floats
+            } else if (!pair && has_peer_out(si, stage_job)) {
                 j.has_peers = 1;
                 for (uint32_t r = 0; r < peers->world; ++r)
                     j.peer_out[r] = r == peers->rank ? nullptr : S.peer_outputs[(size_t)stage_job * 8 + r];
@@ -1186,7 +1215,11 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         const uint64_t min_chunks = (vcpt_max + 31u) / 32u;
         P.tiles = tiles;
         const uint32_t tile_groups = (tiles + warps - 1u) / warps;  // blocks that hold every tile once, one tile per warp
-        if (rt->chain_split_tiles && tile_groups <= (uint32_t)rt->sm_count) {
+        uint32_t best_parts = tile_groups <= (uint32_t)rt->sm_count ? (uint32_t)rt->sm_count / tile_groups : 0u;
+        if (best_parts > cpt / (uint32_t)min_chunks) best_parts = cpt / (uint32_t)min_chunks;
+        if (best_parts > 32u) best_parts = 32u;
+        // (worth it only while it keeps at least 85 % of the warps busy; else the plain equal split of units)
+        if (rt->chain_split_tiles && best_parts >= 1u && (uint64_t)tiles * best_parts * 100u >= (uint64_t)grid_warps * 85u) {
             // Fewer tiles than warps: every tile is cut into the same number of equal parts, one per warp, so a warp
             // has exactly one run of chunks (one pipeline ramp, at most one partial-sum exchange) per phase. The equal
             // split of units yields this when all tiles count the same and the warps are a multiple of the tiles. With
@@ -1245,10 +1278,12 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         M.x_bf16_out = (uint16_t *)S.x_bf16_out;
         M.sum_out = (float *)S.sum_out;
         bool global = false;
-        for (uint32_t i = 0; i < S.n_jobs; ++i) global = global || has_peer_out(si, i);
+        for (uint32_t i = 0; i < S.n_jobs; ++i) global = global || (has_peer_out(si, i) && (int)i != J.ll_job);
         // the last stage's arrival publishes the logits; without a token reduction only peers would need it
         const bool last = si + 1 == n_stages;
         M.arrive_kind = global ? q4::kSyncGlobal : (last && !logits) ? q4::kSyncNone : q4::kSyncLocal;
+        // the next stage polls the tags of its source instead of waiting at a barrier
+        if (!last && J.ll_job >= 0 && !global) M.arrive_kind = q4::kSyncNone;
         prev_arrive = M.arrive_kind;
         any_global = any_global || global;
         // behind this stage's arrival: the carried half of the previous stage's deferred jobs, then the first part of
@@ -1316,6 +1351,49 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     for (auto &fx : pair_fixups) {
         jobs[fx.first].h_out = (uint16_t *)(hbuf + h_off[fx.second]);
         jobs[fx.first].amax = (unsigned int *)(reset + 256 + fx.second * 4);
+    }
+    // tagged hand-offs: where the producer stores its {value, tag} words and what the consumer's rebuild polls
+    {
+        size_t ll_total = 0;
+        for (auto &fx : ll_fixups)
+            if (sj[fx.second].ll_mode == 1) ll_total += ((size_t)jobs[fx.first].n * 8 + 255) & ~(size_t)255;
+        uint8_t *llbuf = nullptr;
+        if (ll_total) {
+            e = build.alloc((void **)&llbuf, ll_total, true);
+            if (e != cudaSuccess) return fail_cuda(e, "decode chain allocation");
+        }
+        size_t ll_used = 0;
+        uint32_t arena_handoffs = 0;
+        for (auto &fx : ll_fixups) {
+            const uint32_t si = fx.second;
+            q4::StackJob &j = jobs[fx.first];
+            size_t producer = 0, consumer = 0;
+            for (size_t pi = 0; pi < phases.size(); ++pi) {
+                if (phase_role[pi] != 0) continue;
+                if (phase_stage[pi] == si) producer = pi;
+                if (phase_stage[pi] == si + 1) consumer = pi;
+            }
+            q4::StackPhase &C = phases[consumer];
+            C.src_tagged = 1;
+            C.src_tag_phase = (uint32_t)producer;
+            if (sj[si].ll_mode == 1) {
+                j.ll_out[0] = (unsigned long long *)(llbuf + ll_used);
+                C.src0 = llbuf + ll_used;
+                C.src_parts = 1;
+                C.src_part_stride = 0;
+                ll_used += ((size_t)j.n * 8 + 255) & ~(size_t)255;
+            } else {
+                // two copies per arena slot, used alternately by successive hand-offs: a rank may be one hand-off ahead
+                // of the slowest reader of the previous one, never two
+                const size_t copy = (size_t)(arena_handoffs++ & 1u) * j.n * 8;
+                const q4b_stage &S = stages[si];
+                for (uint32_t r = 0; r < peers->world; ++r) {
+                    uint8_t *slot = r == peers->rank ? (uint8_t *)S.outputs[sj[si].ll_job] : (uint8_t *)S.peer_outputs[(size_t)sj[si].ll_job * 8 + r];
+                    j.ll_out[r] = slot ? (unsigned long long *)(slot + copy) : nullptr;
+                }
+                C.src0 = (const uint8_t *)stages[si + 1].src0 + copy;
+            }
+        }
     }
     for (size_t pi = 0; pi < phases.size(); ++pi) {
         if (phases[pi].x_kind != q4::kRebuildH) continue;

@@ -29,6 +29,10 @@ struct StackJob {
     const uint8_t *b[2];   // biases
     float *out[2];         // fp32 results per side, indexed by row; pair: either may be null
     float *peer_out[kMaxPeers];  // other ranks' copies of out[0] (ordinary jobs), null where not wanted
+    // Tagged hand-off (ordinary jobs): every result is also stored as an 8-byte {value, tag} word into this GPU's copy
+    // and every other rank's copy of a vector that the next stage's rebuild polls -- value and tag travel in one store,
+    // so neither a fence nor a barrier stands between producer and consumer, on one GPU or across NVLink.
+    unsigned long long *ll_out[kMaxPeers];  // indexed by row; null entries are skipped; all null: no hand-off
     uint16_t *h_out;       // pair: bf16(silu(a) * b), indexed by row
     unsigned int *amax;    // pair: running maximum of |h| as fp32 bits (zero at launch)
     uint32_t n;            // rows per side
@@ -40,6 +44,8 @@ struct StackJob {
                            // empty, so a job whose chunks cost more -- weights at a byte offset -- gets fewer per warp)
     uint32_t pair;
     uint32_t has_peers;
+    uint32_t has_ll;
+    uint32_t pad;
 };
 
 enum : uint32_t { kRebuildNone = 0, kRebuildBf16 = 1, kRebuildSwiglu = 2, kRebuildRms = 3, kRebuildH = 4 };
@@ -62,6 +68,8 @@ struct StackPhase {
     uint32_t x_kind;              // how the activation is rebuilt after the wait (kRebuild*)
     const void *src0, *src1;      // Bf16: bf16[k]; Swiglu: fp32 gate[k], up[k]; Rms: fp32 [src_parts][k]; H: bf16[k], amax word
     uint32_t src_parts, src_part_stride;  // Rms: the vector is the sum, in order, of src_parts vectors this many bytes apart
+    uint32_t src_tagged;          // Rms: the source vectors are {value, tag} words written by phase src_tag_phase of this
+    uint32_t src_tag_phase;       //      launch; the rebuild polls until every word carries that phase's tag
     uint16_t *x_bf16_out;         // optional: block 0 stores the bf16 activation it built
     float *sum_out;               // optional (Rms): block 0 stores the summed fp32 vector
     float eps;

@@ -145,13 +145,15 @@ class SyntheticStack:
         if jobs:
             self.rt.matmul_batch_device(x_ptr, capi.Q4B_BF16, 1, k, jobs, ptrs, 0, stream)
 
-    def build_chain(self):
-        """The whole token as one persistent kernel (single GPU): stage list for `CudaRuntime.chain_create`."""
+    def build_chain(self, layers=None):
+        """The whole token as one persistent kernel (single GPU): stage list for `CudaRuntime.chain_create`.
+        `layers`: only the first so many layers, then lm_head (shallow chains are what different evaluation orders can
+        be compared on: the stack amplifies last-bit differences by about an order of magnitude per layer)."""
         if self.world != 1:
             raise ValueError("the persistent decode chain covers one GPU; sharded stacks use decode_token with gathers")
         stages = []
         gate, up = self.outs[self.gate_i], self.outs[self.up_i]
-        for layer in range(self.layers):
+        for layer in range(self.layers if layers is None else layers):
             projs = self.proj[layer]
             first = layer == 0
             stages.append({"x_kind": capi.X_BF16 if first else capi.X_RMS, "k": self.hidden,
@@ -169,15 +171,15 @@ class SyntheticStack:
     def sharded_arena_bytes(self) -> int:
         """Size of the exchange arena of `build_chain_sharded`: one partial down output per rank, the barrier words
         and the token candidates."""
-        return self.world * ((self.hidden * 4 + 255) & ~255) + 512
+        return self.world * ((self.hidden * 16 + 255) & ~255) + 512
 
-    def build_chain_sharded(self, dist, arenas=None):
+    def build_chain_sharded(self, dist, arenas=None, layers=None):
         """The whole token as one persistent kernel per rank. Projections of the hidden activation are row-sharded;
         gate and up are fused into the slice of the SwiGLU vector this rank owns, and the down projection is cut
         along K so that each rank consumes exactly that slice: it multiplies inputs [r0, r1) of the whole down
         matrix (read in place through strided rows) and stores its partial output into every rank's exchange arena
-        with peer stores. The next activation is the RMS-norm of the partial outputs added in rank order -- one
-        cross-GPU barrier per layer and no collective library on the data path. Summation order differs from the
+        with peer stores, as tagged words that the next stage's rebuild polls. The next activation is the RMS-norm of
+        the partial outputs added in rank order -- no cross-GPU barrier and no collective library on the data path. Summation order differs from the
         single-GPU chain (fp32 partial sums per rank), so results agree to fp32 rounding, not bit for bit.
         `dist` (torch.distributed) only carries the 64-byte IPC handles at set-up. `arenas` (tests): exchange arenas
         already mapped here, one base pointer per rank, in place of the IPC exchange."""
@@ -186,7 +188,9 @@ class SyntheticStack:
         def align(n):
             return (n + 255) & ~255
 
-        part_stride = align(self.hidden * 4)
+        # a slot per rank, wide enough for two copies of the partial output as 8-byte {value, tag} words: the chain then
+        # hands the partials over without a fence or a cross-GPU barrier (q4b_stage: src_part_stride >= 16 k)
+        part_stride = align(self.hidden * 16)
         off_parts, off_flags = 0, world * part_stride
         off_cand = off_flags + 256
         size = off_cand + 256
@@ -211,7 +215,7 @@ class SyntheticStack:
             raise ValueError("the K-sharded down projection needs gate/up slices that are multiples of 128 rows")
         rms_src = {"src0": base + off_parts, "src_parts": world, "src_part_stride": part_stride, "sum_out": self.d.data_ptr()}
         stages = []
-        for layer in range(self.layers):
+        for layer in range(self.layers if layers is None else layers):
             jobs, outs = [], []
             for p, o in zip(self.proj[layer], self.outs):
                 if p.job is not None:
@@ -236,11 +240,11 @@ class SyntheticStack:
             dist.barrier()  # every arena is mapped everywhere before the first launch
         return rt.chain_create(stages, self.logits.data_ptr(), p.rows, p.row0, self.token.data_ptr(), self.best.data_ptr(), peers)
 
-    def decode_token(self, stream: int = 0, gather=None) -> None:
+    def decode_token(self, stream: int = 0, gather=None, layers=None) -> None:
         """Enqueue one token on `stream` (a raw cudaStream_t). `gather(tensor, proj)` makes a row-sharded
-        output whole on every rank; it is None on one GPU."""
+        output whole on every rank; it is None on one GPU. `layers`: only the first so many layers, then lm_head."""
         rt = self.rt
-        for layer in range(self.layers):
+        for layer in range(self.layers if layers is None else layers):
             projs = self.proj[layer]
             self._grouped(self.x.data_ptr(), self.hidden, projs, self.outs, stream)
             gate, up = self.outs[self.gate_i], self.outs[self.up_i]
