@@ -53,6 +53,7 @@ __device__ __forceinline__ void lds_f32_keep(float &v, uint32_t addr, bool pred)
     asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q ld.shared.f32 %0, [%1];\n\t}" : "+f"(v) : "r"(addr), "r"((uint32_t)pred) : "memory");
 }
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void prefetch_l1(const void *p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
 // ---------------------------------------------------------------------------------------------------------
 // Barriers. Every block arrives exactly once per barrier and every block makes the same sequence of arrivals, so
@@ -656,12 +657,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
         const uint32_t cs4 = c_lo & ~3u;
         // pointers such that chunk cs4 lands at the start of the buffer
         const XBuf X{(second ? xp1 : xp0) - (size_t)cs4 * kXChunkBytes, (second ? xsum1 : xsum0) - (size_t)cs4 * 2u, misc + (second ? 1 : 0)};
-        // descriptors of the phase after this one: bring them into L2 while this one runs
-        if (warp == 1 && ph + 2 < sp.n_phases) {
-            const StackPhase &N = sp.phases[ph + 2];
-            if (lane == 0) prefetch_l2(&N);
-            const uint32_t lines = (N.n_jobs * (uint32_t)sizeof(StackJob) + 127u) / 128u;
-            if (lane >= 1 && lane <= lines) prefetch_l2(reinterpret_cast<const uint8_t *>(sp.jobs + N.job_begin) + (lane - 1u) * 128u);
+        // Descriptors ahead: the phase after the next one into L2, the next one (whose first run of chunks every warp
+        // sets up at the end of this phase, a chain of dependent loads) into this SM's L1.
+        if (warp == 1) {
+            if (ph + 2 < sp.n_phases) {
+                const StackPhase &N2 = sp.phases[ph + 2];
+                if (lane == 0) prefetch_l2(&N2);
+                const uint32_t lines = (N2.n_jobs * (uint32_t)sizeof(StackJob) + 127u) / 128u;
+                if (lane >= 1 && lane <= lines) prefetch_l2(reinterpret_cast<const uint8_t *>(sp.jobs + N2.job_begin) + (lane - 1u) * 128u);
+            }
+            if (ph + 1 < sp.n_phases) {
+                const StackPhase &N1 = sp.phases[ph + 1];
+                if (lane < 2) prefetch_l1(reinterpret_cast<const uint8_t *>(&N1) + lane * 128u);
+                const uint32_t lines = (N1.n_jobs * (uint32_t)sizeof(StackJob) + 127u) / 128u;
+                if (lane >= 2 && lane < 2u + lines) prefetch_l1(reinterpret_cast<const uint8_t *>(sp.jobs + N1.job_begin) + (lane - 2u) * 128u);
+            }
         }
         if (P.wait_kind != kSyncNone || P.x_kind != kRebuildNone) {
             if (sp.trace && threadIdx.x == 0) trace_slot()[0] = stack_ns();
@@ -703,16 +713,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                 if (nworker < N.workers) {
                     const Q4Split nsplit{N.units, N.cpt, N.workers};
                     const uint32_t nu = (uint32_t)q4_split_begin(nsplit, nworker), nu1 = (uint32_t)q4_split_begin(nsplit, nworker + 1);
+                    if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 58] = stack_ns() + (nu & 0);
                     if (nu < nu1) {
                         job_rel = 0;
                         segment_setup(N, sp.jobs, nu, nu1, job_rel, lane, sg);
+                        if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 59] = stack_ns() + ((uint32_t)(uintptr_t)sg.wa & 0);
                         segment_prologue(sg, ring, pring, lane);
                         prefetched = true;
+                        if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 60] = stack_ns();
                     }
                 }
             }
         };
-        if (!more) request_next_phase();
         const uint32_t xp_addr = (uint32_t)__cvta_generic_to_shared(X.xp) + (g & 3u) * 128u + t * 32u;
         const uint32_t xsum_addr = (uint32_t)__cvta_generic_to_shared(X.xsum) + (t >> 1) * 4u;
         while (more) {
@@ -810,17 +822,20 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
                 }
                 cp_async_wait<0>();
                 __syncwarp();
-                // the ring is free: request the next run of chunks before this tile is finished, so that the finish
-                // (a round trip to the other contributors' slots for a split tile) overlaps the load latency
+                // the ring is free: within a phase the next run of chunks is requested before this tile is finished, so
+                // that the finish (a round trip to the other contributors' slots for a split tile) overlaps the load
+                // latency. After the last run the order is the other way round: results and arrival first -- other
+                // blocks wait for them -- then the next phase's first weights (pushing 8 KB per warp into a memory
+                // system that every warp floods at the same moment takes a few microseconds).
+                if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 56] = stack_ns();
                 const TileEnd te{sg.job, sg.tile_local, sg.tile_row, sg.c0v, sg.c1v};
                 u += sg.c1v - sg.c0v;
                 more = u < u1;
                 if (more) {
                     segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
                     segment_prologue(sg, ring, pring, lane);
-                } else {
-                    request_next_phase();
                 }
+                if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 57] = stack_ns();
                 // digits back together: a lane's columns are digits (0, 1) of its group for even t, (2, none) for odd t
                 const float w0 = (t & 1u) ? 65536.f : 1.f, w1 = (t & 1u) ? 0.f : 256.f;
                 const float part_a = fmaf(acc[1], w1, acc[0] * w0), part_b = fmaf(acc[3], w1, acc[2] * w0);
@@ -839,6 +854,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             ++sync.local_gen;
             if (P.arrive_kind == kSyncGlobal) ++sync.global_gen;
         }
+        request_next_phase();
     }
 
     // ---- logits -> token: per-block candidates, barrier, block 0 picks (ties to the lowest index) ----
