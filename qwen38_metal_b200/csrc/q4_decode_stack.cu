@@ -302,6 +302,11 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
                     v[it][2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
                     v[it][2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
                 }
+            } else if (P.x_kind == kRebuildF32) {
+                const float4 *p0 = reinterpret_cast<const float4 *>(static_cast<const float *>(P.src0) + (size_t)b * 8);
+                const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1);
+                v[it][0] = a0.x; v[it][1] = a0.y; v[it][2] = a0.z; v[it][3] = a0.w;
+                v[it][4] = a1.x; v[it][5] = a1.y; v[it][6] = a1.z; v[it][7] = a1.w;
             } else if (P.x_kind == kRebuildSwiglu) {
                 const float4 *p0 = reinterpret_cast<const float4 *>(static_cast<const float *>(P.src0) + (size_t)b * 8);
                 const float4 *p1 = reinterpret_cast<const float4 *>(static_cast<const float *>(P.src1) + (size_t)b * 8);
@@ -598,7 +603,7 @@ __device__ __forceinline__ void chunk_mma_i8(const uint4 &cwa, const uint4 &cwb,
 __device__ __forceinline__ float small_int_to_float(int i) { return __int_as_float(i + 0x4B400000) - 12582912.0f; }
 
 template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_constant__ StackParams sp) {
+__device__ __forceinline__ void stack_body(const StackParams &sp) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -625,6 +630,30 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
 
     unsigned long long *gbase_smem = reinterpret_cast<unsigned long long *>(misc + 68);
     SyncState sync{0u, 0u, gbase_smem};
+    bool prefetched = false;
+    Segment sg;
+    uint32_t job_rel = 0;
+    // Weights of a phase's first run of chunks depend on nothing, so they are requested as soon as the ring is free:
+    // at the very start of the kernel for the first phase, and for every later phase once the warp has delivered the
+    // results of the phase before and arrived at its barrier.
+    auto request_phase = [&](uint32_t next) {
+        prefetched = false;
+        if (next < sp.n_phases) {
+            const StackPhase &N = sp.phases[next];
+            const uint32_t nworker = phase_worker(N, warp, WARPS);
+            if (nworker < N.workers) {
+                const Q4Split nsplit{N.units, N.cpt, N.workers};
+                const uint32_t nu = (uint32_t)q4_split_begin(nsplit, nworker), nu1 = (uint32_t)q4_split_begin(nsplit, nworker + 1);
+                if (nu < nu1) {
+                    job_rel = 0;
+                    segment_setup(N, sp.jobs, nu, nu1, job_rel, lane, sg);
+                    segment_prologue(sg, ring, pring, lane);
+                    prefetched = true;
+                }
+            }
+        }
+    };
+    request_phase(0);
     if (threadIdx.x == 0) {
         *arrive_smem = 0;
         *amax_smem = 0;
@@ -634,10 +663,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
     __syncthreads();
     // tags of the split-tile partial slots: unique per launch and phase, never zero
     const uint32_t tag_base = reinterpret_cast<uint32_t *>(misc)[3] * kMaxPhases + 1u;
-
-    bool prefetched = false;
-    Segment sg;
-    uint32_t job_rel = 0;
 
     for (uint32_t ph = 0; ph < sp.n_phases; ++ph) {
         const StackPhase &P = sp.phases[ph];
@@ -703,28 +728,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
             segment_prologue(sg, ring, pring, lane);
         }
-        // weights of the next phase's first run of chunks: they depend on nothing, so they are requested as soon as the
-        // ring is free -- before this phase's last tile is finished and before any barrier
-        auto request_next_phase = [&]() {
-            prefetched = false;
-            if (ph + 1 < sp.n_phases) {
-                const StackPhase &N = sp.phases[ph + 1];
-                const uint32_t nworker = phase_worker(N, warp, WARPS);
-                if (nworker < N.workers) {
-                    const Q4Split nsplit{N.units, N.cpt, N.workers};
-                    const uint32_t nu = (uint32_t)q4_split_begin(nsplit, nworker), nu1 = (uint32_t)q4_split_begin(nsplit, nworker + 1);
-                    if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 58] = stack_ns() + (nu & 0);
-                    if (nu < nu1) {
-                        job_rel = 0;
-                        segment_setup(N, sp.jobs, nu, nu1, job_rel, lane, sg);
-                        if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 59] = stack_ns() + ((uint32_t)(uintptr_t)sg.wa & 0);
-                        segment_prologue(sg, ring, pring, lane);
-                        prefetched = true;
-                        if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 60] = stack_ns();
-                    }
-                }
-            }
-        };
         const uint32_t xp_addr = (uint32_t)__cvta_generic_to_shared(X.xp) + (g & 3u) * 128u + t * 32u;
         const uint32_t xsum_addr = (uint32_t)__cvta_generic_to_shared(X.xsum) + (t >> 1) * 4u;
         while (more) {
@@ -854,7 +857,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             ++sync.local_gen;
             if (P.arrive_kind == kSyncGlobal) ++sync.global_gen;
         }
-        request_next_phase();
+        request_phase(ph + 1u);
     }
 
     // ---- logits -> token: per-block candidates, barrier, block 0 picks (ties to the lowest index) ----
@@ -925,17 +928,41 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_co
             }
         }
     }
-    // The launch is over once every block has got here: only then may the words that the next launch reads at its start
-    // change (every block read them before its first arrival).
-    phase_arrive<WARPS>(sp, kSyncLocal, sync, arrive_smem, false, lane, nullptr);
-    ++sync.local_gen;
-    if (blockIdx.x == 0) {
-        if (!phase_wait(sp, kSyncLocal, sync)) return;
-        if (threadIdx.x == 0) {
-            *sp.launch_seq = reinterpret_cast<uint32_t *>(misc)[3] + 1u;
+    // End of the launch. Every block counts itself out; the block that counts last -- every other block has finished,
+    // and every block read the launch count before it did anything -- puts the words back that the next launch expects:
+    // barrier counter and running maxima to zero, the launch count (tags of partial slots and hand-offs) one further,
+    // the cross-GPU arrivals this launch used up. So no memset precedes a launch. (A launch that gave up on a wait
+    // leaves them inconsistent; the host repairs them before the next launch.)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(sp.local_bar + 1, 1u);
+        if (done + 1u == gridDim.x) {
+            __threadfence();
+            sp.local_bar[0] = 0;
+            sp.local_bar[1] = 0;
+            for (uint32_t i = 0; i < sp.n_amax; ++i) sp.amax_words[i] = 0;
             if (sp.peers) *sp.peers->consumed = *gbase_smem + (unsigned long long)sync.global_gen * sp.peers->world;
+            *sp.launch_seq = reinterpret_cast<uint32_t *>(misc)[3] + 1u;
         }
     }
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_constant__ StackParams sp) {
+    stack_body<WARPS>(sp);
+}
+
+// The same kernel for a program of ONE phase that travels in the kernel parameters: a single grouped decode launch
+// (q4b_matvec_batch and friends) builds its activation, streams its projections and stores its results in one launch,
+// without a device-side program or a host-to-device copy in front of it.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_inline_kernel(const __grid_constant__ InlineProgram prog) {
+    StackParams sp = prog.params;
+    sp.phases = &prog.phase;
+    sp.jobs = prog.jobs;
+    sp.n_phases = 1;
+    stack_body<WARPS>(sp);
 }
 
 }  // namespace q4
@@ -971,13 +998,30 @@ extern "C" int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1) {
     return blocks >= 1 ? 1 : 0;
 }
 
-// `reset_region`: the words that must be zero when the kernel starts (local arrival counter, running maxima).
-extern "C" cudaError_t q4k_stack_launch(const q4::StackParams *params, void *reset_region, size_t reset_bytes, int sm_count,
-                                        cudaStream_t stream) {
-    cudaError_t e = cudaMemsetAsync(reset_region, 0, reset_bytes, stream);
-    if (e != cudaSuccess) return e;
+extern "C" cudaError_t q4k_stack_launch(const q4::StackParams *params, int sm_count, cudaStream_t stream) {
     q4::StackParams sp = *params;
     void *args[] = {&sp};
     return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(q4::q4_stack_kernel<kStackWarps>), dim3(sm_count), dim3(kStackWarps * 32),
                                        args, q4k_stack_smem_bytes(sp.halfs[0], sp.halfs[1]), stream);
+}
+
+extern "C" int q4k_stack_inline_supported(uint32_t halfs) {
+    const size_t smem = q4k_stack_smem_bytes(halfs, 0);
+    if (cudaFuncSetAttribute(q4::q4_stack_inline_kernel<kStackWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4::q4_stack_inline_kernel<kStackWarps>, kStackWarps * 32, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return blocks >= 1 ? 1 : 0;
+}
+
+extern "C" cudaError_t q4k_stack_launch_inline(const q4::InlineProgram *program, int sm_count, cudaStream_t stream) {
+    q4::InlineProgram prog = *program;
+    void *args[] = {&prog};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(q4::q4_stack_inline_kernel<kStackWarps>), dim3(sm_count),
+                                       dim3(kStackWarps * 32), args, q4k_stack_smem_bytes(prog.params.halfs[0], 0), stream);
 }

@@ -149,6 +149,11 @@ struct q4b_runtime {
     Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
     Pool outs[q4::kMaxJobs];
     HostPool results;  // staging for downloads (host-buffer entry points)
+    // single decode launches (one activation row) run as a one-phase program of the persistent kernel
+    Pool inline_partials, inline_state;  // split-tile slots; [0] barrier words, [64] launch count
+    uint32_t inline_max_halfs = 0;       // longest activation the kernel's shared memory takes (0: path unavailable)
+    uint64_t inline_failures_seen = 0;
+    bool inline_off = false;
     uint64_t launches = 0;
     std::string force_variant;
     // per-kernel timing window (q4b_profile_begin/end)
@@ -247,6 +252,95 @@ int profile_close(q4b_runtime *rt, cudaStream_t stream, uint64_t bytes, uint64_t
     rt->prof_bytes += bytes;
     rt->prof_flops += flops;
     return Q4B_OK;
+}
+
+// One activation row: the persistent kernel as a one-phase program in the kernel parameters -- the activation is built
+// in shared memory by every block (no separate preparation kernel), projections are streamed on the integer
+// tensor-core path, split tiles are combined through tagged slots. One launch per call.
+int launch_single_row(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t k, const Resolved *jobs, uint32_t n_jobs,
+                      float *const *outs, cudaStream_t stream) {
+    const uint32_t warps = q4k_stack_warps(), grid_warps = (uint32_t)rt->sm_count * warps;
+    if (rt->inline_failures_seen != rt->failures) {
+        // a kernel gave up on a wait since the last launch: its counters and tags may be anywhere
+        Q4B_CUDA(cudaMemsetAsync(rt->inline_partials.ptr, 0, rt->inline_partials.capacity, stream), "decode launch repair");
+        Q4B_CUDA(cudaMemsetAsync(rt->inline_state.ptr, 0, 256, stream), "decode launch repair");
+        rt->inline_failures_seen = rt->failures;
+    }
+    q4::InlineProgram prog;
+    memset(&prog, 0, sizeof prog);
+    q4::StackPhase &P = prog.phase;
+    P.k = k;
+    P.kp = (k + 127u) & ~127u;
+    P.groups = k / 64;
+    P.cpt = (P.groups + 1u) / 2u;
+    P.n_jobs = n_jobs;
+    P.x_kind = x_dtype == Q4B_F32 ? q4::kRebuildF32 : q4::kRebuildBf16;
+    P.src0 = x_dev;
+    P.src_parts = 1;
+    const uint32_t cpt = P.cpt;
+    uint32_t tiles = 0;
+    uint64_t units = 0, bytes = 0, rows = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        q4::StackJob &j = prog.jobs[i];
+        j.w[0] = j.w[1] = jobs[i].w;
+        j.s[0] = j.s[1] = jobs[i].s;
+        j.b[0] = j.b[1] = jobs[i].b;
+        j.out[0] = j.out[1] = outs[i];
+        j.n = jobs[i].n;
+        j.rows_per_tile = 16;
+        j.b_row_offset = 8;
+        j.w_stride = k / 2;
+        j.p_stride = (k / 64) * 2;
+        j.tile_begin = tiles;
+        j.vcpt = cpt;
+        j.unit_begin = (uint32_t)units;
+        const uint32_t job_tiles = (jobs[i].n + 15u) / 16u;
+        tiles += job_tiles;
+        units += (uint64_t)job_tiles * cpt;
+        bytes += (uint64_t)jobs[i].n * (k / 2 + (uint64_t)P.groups * 4) + (uint64_t)jobs[i].n * 4;
+        rows += jobs[i].n;
+    }
+    if (units > 0xffffffffull) return fail(Q4B_UNSUPPORTED, "launch is too large");
+    P.tiles = tiles;
+    P.units = units;
+    // few tiles: every tile in equal parts, one per warp, a block on one part of sixteen tiles (it then builds only that
+    // slice of the activation); many tiles: equal runs of units
+    const uint32_t min_chunks = (cpt + 31u) / 32u;
+    const uint32_t tile_groups = (tiles + warps - 1u) / warps;
+    uint32_t parts = tile_groups <= (uint32_t)rt->sm_count ? (uint32_t)rt->sm_count / tile_groups : 0u;
+    if (parts > cpt / min_chunks) parts = cpt / min_chunks;
+    if (parts > 32u) parts = 32u;
+    uint64_t workers = grid_warps;
+    if (parts >= 1u && (uint64_t)tiles * parts * 100u >= (uint64_t)grid_warps * 70u) {
+        workers = (uint64_t)tiles * parts;
+        P.kparts = parts;
+        P.sliced = parts > 1u ? 1u : 0u;
+    } else {
+        if (workers > units / min_chunks) workers = units / min_chunks;
+        if (workers == 0) workers = 1;
+    }
+    P.workers = (uint32_t)workers;
+    q4::StackParams &sp = prog.params;
+    sp.halfs[0] = P.kp;
+    if (P.sliced) {
+        uint32_t chunks = 0;
+        for (uint32_t part = 0; part < P.kparts; ++part) {
+            const uint32_t lo = (cpt * part / P.kparts) & ~3u, hi = cpt * (part + 1u) / P.kparts;
+            chunks = hi - lo > chunks ? hi - lo : chunks;
+        }
+        sp.halfs[0] = (chunks + 1u) * 128u;
+    }
+    sp.local_bar = (unsigned int *)rt->inline_state.ptr;
+    sp.launch_seq = (unsigned int *)rt->inline_state.ptr + 64;
+    sp.error_flag = (int *)rt->error_flag.ptr;
+    sp.partials = (uint4 *)rt->inline_partials.ptr;
+    sp.max_workers = grid_warps;
+    sp.spin_limit = rt->chain_spin_limit;
+    sp.flags = rt->chain_flags;
+    if (int st = profile_open(rt, stream)) return st;
+    Q4B_CUDA(q4k_stack_launch_inline(&prog, rt->sm_count, stream), "decode launch");
+    rt->launches++;
+    return profile_close(rt, stream, bytes + (uint64_t)k * (x_dtype == Q4B_F32 ? 4 : 2), 2ull * rows * k);
 }
 
 // One streaming launch: up to kMaxJobs projections, up to 8 bf16 (2 fp32) activation rows.
@@ -352,6 +446,13 @@ int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, 
                    const std::vector<Resolved> &jobs, float *const *outs, uint32_t flags, cudaStream_t stream) {
     const bool tensor = (flags & Q4B_FLAG_TENSOR) ? true : (flags & Q4B_FLAG_STREAM) ? false : m >= rt->gemm_min_m;
     if (tensor) return enqueue_gemm(rt, x_dev, x_dtype, m, k, jobs, outs, flags, stream);
+    if (m == 1 && !(flags & Q4B_FLAG_ACCUMULATE) && rt->inline_max_halfs && k % 512 == 0 && k <= rt->inline_max_halfs && k <= q4k_stack_max_k()) {
+        for (size_t j0 = 0; j0 < jobs.size(); j0 += q4::kMaxJobs) {
+            const uint32_t nj = (uint32_t)((jobs.size() - j0) < (size_t)q4::kMaxJobs ? (jobs.size() - j0) : (size_t)q4::kMaxJobs);
+            if (int st = launch_single_row(rt, x_dev, x_dtype, (uint32_t)k, &jobs[j0], nj, outs + j0, stream)) return st;
+        }
+        return Q4B_OK;
+    }
     const uint32_t rows_per_launch = x_dtype == Q4B_F32 ? 2u : 8u;
     const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
     for (uint64_t m0 = 0; m0 < m; m0 += rows_per_launch) {
@@ -460,6 +561,22 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     if (e == cudaSuccess) e = cudaMemset(rt->counters.ptr, 0, rt->counters.capacity);
     if (e == cudaSuccess) e = rt->error_flag.ensure(256);
     if (e == cudaSuccess) e = cudaMemset(rt->error_flag.ptr, 0, rt->error_flag.capacity);
+    if (const char *off = getenv("Q4B_NO_INLINE")) rt->inline_off = strtol(off, nullptr, 10) != 0;
+    if (e == cudaSuccess && !rt->inline_off) {
+        // the largest activation for which the one-phase kernel is resident: try the chain's limit, then half of it
+        for (uint32_t halfs : {q4k_stack_max_k(), q4k_stack_max_k() / 2u, 8192u, 4096u}) {
+            if (q4k_stack_inline_supported(halfs)) {
+                rt->inline_max_halfs = halfs;
+                break;
+            }
+        }
+        if (rt->inline_max_halfs) {
+            e = rt->inline_partials.ensure((size_t)rt->sm_count * q4k_stack_warps() * 32 * sizeof(uint4));
+            if (e == cudaSuccess) e = cudaMemset(rt->inline_partials.ptr, 0, rt->inline_partials.capacity);
+            if (e == cudaSuccess) e = rt->inline_state.ensure(1024);
+            if (e == cudaSuccess) e = cudaMemset(rt->inline_state.ptr, 0, rt->inline_state.capacity);
+        }
+    }
     if (e != cudaSuccess) {
         q4b_runtime_destroy(rt);
         return fail_cuda(e, "scratch allocation");
@@ -480,6 +597,8 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
+    rt->inline_partials.release();
+    rt->inline_state.release();
     rt->results.release();
     for (cudaEvent_t ev : rt->prof_events) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) {
@@ -1436,6 +1555,8 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     sp.halfs[0] = halfs[0];
     sp.halfs[1] = halfs[1];
     sp.local_bar = (unsigned int *)reset;
+    sp.amax_words = (unsigned int *)(reset + 256);
+    sp.n_amax = (uint32_t)n_pairs;
     sp.error_flag = (int *)rt->error_flag.ptr;
     sp.partials = (uint4 *)partials;
     sp.launch_seq = (unsigned int *)counters;
@@ -1492,14 +1613,15 @@ extern "C" int q4b_chain_run_device(q4b_chain *chain, void *stream) {
     DeviceGuard guard(rt->device);
     if (chain->failures_seen != rt->failures) {
         // a bounded wait ran out on this runtime since the chain last ran. The counters of a multi-rank chain live
-        // on several GPUs and are out of step now; a single-GPU chain only needs the tags of its split-tile slots cleared (the launch count did not advance).
+        // on several GPUs and are out of step now; a single-GPU chain only needs the tags of its split-tile slots and its counters cleared (the launch that gave up did not put them back).
         if (chain->multi_rank)
             return fail(Q4B_POOL_POISONED, "a kernel gave up on a bounded wait: destroy this multi-rank chain, zero the arena on every rank and create it again");
         Q4B_CUDA(cudaMemsetAsync(chain->params.partials, 0, (size_t)q4::kPartialSets * chain->params.max_workers * 32 * sizeof(uint4), (cudaStream_t)stream),
                  "decode chain repair");
+        Q4B_CUDA(cudaMemsetAsync(chain->reset_region, 0, chain->reset_bytes, (cudaStream_t)stream), "decode chain repair");
         chain->failures_seen = rt->failures;
     }
-    Q4B_CUDA(q4k_stack_launch(&chain->params, chain->reset_region, chain->reset_bytes, rt->sm_count, (cudaStream_t)stream), "decode chain launch");
+    Q4B_CUDA(q4k_stack_launch(&chain->params, rt->sm_count, (cudaStream_t)stream), "decode chain launch");
     rt->launches++;
     return Q4B_OK;
 }
@@ -1612,6 +1734,10 @@ extern "C" int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, u
     if (int st = resolve_jobs(rt, jobs, n_jobs, m, k, &resolved)) return st;
     uint32_t fast = 0;
     for (const Resolved &r : resolved) fast += job_is_fast(r, (uint32_t)(k / 64)) ? 1u : 0u;
+    if (m == 1 && rt->inline_max_halfs && k % 512 == 0 && k <= rt->inline_max_halfs && k <= q4k_stack_max_k()) {
+        snprintf(text, text_len, "single_row_i8 one-phase persistent launch, jobs=%u (byte-addressed %u)", n_jobs, n_jobs - fast);
+        return Q4B_OK;
+    }
     const uint32_t rows = x_dtype == Q4B_F32 ? 2u : 8u;
     const uint32_t mb = (uint32_t)(m < rows ? m : rows);
     const uint32_t v = mb * (x_dtype == Q4B_F32 ? 3u : 1u);

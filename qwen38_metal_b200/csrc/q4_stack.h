@@ -48,7 +48,7 @@ struct StackJob {
     uint32_t pad;
 };
 
-enum : uint32_t { kRebuildNone = 0, kRebuildBf16 = 1, kRebuildSwiglu = 2, kRebuildRms = 3, kRebuildH = 4 };
+enum : uint32_t { kRebuildNone = 0, kRebuildBf16 = 1, kRebuildSwiglu = 2, kRebuildRms = 3, kRebuildH = 4, kRebuildF32 = 5 };
 enum : uint32_t { kSyncNone = 0, kSyncLocal = 1, kSyncGlobal = 2 };
 
 struct StackPhase {
@@ -93,7 +93,10 @@ struct StackParams {
     const StackJob *jobs;
     uint32_t n_phases;
     uint32_t halfs[2];        // capacity of the two activation buffers in inputs (3 bytes each); the second may be 0
-    unsigned int *local_bar;  // arrivals of this GPU's blocks; zero at launch
+    unsigned int *local_bar;  // [0] arrivals of this GPU's blocks, [1] blocks that have finished; zero at launch, put back
+                              // to zero by the last block of a launch
+    unsigned int *amax_words; // running maxima of the gate/up pairs (zero at launch, likewise)
+    uint32_t n_amax;
     int *error_flag;
     uint4 *partials;          // [kPartialSets][max_workers][32 lanes] of {sum a, tag, sum b, tag}
     unsigned int *launch_seq; // launches of this chain so far (read at the start, advanced at the end of the kernel)
@@ -112,6 +115,13 @@ struct StackParams {
     uint32_t dbg_phase;
 };
 
+// A program of one phase inside the kernel parameters (q4_stack_inline_kernel).
+struct InlineProgram {
+    StackParams params;  // phases, jobs and n_phases are ignored
+    StackPhase phase;
+    StackJob jobs[kMaxJobs];
+};
+
 constexpr uint32_t kFlagWarpFenceGpu = 1u;  // every warp fences at device scope before it arrives (default: block scope)
 
 constexpr uint32_t kTraceStamps = 8;  // wait begin, wait end, rebuild end, warp 0 units end, block's arrival, -, -, -
@@ -123,5 +133,7 @@ uint32_t q4k_stack_warps(void);
 uint32_t q4k_stack_max_k(void);       // longest activation the Bf16/Swiglu/Rms rebuilds handle
 size_t q4k_stack_smem_bytes(uint32_t halfs0, uint32_t halfs1);
 int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1);
-cudaError_t q4k_stack_launch(const q4::StackParams *params, void *reset_region, size_t reset_bytes, int sm_count, cudaStream_t stream);
+cudaError_t q4k_stack_launch(const q4::StackParams *params, int sm_count, cudaStream_t stream);
+int q4k_stack_inline_supported(uint32_t halfs);
+cudaError_t q4k_stack_launch_inline(const q4::InlineProgram *program, int sm_count, cudaStream_t stream);
 }
