@@ -166,6 +166,11 @@ int q4b_dequantize_row(q4b_runtime *rt, const q4b_job *job, uint64_t k, uint64_t
 int q4b_matmul_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
                             const q4b_job *jobs, uint32_t n_jobs, float *const *outputs_dev, uint32_t flags,
                             void *stream);
+/* q4_affine_mlp_mapped_batch on device buffers (src/metal_runtime.rs:4479-4689; fused 16-bit chain :4267-4474):
+ * out_dev is [m][down rows] fp32. From the tensor-core hand-over on, gate and up run as one launch that applies the
+ * SwiGLU in its epilogue and hands bf16 rows straight to the down projection. */
+int q4b_mlp_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k, const q4b_job *gate,
+                         const q4b_job *up, const q4b_job *down, float *out_dev, void *stream);
 /* tokens_dev[m] (u32) and, if not null, values_dev[m] (the winning logits); token ids are
  * offset by index_base (row-sharded vocabularies). */
 int q4b_argmax_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,

@@ -109,6 +109,7 @@ def load() -> C.CDLL:
         "q4b_mlp_batch": [vp, vp, i32, u64, u64, P(Job), P(Job), P(Job), vp],
         "q4b_dequantize_row": [vp, P(Job), u64, u64, vp],
         "q4b_matmul_batch_device": [vp, vp, i32, u64, u64, P(Job), u32, P(vp), u32, vp],
+        "q4b_mlp_batch_device": [vp, vp, i32, u64, u64, P(Job), P(Job), P(Job), vp, vp],
         "q4b_argmax_batch_device": [vp, vp, i32, u64, u64, P(Job), u32, vp, vp, vp],
         "q4b_swiglu_device": [vp, vp, vp, u64, vp, vp, vp],
         "q4b_rms_unit_bf16_device": [vp, vp, u32, u32, C.c_float, vp, vp],
@@ -184,7 +185,7 @@ EXPORTS = [
     "q4b_runtime_create", "q4b_runtime_destroy", "q4b_last_error", "q4b_status_name", "q4b_device_info",
     "q4b_shard_upload", "q4b_shard_alloc", "q4b_shard_write", "q4b_shard_read", "q4b_shard_count",
     "q4b_shard_info", "q4b_offset_is_aligned", "q4b_matvec_batch", "q4b_matmul_batch", "q4b_argmax_batch",
-    "q4b_mlp_batch", "q4b_matmul_add_batch", "q4b_dequantize_row", "q4b_matmul_batch_device",
+    "q4b_mlp_batch", "q4b_mlp_batch_device", "q4b_matmul_add_batch", "q4b_dequantize_row", "q4b_matmul_batch_device",
     "q4b_argmax_batch_device", "q4b_swiglu_device", "q4b_rms_unit_bf16_device", "q4b_synth_q4_device",
     "q4b_synth_bf16_device", "q4b_describe_dispatch", "q4b_launch_count", "q4b_profile_begin", "q4b_profile_end", "q4b_trace_enable", "q4b_trace_read", "q4b_device_status", "q4b_matvec_noalloc", "q4b_noalloc_last_error", "q4b_chain_create", "q4b_chain_run_device", "q4b_chain_run",
     "q4b_chain_set_spin_limit", "q4b_chain_phase_count", "q4b_chain_destroy", "q4b_chain_max_k", "q4b_chain_trace_read", "q4b_arena_create", "q4b_arena_open",

@@ -27,6 +27,8 @@
 // Every wait is bounded: a wait that runs out sets an error flag, the block drains and frees its TMEM.
 #include <cuda.h>
 
+#include <cstring>
+
 #include "q4_kernels.h"
 
 #include "q4_device.cuh"
@@ -67,6 +69,15 @@ struct GemmParams {
     uint32_t k_splits, split_blocks;  // parts, K stages per part
     uint64_t split_stride;            // floats between the partial outputs of consecutive parts
     int *error_flag;           // set non-zero when a bounded wait runs out
+    // Pair mode (fused MLP front half, src/metal_runtime.rs:4267-4474): every work item multiplies the same activation
+    // tile with 128 rows of the gate tensor (w, s, b; accumulator 0) and then with the same 128 rows of the up tensor
+    // (w2, s2, b2; accumulator 1); the epilogue holds both sums of an element in one thread and stores
+    // bf16(silu(gate) * up) (qwen38_swiglu_rows, shaders/qwen38.metal:4188-4198) as h_out[m][h_stride], in the
+    // element order of a prepared activation, i.e. ready to be the B operand of the down projection's GEMM.
+    const uint8_t *w2, *s2, *b2;
+    uint16_t *h_out;
+    uint32_t h_stride;
+    uint32_t pair;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -145,6 +156,15 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr)
         : "memory");
 }
+// 32 lanes x 16 consecutive fp32 columns
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major bf16 tile with 128-byte swizzle: rows are 128 bytes, groups
@@ -216,6 +236,7 @@ struct GemmSmem {
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                     const __grid_constant__ CUtensorMap tmap_w,
+                                                                    const __grid_constant__ CUtensorMap tmap_w2,
                                                                     const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t gemm_smem_raw[];
     using L = GemmSmem<BN>;
@@ -278,6 +299,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         const uint32_t lo = part_of(item) * p.split_blocks;
         return k_blocks_all - lo < p.split_blocks ? k_blocks_all - lo : p.split_blocks;
     };
+    const uint32_t subs = p.pair ? 2u : 1u;  // weight tiles per work item (pair mode: gate rows, then the same up rows)
 
     if (warp == 0) {
         // ---- TMA producer: activation tiles ----
@@ -287,7 +309,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
             for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const uint32_t tile = item % out_tiles, kb_lo = part_of(item) * p.split_blocks, k_blocks = stages_of(item);
                 const uint32_t m0 = (tile % p.tiles_m) * BN;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (uint32_t kbs = 0; kbs < k_blocks * subs; ++kbs, ++it) {
+                    const uint32_t kb = kbs < k_blocks ? kbs : kbs - k_blocks;
                     const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
                     if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(full_x(s), L::kBTileBytes);
@@ -303,11 +326,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tcount) {
                 const uint32_t k_blocks = stages_of(item);
-                const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+                // one accumulator per work item, two alternating; in pair mode an item takes both (gate, up) and
+                // the barriers of accumulator 0 stand for the pair
+                const uint32_t acc = p.pair ? 0u : (tcount & 1u), aph = p.pair ? (tcount & 1u) : ((tcount >> 1) & 1u);
                 if (!mbar_wait(acc_empty(acc), aph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (uint32_t kbs = 0; kbs < k_blocks * subs; ++kbs, ++it) {
+                    const uint32_t sub = kbs < k_blocks ? 0u : 1u, kb = kbs - sub * k_blocks;
+                    const uint32_t d_tmem = tmem_base + (acc + sub) * BN;
                     const uint32_t s = it % kGemmStages, ph = (it / kGemmStages) & 1u;
                     if (!mbar_wait(full_x(s), ph, abort_flag) || !mbar_wait(full_w(s), ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -332,11 +358,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
                 const uint32_t tile = item % out_tiles, kb_lo = part_of(item) * p.split_blocks;
                 const uint32_t w_tiles = (stages_of(item) + w_stages - 1) / w_stages;
                 const uint32_t n0 = (tile / p.tiles_m) * kTileN;
-                for (uint32_t wt = 0; wt < w_tiles; ++wt) {
+                for (uint32_t wts = 0; wts < w_tiles * subs && ok; ++wts) {
+                    const uint32_t sub = wts < w_tiles ? 0u : 1u, wt = wts - sub * w_tiles;
                     if (!mbar_wait(staged_empty(wb), ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(staged_full(wb), w_bytes);
                     // x is a byte offset from the (rounded-down) tensor base: a multiple of 16 in both forms
-                    tma_load_2d(smem_base + L::kWStageOffset + wb * w_bytes, &tmap_w, staged_full(wb), (int32_t)((kb_lo + wt * w_stages) * 32u), (int32_t)n0);
+                    tma_load_2d(smem_base + L::kWStageOffset + wb * w_bytes, sub ? &tmap_w2 : &tmap_w, staged_full(wb),
+                                (int32_t)((kb_lo + wt * w_stages) * 32u), (int32_t)n0);
                     if (++wb == w_bufs) {
                         wb = 0;
                         ph ^= 1u;
@@ -352,11 +380,42 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
         for (uint32_t item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++tcount) {
             const uint32_t tile = item % out_tiles;
             float *const out = p.out + (uint64_t)part_of(item) * p.split_stride;
-            const uint32_t acc = tcount & 1u, aph = (tcount >> 1) & 1u;
+            const uint32_t acc = p.pair ? 0u : (tcount & 1u), aph = p.pair ? (tcount & 1u) : ((tcount >> 1) & 1u);
             const uint32_t n0 = (tile / p.tiles_m) * kTileN, m0 = (tile % p.tiles_m) * BN;
             if (!mbar_wait(acc_full(acc), aph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t n = n0 + quarter * 32u + lane;
+            if (p.pair) {
+                // gate sums in accumulator 0, up sums in accumulator 1, the same lane (row) and column (activation row):
+                // h = bf16(silu(gate) * up), stored where the down projection's GEMM expects input n of activation row m
+                // (inside each block of 8 inputs the order is k0,k4,k1,k5,k2,k6,k3,k7)
+                const uint32_t pos = (n & ~7u) | ((n & 3u) << 1) | ((n >> 2) & 1u);
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16], u[16];
+                    tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + c0, r);
+                    tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + BN + c0, u);
+                    tmem_ld_wait();
+                    if (n < p.n) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t m = m0 + c0 + i;
+                            if (m < p.m) {
+                                // hardware exponential and reciprocal (as Metal's fast math in the reference's kernel):
+                                // their error is far below the bf16 rounding that follows, and this epilogue runs
+                                // while the tensor cores wait for the accumulators
+                                const float g = __uint_as_float(r[i]);
+                                const float h = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[i]);
+                                p.h_out[(uint64_t)m * p.h_stride + pos] = (uint16_t)float_to_bf16_bits(h);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty(acc));
+                continue;
+            }
 #pragma unroll 1
             for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -392,7 +451,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
             const uint32_t n0 = (tile / p.tiles_m) * kTileN;
             uint32_t grow = n0 + row;
             grow = grow < p.n ? grow : p.n - 1u;  // rows past N take a valid row's parameters and are never stored
-            const uint8_t *srow = p.s + ((uint64_t)grow * groups + kb_lo) * 2u, *brow = p.b + ((uint64_t)grow * groups + kb_lo) * 2u;
+            for (uint32_t sub = 0; sub < subs && ok; ++sub) {
+            const uint8_t *srow = (sub ? p.s2 : p.s) + ((uint64_t)grow * groups + kb_lo) * 2u, *brow = (sub ? p.b2 : p.b) + ((uint64_t)grow * groups + kb_lo) * 2u;
             // Scales and biases of eight stages come in one 16-byte load each (any byte alignment), one period ahead,
             // so that no load is waited for in the stage loop.
             auto params = [&](const uint8_t *base, uint32_t kb) {
@@ -457,6 +517,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) q4_gemm_tc_kernel(const __gri
                     }
                 }
             }
+            }
         }
     }
 
@@ -508,11 +569,12 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int BN>
-cudaError_t launch_gemm(const CUtensorMap &map, const CUtensorMap &wmap, const q4::GemmParams &p, uint32_t ctas, cudaStream_t stream) {
+cudaError_t launch_gemm(const CUtensorMap &map, const CUtensorMap &wmap, const CUtensorMap &wmap2, const q4::GemmParams &p, uint32_t ctas,
+                        cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(q4::q4_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)q4::GemmSmem<BN>::kTotal);
     if (e != cudaSuccess) return e;
-    q4::q4_gemm_tc_kernel<BN><<<ctas, q4::kGemmThreads, q4::GemmSmem<BN>::kTotal, stream>>>(map, wmap, p);
+    q4::q4_gemm_tc_kernel<BN><<<ctas, q4::kGemmThreads, q4::GemmSmem<BN>::kTotal, stream>>>(map, wmap, wmap2, p);
     return cudaGetLastError();
 }
 
@@ -565,6 +627,46 @@ extern "C" uint32_t q4k_gemm_k_splits(uint32_t m, uint32_t n, uint32_t k, uint32
     return (k_blocks + per - 1) / per;
 }
 
+namespace {
+
+// packed weights as a byte matrix [n][k/2] from the tensor's address rounded down to 16 bytes (TMA needs that;
+// the row pitch k/2 is a multiple of 32): 128-byte swizzled rows when the tensor is aligned, 80-byte windows else.
+// The matrix is declared 16 bytes wider than k/2 in the window form so the last window of a row is in range; the
+// extra bytes are the next row's first bytes or, after the last row, the padding every shard carries.
+bool encode_weight_map(EncodeTiledFn encode, CUtensorMap *wmap, const uint8_t *w, uint32_t n, uint32_t k) {
+    const uint32_t w_mis = (uint32_t)((uintptr_t)w & 15u);
+    const cuuint64_t wdims[2] = {(cuuint64_t)k / 2 + (w_mis ? 16u : 0u), n};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)k / 2};
+    const cuuint32_t wbox[2] = {w_mis ? q4::kWWindowPitch : q4::kWAlignedPitch, (cuuint32_t)q4::kTileN};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode(wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w - w_mis), wdims, wstrides, wbox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, w_mis ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool encode_activation_map(EncodeTiledFn encode, CUtensorMap *map, const uint16_t *xp, uint32_t m, uint32_t k, uint32_t bn) {
+    const cuuint64_t dims[2] = {k, m};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)q4::kTileK, bn};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(xp), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_by_tile(uint32_t bn, const CUtensorMap &map, const CUtensorMap &wmap, const CUtensorMap &wmap2, const q4::GemmParams &p,
+                           uint32_t ctas, cudaStream_t stream) {
+    switch (bn) {
+        case 256: return launch_gemm<256>(map, wmap, wmap2, p, ctas, stream);
+        case 128: return launch_gemm<128>(map, wmap, wmap2, p, ctas, stream);
+        case 64: return launch_gemm<64>(map, wmap, wmap2, p, ctas, stream);
+        case 32: return launch_gemm<32>(map, wmap, wmap2, p, ctas, stream);
+        default: return launch_gemm<16>(map, wmap, wmap2, p, ctas, stream);
+    }
+}
+
+}  // namespace
+
 // xp: prepared activations [m][k] bf16 (q4k_gemm_prepare_x), 16-byte aligned. One projection per launch. `parts`:
 // scratch for m * out_stride * q4k_gemm_k_splits(...) floats when that is more than one, else unused.
 extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_t *w, const uint8_t *s, const uint8_t *b,
@@ -573,31 +675,10 @@ extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, c
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return cudaErrorNotSupported;
     const uint32_t bn = q4k_gemm_tile_m(m);
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {k, m};
-    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)q4::kTileK, bn};
-    const cuuint32_t estr[2] = {1, 1};
-    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(xp), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
-    // packed weights as a byte matrix [n][k/2] from the tensor's address rounded down to 16 bytes (TMA needs that;
-    // the row pitch k/2 is a multiple of 32): 128-byte swizzled rows when the tensor is aligned, 80-byte windows else.
-    // The matrix is declared 16 bytes wider than k/2 in the window form so the last window of a row is in range; the
-    // extra bytes are the next row's first bytes or, after the last row, the padding every shard carries.
-    CUtensorMap wmap;
-    const uint32_t w_mis = (uint32_t)((uintptr_t)w & 15u);
-    {
-        const cuuint64_t wdims[2] = {(cuuint64_t)k / 2 + (w_mis ? 16u : 0u), n};
-        const cuuint64_t wstrides[1] = {(cuuint64_t)k / 2};
-        const cuuint32_t wbox[2] = {w_mis ? q4::kWWindowPitch : q4::kWAlignedPitch, (cuuint32_t)q4::kTileN};
-        if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w - w_mis), wdims, wstrides, wbox, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, w_mis ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cudaErrorInvalidValue;
-    }
+    CUtensorMap map, wmap;
+    if (!encode_activation_map(encode, &map, xp, m, k, bn) || !encode_weight_map(encode, &wmap, w, n, k)) return cudaErrorInvalidValue;
     q4::GemmParams p;
+    memset(&p, 0, sizeof p);
     p.w = w;
     p.s = s;
     p.b = b;
@@ -608,7 +689,7 @@ extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, c
     p.out_stride = out_stride;
     p.tiles_n = (n + q4::kTileN - 1) / q4::kTileN;
     p.tiles_m = (m + bn - 1) / bn;
-    p.w_misalign = w_mis;
+    p.w_misalign = (uint32_t)((uintptr_t)w & 15u);
     p.accumulate = accumulate ? 1u : 0u;
     p.error_flag = error_flag;
     p.k_splits = q4k_gemm_k_splits(m, n, k, sm_count, &p.split_blocks);
@@ -622,17 +703,53 @@ extern "C" cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, c
     }
     const uint32_t tiles = p.tiles_n * p.tiles_m * p.k_splits;
     const uint32_t ctas = tiles < sm_count ? tiles : sm_count;
-    cudaError_t launched;
-    switch (bn) {
-        case 256: launched = launch_gemm<256>(map, wmap, p, ctas, stream); break;
-        case 128: launched = launch_gemm<128>(map, wmap, p, ctas, stream); break;
-        case 64: launched = launch_gemm<64>(map, wmap, p, ctas, stream); break;
-        case 32: launched = launch_gemm<32>(map, wmap, p, ctas, stream); break;
-        default: launched = launch_gemm<16>(map, wmap, p, ctas, stream); break;
-    }
+    const cudaError_t launched = launch_by_tile(bn, map, wmap, wmap, p, ctas, stream);
     if (launched != cudaSuccess || p.k_splits == 1) return launched;
     const uint64_t elements = (uint64_t)m * out_stride;
     q4::q4_gemm_sum_parts_kernel<<<(uint32_t)((elements + 255) / 256), 256, 0, stream>>>(parts, p.split_stride, p.k_splits, elements, out,
                                                                                   accumulate ? 1 : 0);
     return cudaGetLastError();
+}
+
+// 1 when the gate and up tensors can share one pair launch: the staged weight tiles of a launch have one geometry, so
+// both tensors must sit at the same offset from a 16-byte boundary
+extern "C" int q4k_gemm_pair_supported(const uint8_t *w_gate, const uint8_t *w_up) {
+    return (((uintptr_t)w_gate ^ (uintptr_t)w_up) & 15u) == 0 ? 1 : 0;
+}
+
+// Fused front half of the MLP: h[m][n] = bf16(silu(x gate^T) * (x up^T)) in one launch, written as the prepared
+// activation of the down projection (h_stride elements between activation rows, 16-byte aligned rows).
+extern "C" cudaError_t q4k_gemm_tc_pair(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_t *wg, const uint8_t *sg, const uint8_t *bg,
+                                        const uint8_t *wu, const uint8_t *su, const uint8_t *bu, uint32_t n, uint16_t *h_out,
+                                        uint32_t h_stride, int *error_flag, uint32_t sm_count, cudaStream_t stream) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return cudaErrorNotSupported;
+    if (!q4k_gemm_pair_supported(wg, wu)) return cudaErrorNotSupported;
+    const uint32_t bn = q4k_gemm_tile_m(m);
+    CUtensorMap map, wmap, wmap2;
+    if (!encode_activation_map(encode, &map, xp, m, k, bn) || !encode_weight_map(encode, &wmap, wg, n, k) ||
+        !encode_weight_map(encode, &wmap2, wu, n, k))
+        return cudaErrorInvalidValue;
+    q4::GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.w = wg;
+    p.s = sg;
+    p.b = bg;
+    p.w2 = wu;
+    p.s2 = su;
+    p.b2 = bu;
+    p.h_out = h_out;
+    p.h_stride = h_stride;
+    p.pair = 1;
+    p.n = n;
+    p.m = m;
+    p.k = k;
+    p.tiles_n = (n + q4::kTileN - 1) / q4::kTileN;
+    p.tiles_m = (m + bn - 1) / bn;
+    p.w_misalign = (uint32_t)((uintptr_t)wg & 15u);
+    p.error_flag = error_flag;
+    p.k_splits = 1;
+    p.split_blocks = k / q4::kTileK;
+    const uint32_t tiles = p.tiles_n * p.tiles_m;
+    return launch_by_tile(bn, map, wmap, wmap2, p, tiles < sm_count ? tiles : sm_count, stream);
 }

@@ -79,6 +79,11 @@ cudaError_t q4k_gemm_tc(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_
                         uint32_t n, float *out, uint32_t out_stride, int accumulate, int *error_flag, uint32_t sm_count,
                         float *parts, cudaStream_t stream);
 
+int q4k_gemm_pair_supported(const uint8_t *w_gate, const uint8_t *w_up);
+cudaError_t q4k_gemm_tc_pair(const uint16_t *xp, uint32_t m, uint32_t k, const uint8_t *wg, const uint8_t *sg, const uint8_t *bg,
+                             const uint8_t *wu, const uint8_t *su, const uint8_t *bu, uint32_t n, uint16_t *h_out, uint32_t h_stride,
+                             int *error_flag, uint32_t sm_count, cudaStream_t stream);
+
 cudaError_t q4k_synth_q4(uint64_t seed, uint64_t tensor, float sigma, uint64_t row0, uint64_t rows, uint32_t k,
                          uint8_t *w, uint8_t *s, uint8_t *b, cudaStream_t stream);
 cudaError_t q4k_synth_bf16(uint64_t seed, uint64_t tensor, uint64_t count, uint16_t *out, cudaStream_t stream);

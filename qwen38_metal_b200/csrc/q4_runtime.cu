@@ -154,6 +154,7 @@ struct q4b_runtime {
     uint32_t inline_max_halfs = 0;       // longest activation the kernel's shared memory takes (0: path unavailable)
     uint64_t inline_failures_seen = 0;
     bool inline_off = false;
+    bool mlp_unfused = false;            // Q4B_MLP_UNFUSED=1: never use the fused gate/up launch
     uint64_t launches = 0;
     std::string force_variant;
     // per-kernel timing window (q4b_profile_begin/end)
@@ -561,6 +562,7 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     if (e == cudaSuccess) e = cudaMemset(rt->counters.ptr, 0, rt->counters.capacity);
     if (e == cudaSuccess) e = rt->error_flag.ensure(256);
     if (e == cudaSuccess) e = cudaMemset(rt->error_flag.ptr, 0, rt->error_flag.capacity);
+    if (const char *unf = getenv("Q4B_MLP_UNFUSED")) rt->mlp_unfused = strtol(unf, nullptr, 10) != 0;
     if (const char *off = getenv("Q4B_NO_INLINE")) rt->inline_off = strtol(off, nullptr, 10) != 0;
     if (e == cudaSuccess && !rt->inline_off) {
         // the largest activation for which the one-phase kernel is resident: try the chain's limit, then half of it
@@ -973,11 +975,16 @@ extern "C" int q4b_argmax_batch(q4b_runtime *rt, const void *x, int x_dtype, uin
     return Q4B_OK;
 }
 
-extern "C" int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *gate,
-                             const q4b_job *up, const q4b_job *down, float *out) {
+// down(silu(gate x) * (up x)) on device buffers. From gemm_min_m activation rows on, and when gate and up sit at the same
+// offset from a 16-byte boundary, the front half is ONE tensor-core launch whose epilogue applies the SwiGLU and
+// writes the hidden rows as bf16 in the layout the down projection's GEMM reads -- no fp32 [m][inter] buffers, no
+// separate SwiGLU or conversion pass (the reference keeps this chain in 16-bit intermediates under one fence,
+// src/metal_runtime.rs:4267-4474). Otherwise: two projections, the SwiGLU kernel, the down projection.
+extern "C" int q4b_mlp_batch_device(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k, const q4b_job *gate,
+                                    const q4b_job *up, const q4b_job *down, float *out_dev, void *stream) {
     if (int st = check_rt(rt)) return st;
     if (int st = check_dtype(x_dtype)) return st;
-    if (!x || !out || !gate || !up || !down) return fail(Q4B_INVALID_ARGUMENT, "activation, job or output pointer is null");
+    if (!x_dev || !out_dev || !gate || !up || !down) return fail(Q4B_INVALID_ARGUMENT, "activation, job or output pointer is null");
     if (m == 0 || k == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
     // gate and up must agree (src/metal_runtime.rs:4511-4517)
     if (gate->output_rows != up->output_rows)
@@ -985,37 +992,68 @@ extern "C" int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64
                     (unsigned long long)up->output_rows, (unsigned long long)gate->output_rows);
     std::lock_guard<std::recursive_mutex> lock(rt->mu);
     DeviceGuard guard(rt->device);
+    cudaStream_t s = (cudaStream_t)stream;
     const uint64_t inter = gate->output_rows;
     std::vector<Resolved> gu, dn;
     const q4b_job pair[2] = {*gate, *up};
     if (int st = resolve_jobs(rt, pair, 2, m, k, &gu)) return st;
     if (int st = resolve_jobs(rt, down, 1, m, inter, &dn)) return st;
-    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
-    Q4B_CUDA(rt->x_in.ensure((size_t)m * k * esize), "activation buffer");
+    const bool fused = m >= rt->gemm_min_m && !rt->mlp_unfused && inter % 64 == 0 && q4k_gemm_pair_supported(gu[0].w, gu[1].w);
+    if (fused) {
+        Q4B_CUDA(rt->gemm_x.ensure((size_t)m * k * 2), "activation scratch");
+        Q4B_CUDA(rt->hidden.ensure((size_t)m * inter * 2), "hidden buffer");
+        Q4B_CUDA(q4k_gemm_prepare_x(x_dev, x_dtype == Q4B_F32 ? 1 : 0, m * k, (uint16_t *)rt->gemm_x.ptr, s), "q4_gemm_prepare_x launch");
+        if (int st = profile_open(rt, s)) return st;
+        Q4B_CUDA(q4k_gemm_tc_pair((const uint16_t *)rt->gemm_x.ptr, (uint32_t)m, (uint32_t)k, gu[0].w, gu[0].s, gu[0].b, gu[1].w, gu[1].s,
+                                  gu[1].b, (uint32_t)inter, (uint16_t *)rt->hidden.ptr, (uint32_t)inter, (int *)rt->error_flag.ptr,
+                                  (uint32_t)rt->sm_count, s),
+                 "q4_gemm_tc pair launch");
+        if (int st = profile_close(rt, s, 2 * inter * (k / 2 + (k / 64) * 4) + m * k * 2 + m * inter * 2, 4ull * m * inter * k)) return st;
+        uint32_t split_blocks = 0;
+        const uint32_t splits = q4k_gemm_k_splits((uint32_t)m, dn[0].n, (uint32_t)inter, (uint32_t)rt->sm_count, &split_blocks);
+        if (splits > 1) Q4B_CUDA(rt->gemm_parts.ensure((size_t)splits * m * dn[0].n * 4), "partial output scratch");
+        if (int st = profile_open(rt, s)) return st;
+        Q4B_CUDA(q4k_gemm_tc((const uint16_t *)rt->hidden.ptr, (uint32_t)m, (uint32_t)inter, dn[0].w, dn[0].s, dn[0].b, dn[0].n, out_dev,
+                             dn[0].n, 0, (int *)rt->error_flag.ptr, (uint32_t)rt->sm_count, (float *)rt->gemm_parts.ptr, s),
+                 "q4_gemm_tc launch");
+        rt->launches += 3;
+        return profile_close(rt, s, (uint64_t)dn[0].n * (inter / 2 + (inter / 64) * 4) + m * inter * 2 + m * dn[0].n * 4, 2ull * m * dn[0].n * inter);
+    }
     Q4B_CUDA(rt->gate.ensure((size_t)m * inter * 4), "gate buffer");
     Q4B_CUDA(rt->up.ensure((size_t)m * inter * 4), "up buffer");
     Q4B_CUDA(rt->hidden.ensure((size_t)m * inter * 4), "hidden buffer");
-    Q4B_CUDA(rt->outs[0].ensure((size_t)m * dn[0].n * 4), "output buffer");
+    float *gu_out[2] = {(float *)rt->gate.ptr, (float *)rt->up.ptr};
+    if (int st = enqueue_matmul(rt, x_dev, x_dtype, m, k, gu, gu_out, 0, s)) return st;
+    Q4B_CUDA(q4k_swiglu(gu_out[0], gu_out[1], m * inter, (float *)rt->hidden.ptr, nullptr, s), "swiglu launch");
+    rt->launches++;
+    // the intermediate stays fp32 (the decode chain of the reference, src/metal_runtime.rs:4616-4645)
+    return enqueue_matmul(rt, rt->hidden.ptr, Q4B_F32, m, inter, dn, &out_dev, 0, s);
+}
+
+extern "C" int q4b_mlp_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *gate,
+                             const q4b_job *up, const q4b_job *down, float *out) {
+    if (int st = check_rt(rt)) return st;
+    if (int st = check_dtype(x_dtype)) return st;
+    if (!x || !out || !gate || !up || !down) return fail(Q4B_INVALID_ARGUMENT, "activation, job or output pointer is null");
+    if (m == 0 || k == 0) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    std::lock_guard<std::recursive_mutex> lock(rt->mu);
+    DeviceGuard guard(rt->device);
+    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
+    const uint64_t rows = down->output_rows;
+    if (rows == 0 || rows > 0xffffffffull) return fail(Q4B_EMPTY_DIMENSION, "matrix dimensions must be greater than zero");
+    Q4B_CUDA(rt->x_in.ensure((size_t)m * k * esize), "activation buffer");
+    Q4B_CUDA(rt->outs[0].ensure((size_t)m * rows * 4), "output buffer");
     cudaStream_t s = rt->stream;
     Q4B_CUDA(cudaMemcpyAsync(rt->x_in.ptr, x, (size_t)m * k * esize, cudaMemcpyHostToDevice, s), "activation upload");
-    float *gu_out[2] = {(float *)rt->gate.ptr, (float *)rt->up.ptr};
-    int st = enqueue_matmul(rt, rt->x_in.ptr, x_dtype, m, k, gu, gu_out, 0, s);
-    if (st == Q4B_OK) {
-        cudaError_t e = q4k_swiglu(gu_out[0], gu_out[1], m * inter, (float *)rt->hidden.ptr, nullptr, s);
-        rt->launches++;
-        if (e != cudaSuccess) st = fail_cuda(e, "swiglu launch");
-    }
     float *dn_out = (float *)rt->outs[0].ptr;
-    // the intermediate stays fp32 (the decode chain of the reference, src/metal_runtime.rs:4616-4645)
-    if (st == Q4B_OK) st = enqueue_matmul(rt, rt->hidden.ptr, Q4B_F32, m, inter, dn, &dn_out, 0, s);
-    if (st != Q4B_OK) {
+    if (int st = q4b_mlp_batch_device(rt, rt->x_in.ptr, x_dtype, m, k, gate, up, down, dn_out, s)) {
         cudaStreamSynchronize(s);
         return st;
     }
-    Q4B_CUDA(rt->results.ensure((size_t)m * dn[0].n * 4), "result staging");
-    Q4B_CUDA(cudaMemcpyAsync(rt->results.ptr, dn_out, (size_t)m * dn[0].n * 4, cudaMemcpyDeviceToHost, s), "result download");
+    Q4B_CUDA(rt->results.ensure((size_t)m * rows * 4), "result staging");
+    Q4B_CUDA(cudaMemcpyAsync(rt->results.ptr, dn_out, (size_t)m * rows * 4, cudaMemcpyDeviceToHost, s), "result download");
     if (int fst = finish(rt, s)) return fst;
-    memcpy(out, rt->results.ptr, (size_t)m * dn[0].n * 4);
+    memcpy(out, rt->results.ptr, (size_t)m * rows * 4);
     return Q4B_OK;
 }
 

@@ -234,6 +234,10 @@ class CudaRuntime:
         _check(self._lib.q4b_matmul_batch_device(self._h, x_ptr, dtype, m, k, _jobs(jobs), len(jobs), ptrs, flags,
                                                  stream))
 
+    def mlp_batch_device(self, x_ptr: int, dtype: int, m: int, k: int, gate, up, down, out_ptr: int, stream: int = 0) -> None:
+        g, u, d = gate.to_c(), up.to_c(), down.to_c()
+        _check(self._lib.q4b_mlp_batch_device(self._h, x_ptr, dtype, m, k, C.byref(g), C.byref(u), C.byref(d), out_ptr, stream))
+
     def argmax_batch_device(self, x_ptr: int, dtype: int, m: int, k: int, job, index_base: int, tokens_ptr: int,
                             values_ptr: int = 0, stream: int = 0) -> None:
         cj = job.to_c()

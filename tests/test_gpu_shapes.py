@@ -309,3 +309,39 @@ def test_small_m_sweep_full_shapes_sampled(runtime, oracle, name, n, k, off):
                     # against the exact oracle the distance is the bf16 rounding of w itself (about 1.5e-3; the
                     # oracle's own 16-bit tile form is as far away), which scatters on a sample of a few dozen values
                     assert oracle.rel_l2(got, exact[:m]) <= (2e-3 if got.size >= 512 else 3e-3), (m, r0)
+
+
+@pytest.mark.parametrize("off", [0, 2], ids=["aligned", "at +2"])
+def test_fused_mlp_full_width_sampled(runtime, oracle, off):
+    """The fused MLP at the model's width (K = 5120, intermediate 17408, down to 5120; src/metal_runtime.rs:4267-4474):
+    gate and up in ONE tensor-core launch with the SwiGLU in its epilogue, bf16 hidden rows handed straight to the down
+    projection. 256 activation rows on the GPU; for three of them the whole chain is evaluated by the oracle's 16-bit
+    tile form (full gate and up matrices regenerated on the CPU) and compared on sampled rows of the down projection:
+    <= 5e-4 against that form, <= 4e-3 against the exact one, the bars of the reference's own fused-MLP test."""
+    import torch
+
+    from qwen38_metal_b200 import capi
+
+    k, inter, n, m = 5120, 17408, 5120, 256
+    gate, up, down = _synth_job(runtime, 811, inter, k, off), _synth_job(runtime, 812, inter, k, off), _synth_job(runtime, 813, n, inter, off)
+    x = torch.empty(m * k, dtype=torch.bfloat16, device="cuda")
+    runtime.synth_bf16(SEED, 9100, m * k, x.data_ptr(), 0)
+    out = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+    launches = runtime.launch_count()
+    runtime.mlp_batch_device(x.data_ptr(), capi.Q4B_BF16, m, k, gate, up, down, out.data_ptr(), 0)
+    torch.cuda.synchronize()
+    runtime.device_status()
+    assert runtime.launch_count() - launches == 3  # activation preparation, fused gate/up, down
+    y = out.cpu().numpy().reshape(m, n)
+    rows = [0, 100, 255]
+    xf = oracle.bf16_to_f32(x.view(torch.int16).cpu().numpy().view(np.uint16)).reshape(m, k)[rows]
+    wg, wu = oracle.synth_q4(SEED, 811, inter, k), oracle.synth_q4(SEED, 812, inter, k)
+    for form, bar in (("tiles", 5e-4), ("exact", 4e-3)):
+        mm = (lambda a, t, r: oracle.matmul_bf16_tiles(a, *t, r, threads=8)) if form == "tiles" else \
+             (lambda a, t, r: oracle.matmul_factored_f32(a, *t, r, threads=8))
+        h = oracle.swiglu(mm(xf, wg, inter), mm(xf, wu, inter))
+        if form == "tiles":
+            h = oracle.bf16_to_f32(oracle.f32_to_bf16(h))
+        for r0 in (0, (n // 2) & ~15, n - 16):
+            wd = oracle.synth_q4(SEED, 813, 16, inter, row0=r0)
+            assert oracle.rel_l2(y[rows][:, r0:r0 + 16], mm(h, wd, 16)) <= bar, (form, r0)
