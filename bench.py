@@ -524,7 +524,7 @@ def run_ours(args) -> int:
             "path": ("persistent decode chain (one cooperative launch per token and GPU"
                      + (", peer stores + cross-GPU barriers)" if world > 1 else ")")) if chain is not None
                     else "CUDA graph of per-stage launches + NCCL all-gathers",
-            "roofline": {"bound": "hbm", "kernel": "q4_gemv_fast_kernel / q4_gemv_generic_kernel (per-stage launches)", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "q4_stack_inline_kernel (per-stage launches, one per projection group)", "achieved": achieved, "peak": peak,
                          "peak_source": peak_source, "unit": UNIT, "frac": achieved / peak if peak else None,
                          "frac_of_8TBs": achieved / NOMINAL_HBM_GBS, "launches": prof["launches"],
                          "avg_launch_us": prof["ms"] * 1e3 / max(1, prof["launches"]),
@@ -540,8 +540,8 @@ def run_ours(args) -> int:
                                 "frac_of_8TBs": value / world / NOMINAL_HBM_GBS, "launches": args.steps,
                                 "avg_launch_us": ms * 1e3 / args.steps, "bytes_per_launch": total_bytes // world,
                                 # dram__bytes_read+write of one launch: captured with ncu on the 4-layer stack
-                                # (1.6026 GB for 1.5297 GB algorithmic) and scaled by the bytes of this launch
-                                "traffic": int(total_bytes // world * 1.0477),
+                                # (1.5800 + 0.0158 GB for 1.5297 GB algorithmic) and scaled by the bytes of this launch
+                                "traffic": int(total_bytes // world * 1.0432),
                                 "traffic_source": "ncu capture of a 4-layer launch, scaled by algorithmic bytes (profiles/)"}
             line["launch_per_stage_graph"] = {"value": total_bytes * args.steps / (ms_graph * 1e-3) / 1e9, "unit": UNIT,
                                               "ms_per_step": ms_graph / args.steps, "gpu_launches": launches_per_token}

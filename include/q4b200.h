@@ -285,7 +285,8 @@ int q4b_synth_bf16_device(q4b_runtime *rt, uint64_t seed, uint64_t tensor, uint6
  * inputs, any byte alignment of the three tensors) that calls no cudaMalloc/cudaFree and no allocating library
  * routine: every scratch buffer lives in a static device array of about 1.1 MB that each GPU loading the library
  * holds until exit. For code that only receives pointers and a stream, or runs where allocator traffic is
- * forbidden. All pointers are device pointers on `device`; out_dev receives n floats. The array is shared by all
+ * forbidden. All pointers are device pointers on `device`; out_dev receives n floats. The tensors need no padding:
+ * only 16-byte blocks that a tensor itself touches are read. The array is shared by all
  * calls on a device and keeps the last call's contents: calls that overlap on the GPU race on it, so order them.
  * The first call on a device also looks up the array's address and the kernel occupancy; make it outside any
  * stream capture. Shapes beyond the limits are rejected with Q4B_UNSUPPORTED.

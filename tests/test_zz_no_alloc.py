@@ -54,3 +54,36 @@ def test_noalloc_rejects_what_the_static_array_cannot_hold(runtime):
     assert b"32768" in lib.q4b_noalloc_last_error()
     assert lib.q4b_matvec_noalloc(0, p, 100, p, p, p, 16, p, None) == 5          # InputNotGrouped
     assert lib.q4b_matvec_noalloc(0, None, 128, p, p, p, 16, p, None) == 13       # InvalidArgument
+
+
+@pytest.mark.parametrize("n,k,offset", [(40, 192, 0), (33, 192, 2), (50, 1024, 6), (16, 5120, 0)])
+def test_noalloc_on_tensors_without_padding(runtime, oracle, n, k, offset):
+    """Callers of this entry point bring their own tensors, which nothing pads: the three arrays here are torch byte
+    buffers of exactly offset + size bytes (the library's own shards carry 1 KB of slack, these do not), with an odd
+    group count and byte offsets in the mix. The kernels read only 16-byte blocks that a tensor itself touches (the
+    address arithmetic is checked on the CPU in tests/test_decomp.py); here the results must match the oracle."""
+    import torch
+
+    from qwen38_metal_b200 import capi
+
+    lib = capi.load()
+    w, s, b = oracle.synth_q4(910, n + k, n, k)
+    x_bits = oracle.synth_bf16(910, 6000 + k, k)
+
+    def exact(arr):
+        raw = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+        buf = torch.zeros(offset + raw.size, dtype=torch.uint8, device="cuda")
+        buf[offset:] = torch.from_numpy(raw.copy()).cuda()
+        return buf
+
+    wb, sb, bb = exact(w), exact(s), exact(b)
+    xb = torch.from_numpy(x_bits.view(np.int16).copy()).cuda()
+    out = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(2):
+        st = lib.q4b_matvec_noalloc(0, xb.data_ptr(), k, wb.data_ptr() + offset, sb.data_ptr() + offset, bb.data_ptr() + offset, n,
+                                    out.data_ptr(), None)
+        assert st == 0, lib.q4b_noalloc_last_error()
+        torch.cuda.synchronize()
+        x = oracle.bf16_to_f32(x_bits)
+        assert oracle.rel_l2(out.cpu().numpy(), oracle.matmul_factored_f32(x, w, s, b, n)[0]) <= 1e-5
