@@ -72,8 +72,7 @@ struct SyncState {
 // and the block that completes the local count of a cross-GPU barrier forwards one arrival to every rank.
 template <int WARPS>
 __device__ __forceinline__ void phase_arrive(const StackParams &sp, uint32_t kind, const SyncState &ss, uint32_t *arrive_smem,
-                                             bool stored_to_peers, uint32_t lane, unsigned long long *tr, unsigned int *amax_global = nullptr,
-                                             uint32_t *amax_smem = nullptr) {
+                                             bool stored_to_peers, uint32_t lane, unsigned long long *tr) {
     if (stored_to_peers) __threadfence_system();
     else if (sp.flags & kFlagWarpFenceGpu) __threadfence();
     else __threadfence_block();  // the block's last warp fences at device scope for everyone it has seen arrive
@@ -82,10 +81,6 @@ __device__ __forceinline__ void phase_arrive(const StackParams &sp, uint32_t kin
     const uint32_t before = atomicAdd(arrive_smem, 1u);
     if (before != WARPS - 1) return;
     *reinterpret_cast<volatile uint32_t *>(arrive_smem) = 0;  // the next arrival follows a block barrier
-    if (amax_global) {
-        const uint32_t mx = atomicExch(amax_smem, 0u);
-        if (mx) atomicMax(amax_global, mx);
-    }
     __threadfence();
     const unsigned int target = (ss.local_gen + 1u) * gridDim.x;
     const unsigned int seen = atomicAdd(sp.local_bar, 1u);
@@ -241,43 +236,13 @@ __device__ __forceinline__ void block_sum_max(float &sum, uint32_t &mx, float *r
     mx = top;
 }
 
-// The hidden vector as the gate/up epilogue left it: bf16 values and their maximum magnitude. No reduction, no
-// transcendental: 2 bytes per input.
+// bf16 vector | fp32 vector | bf16(silu(gate)*up) of two fp32 vectors | weightless RMS-norm of an fp32 vector given as
+// the sum of src_parts vectors (plain, or tagged words that are polled) | the hidden vector as a fused gate/up
+// epilogue left it (tagged pairs of bf16 values, polled; only this SM's slice is read and scaled by the slice's own
+// maximum). Values are held in registers between the reduction and the conversion.
 // [b_lo, b_hi): the 8-input blocks this SM holds (all of them, or the slice of a K-major phase; b_lo is a multiple of
 // 64 and X is offset so that block b_lo lands at the start of the buffer); [o_lo, o_hi): blocks this SM writes to the
 // optional bf16 copy.
-template <int WARPS>
-__device__ __forceinline__ void rebuild_from_h(const StackPhase &P, const XBuf &X, uint32_t b_lo, uint32_t b_hi, uint32_t o_lo, uint32_t o_hi) {
-    constexpr uint32_t T = WARPS * 32;
-    const uint32_t blocks = P.k / 8;
-    const uint32_t amax = __ldcg(static_cast<const unsigned int *>(P.src1));
-    const int e = scale_exponent(amax);
-    const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
-    if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
-    const uint16_t *h = static_cast<const uint16_t *>(P.src0);
-    for (uint32_t b0 = b_lo + (threadIdx.x & ~31u); b0 < b_hi; b0 += T) {
-        const uint32_t b = b0 + (threadIdx.x & 31u);
-        float v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.f;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (b < blocks) {
-            raw = __ldcg(reinterpret_cast<const uint4 *>(h + (size_t)b * 8));
-            const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                v[2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
-                v[2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
-            }
-        }
-        emit_block(v, scale, b, b < b_hi, X);
-        if (P.x_bf16_out && b >= o_lo && b < o_hi && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = raw;
-    }
-    __syncthreads();
-}
-
-// bf16 vector | bf16(silu(gate)*up) of two fp32 vectors | weightless RMS-norm of an fp32 vector given as the sum of
-// src_parts vectors. Values are held in registers between the reduction and the conversion.
 template <int WARPS>
 __device__ __forceinline__ void rebuild_general(const StackParams &sp, const StackPhase &P, const XBuf &X, float *red, uint32_t b_lo, uint32_t b_hi,
                                                 uint32_t o_lo, uint32_t o_hi, uint32_t src_tag) {
@@ -287,14 +252,41 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
     float v[kStackMaxIters][8];
     float ss = 0.f;
     uint32_t amax = 0;
+    // the hidden vector is read slice by slice (statistics of the slice); everything else needs the whole vector
+    const uint32_t base = P.x_kind == kRebuildH ? b_lo : 0u, limit = P.x_kind == kRebuildH ? b_hi : blocks_p;
 #pragma unroll
     for (int it = 0; it < kStackMaxIters; ++it) {
-        const uint32_t b = threadIdx.x + it * T;
+        const uint32_t b = base + threadIdx.x + it * T;
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[it][i] = 0.f;
-        if (it * T >= blocks_p) continue;  // (uniform) nothing left for any thread
-        if (b < blocks) {
-            if (P.x_kind == kRebuildBf16) {
+        if (base + it * T >= limit) continue;  // (uniform) nothing left for any thread
+        if (b < blocks && b < limit) {
+            if (P.x_kind == kRebuildH) {
+                // four {two bf16 values, tag} words per block of 8: wait (bounded) for the epilogues that produce them
+                const uint4 *p0 = reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(P.src0) + (size_t)b * 32);
+                uint4 q[2];
+                uint32_t spins = 0;
+                while (true) {
+                    bool ok = true;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w) : "l"(p0 + i) : "memory");
+                        ok = ok && q[i].y == src_tag && q[i].w == src_tag;
+                    }
+                    if (ok) break;
+                    if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
+                        *sp.error_flag = 1;
+                        break;
+                    }
+                    __nanosleep(40);
+                }
+                const uint32_t r[4] = {q[0].x, q[0].z, q[1].x, q[1].z};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    v[it][2 * i] = bf16_bits_to_float(r[i] & 0xffffu);
+                    v[it][2 * i + 1] = bf16_bits_to_float(r[i] >> 16);
+                }
+            } else if (P.x_kind == kRebuildBf16) {
                 const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(P.src0) + (size_t)b * 8));
                 const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -371,7 +363,7 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
         amax = float_to_bf16_bits(__uint_as_float(amax) * inv) << 16;
 #pragma unroll
         for (int it = 0; it < kStackMaxIters; ++it) {
-            if (it * T >= blocks_p) continue;
+            if (base + it * T >= limit) continue;
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[it][i] = bf16_bits_to_float(float_to_bf16_bits(v[it][i] * inv));
         }
@@ -381,8 +373,8 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
     if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
 #pragma unroll
     for (int it = 0; it < kStackMaxIters; ++it) {
-        const uint32_t b = threadIdx.x + it * T;
-        if (it * T >= blocks_p) continue;
+        const uint32_t b = base + threadIdx.x + it * T;
+        if (base + it * T >= limit) continue;
         emit_block(v[it], scale, b, b >= b_lo && b < b_hi, X);
         if (P.x_bf16_out && b >= o_lo && b < o_hi && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = pack_bf16x8(v[it]);
     }
@@ -470,8 +462,8 @@ struct TileEnd {
 // no counter are needed -- and the owner adds them to its own in worker order once their tags show this launch and
 // phase. The wait for a late contributor is bounded. Returns true when this warp stored into other GPUs' memory.
 __device__ __forceinline__ bool finish_tile_m1(const StackParams &sp, const StackPhase &P, const StackJob &J, uint32_t worker,
-                                               const TileEnd &te, float acc_a, float acc_b, float inv, uint32_t tag,
-                                               uint32_t *amax_smem, uint32_t lane, uint32_t g, uint32_t t) {
+                                               const TileEnd &te, float acc_a, float acc_b, uint32_t tag, uint32_t lane, uint32_t g,
+                                               uint32_t t) {
     const bool whole = te.c0v == 0 && te.c1v == J.vcpt;
     if (!whole) {
         const Q4Split split{P.units, P.cpt, P.workers};
@@ -518,22 +510,21 @@ __device__ __forceinline__ bool finish_tile_m1(const StackParams &sp, const Stac
     // those of group B in lanes 2 and 3
     acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
     acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
-    const float ya = (acc_a + __shfl_xor_sync(0xffffffffu, acc_a, 2)) * inv;  // inv is a power of two: exact
-    const float yb = (acc_b + __shfl_xor_sync(0xffffffffu, acc_b, 2)) * inv;
+    const float ya = acc_a + __shfl_xor_sync(0xffffffffu, acc_a, 2);
+    const float yb = acc_b + __shfl_xor_sync(0xffffffffu, acc_b, 2);
     const uint32_t row_a = te.tile_row + g, row_b = row_a + J.b_row_offset;
     if (J.pair) {
         const bool valid = t == 0 && row_a < J.n;
         const float h = (ya * (1.0f / (1.0f + expf(-ya)))) * yb;  // qwen38_swiglu_rows, shaders/qwen38.metal:4188-4198
-        const uint32_t hb = float_to_bf16_bits(h);
-        const uint32_t mag = __reduce_max_sync(0xffffffffu, valid ? ((hb << 16) & 0x7fffffffu) : 0u);
+        const uint32_t hb = valid ? float_to_bf16_bits(h) : 0u;
+        // rows come in pairs: the lane of the even row stores both bf16 values and the tag as one 8-byte word
+        const uint32_t hb_next = __shfl_down_sync(0xffffffffu, hb, 4);
         if (valid) {
-            J.h_out[row_a] = (uint16_t)hb;
+            if ((g & 1u) == 0)
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(J.h_out + (row_a >> 1)), "r"(hb | (hb_next << 16)), "r"(tag) : "memory");
             if (J.out[0]) J.out[0][row_a] = ya;
             if (J.out[1]) J.out[1][row_a] = yb;
         }
-        // the block's maximum goes to device memory once, with the block's arrival: thousands of tiles adding to one
-        // word would queue up behind each other
-        if (lane == 0) atomicMax(amax_smem, mag);
         return false;
     }
     if (t != 0) return J.has_peers != 0;
@@ -614,7 +605,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     float *xsum1 = xsum0 + sp.halfs[0] / 64 + 4;
     float *misc = xsum1 + sp.halfs[1] / 64 + 4;
     uint32_t *arrive_smem = reinterpret_cast<uint32_t *>(misc + 2);
-    uint32_t *amax_smem = reinterpret_cast<uint32_t *>(misc + 70);
     float *red = misc + 4;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * kStackRingBytes;
     const uint32_t pring = ring + kStages * kStageBytesAligned;
@@ -656,7 +646,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     request_phase(0);
     if (threadIdx.x == 0) {
         *arrive_smem = 0;
-        *amax_smem = 0;
         *gbase_smem = sp.peers ? *reinterpret_cast<volatile unsigned long long *>(sp.peers->consumed) : 0ull;
         reinterpret_cast<uint32_t *>(misc)[3] = *reinterpret_cast<volatile unsigned int *>(sp.launch_seq);
     }
@@ -709,8 +698,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             // the bf16 copy of the activation is written by block 0, or by the first kparts blocks (one part each)
             const bool writes = blockIdx.x < ((P.kparts > 1u && P.sliced) ? P.kparts : 1u);
             const uint32_t o_lo = writes ? c_lo * 16u : 0u, o_hi = writes ? c_hi * 16u : 0u;
-            if (P.x_kind == kRebuildH) rebuild_from_h<WARPS>(P, X, cs4 * 16u, c_hi * 16u, o_lo, o_hi);
-            else if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase);
+            if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase);
             if (sp.trace && threadIdx.x == 0) trace_slot()[2] = stack_ns();
         }
 
@@ -841,8 +829,11 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                 if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 57] = stack_ns();
                 // digits back together: a lane's columns are digits (0, 1) of its group for even t, (2, none) for odd t
                 const float w0 = (t & 1u) ? 65536.f : 1.f, w1 = (t & 1u) ? 0.f : 256.f;
-                const float part_a = fmaf(acc[1], w1, acc[0] * w0), part_b = fmaf(acc[3], w1, acc[2] * w0);
-                stored_to_peers |= finish_tile_m1(sp, P, sp.jobs[te.job], worker, te, part_a, part_b, *X.inv, tag_base + ph, amax_smem, lane, g, t);
+                // ... and the power-of-two scaling of this SM's activation undone (exact) before sums of different SMs meet:
+                // the slices of a K-major phase are scaled independently
+                const float inv = *X.inv;
+                const float part_a = fmaf(acc[1], w1, acc[0] * w0) * inv, part_b = fmaf(acc[3], w1, acc[2] * w0) * inv;
+                stored_to_peers |= finish_tile_m1(sp, P, sp.jobs[te.job], worker, te, part_a, part_b, tag_base + ph, lane, g, t);
             }
         }
         if (sp.trace && threadIdx.x == 0) trace_slot()[3] = stack_ns();
@@ -852,8 +843,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
         }
 
         if (P.arrive_kind != kSyncNone) {
-            const StackJob &J0 = sp.jobs[P.job_begin];
-            phase_arrive<WARPS>(sp, P.arrive_kind, sync, arrive_smem, stored_to_peers, lane, trace_slot(), J0.pair ? J0.amax : nullptr, amax_smem);
+            phase_arrive<WARPS>(sp, P.arrive_kind, sync, arrive_smem, stored_to_peers, lane, trace_slot());
             ++sync.local_gen;
             if (P.arrive_kind == kSyncGlobal) ++sync.global_gen;
         }
@@ -930,7 +920,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     }
     // End of the launch. Every block counts itself out; the block that counts last -- every other block has finished,
     // and every block read the launch count before it did anything -- puts the words back that the next launch expects:
-    // barrier counter and running maxima to zero, the launch count (tags of partial slots and hand-offs) one further,
+    // barrier counters to zero, the launch count (tags of partial slots and hand-offs) one further,
     // the cross-GPU arrivals this launch used up. So no memset precedes a launch. (A launch that gave up on a wait
     // leaves them inconsistent; the host repairs them before the next launch.)
     __syncthreads();
@@ -941,7 +931,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             __threadfence();
             sp.local_bar[0] = 0;
             sp.local_bar[1] = 0;
-            for (uint32_t i = 0; i < sp.n_amax; ++i) sp.amax_words[i] = 0;
             if (sp.peers) *sp.peers->consumed = *gbase_smem + (unsigned long long)sync.global_gen * sp.peers->world;
             *sp.launch_seq = reinterpret_cast<uint32_t *>(misc)[3] + 1u;
         }

@@ -1192,6 +1192,7 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         // Tagged hand-off to the next stage (its RMS-norm source is this job's output): 0 none, 1 through a buffer of
         // the chain (one GPU, or an output that stays local), 2 through the ranks' exchange arenas
         int ll_job = -1, ll_mode = 0;
+        bool plain_consumed = false;   // a later stage reads an output of this stage as plain floats: needs a barrier
     };
     std::vector<StageJobs> sj(n_stages);
     uint32_t halfs[2] = {0, 0};
@@ -1252,6 +1253,7 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         J.deferred.clear();
         J.ll_job = -1;
         J.ll_mode = 0;
+        J.plain_consumed = false;
     }
     // ---- fusion and deferral ----
     for (uint32_t si = 0; si + 1 < n_stages; ++si) {
@@ -1283,6 +1285,24 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
                     sj[si].ll_job = (int)i;
                     sj[si].ll_mode = 2;
                 }
+            }
+        }
+        // which outputs does a later stage (or the token reduction) read as plain floats? The fused SwiGLU and the tagged
+        // hand-off are served by tags, everything else needs this stage's barrier
+        for (uint32_t i = 0; i < S.n_jobs; ++i) {
+            const uintptr_t lo = (uintptr_t)S.outputs[i], hi = lo + (uint64_t)sj[si].res[i].n * 4;
+            if (logits && ByteRange{(uintptr_t)logits, (uintptr_t)logits + (uint64_t)vocab * 4}.overlaps(lo, hi)) sj[si].plain_consumed = true;
+            for (uint32_t later = si + 1; later < n_stages; ++later) {
+                const bool served_by_tags = later == si + 1 && (((int)i == sj[si].pair_a || (int)i == sj[si].pair_b) || (int)i == sj[si].ll_job);
+                if (!served_by_tags)
+                    for (const ByteRange &r : reads[later]) sj[si].plain_consumed = sj[si].plain_consumed || r.overlaps(lo, hi);
+                // a stage that writes the same buffer again ends this value's life (layers reuse their buffers)
+                bool rewritten = false;
+                for (uint32_t j = 0; j < stages[later].n_jobs; ++j) {
+                    const uintptr_t wlo = (uintptr_t)stages[later].outputs[j], whi = wlo + (uint64_t)sj[later].res[j].n * 4;
+                    rewritten = rewritten || (wlo <= lo && hi <= whi);
+                }
+                if (rewritten) break;
             }
         }
         // deferral: outputs that no later stage (and not the token reduction) reads
@@ -1439,8 +1459,9 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         // the last stage's arrival publishes the logits; without a token reduction only peers would need it
         const bool last = si + 1 == n_stages;
         M.arrive_kind = global ? q4::kSyncGlobal : (last && !logits) ? q4::kSyncNone : q4::kSyncLocal;
-        // the next stage polls the tags of its source instead of waiting at a barrier
-        if (!last && J.ll_job >= 0 && !global) M.arrive_kind = q4::kSyncNone;
+        // the next stages poll the tags of what they read (hidden vector of a fused pair, hand-off of a projection)
+        // instead of waiting at a barrier -- unless something of this stage is consumed through plain memory
+        if (!last && !global && !J.plain_consumed && (J.ll_job >= 0 || J.pair_a >= 0)) M.arrive_kind = q4::kSyncNone;
         prev_arrive = M.arrive_kind;
         any_global = any_global || global;
         // behind this stage's arrival: the carried half of the previous stage's deferred jobs, then the first part of
@@ -1495,20 +1516,17 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     if (!c) return fail(Q4B_CUDA_ERROR, "out of host memory");
     std::unique_ptr<q4b_chain> guard_chain(c);
     uint8_t *reset = nullptr, *hbuf = nullptr;
-    const size_t reset_bytes = 256 + n_pairs * 4;
+    const size_t reset_bytes = 256;
     size_t h_total = 0;
     std::vector<size_t> h_off(n_pairs);
     for (size_t i = 0; i < n_pairs; ++i) {
         h_off[i] = h_total;
-        h_total += ((size_t)pair_k[i] * 2 + 255) & ~(size_t)255;
+        h_total += ((size_t)pair_k[i] * 4 + 255) & ~(size_t)255;  // one {two bf16 values, tag} word per two rows
     }
     cudaError_t e = build.alloc((void **)&reset, reset_bytes, true);
     if (e == cudaSuccess) e = build.alloc((void **)&hbuf, h_total + 256, true);
     if (e != cudaSuccess) return fail_cuda(e, "decode chain allocation");
-    for (auto &fx : pair_fixups) {
-        jobs[fx.first].h_out = (uint16_t *)(hbuf + h_off[fx.second]);
-        jobs[fx.first].amax = (unsigned int *)(reset + 256 + fx.second * 4);
-    }
+    for (auto &fx : pair_fixups) jobs[fx.first].h_out = (unsigned long long *)(hbuf + h_off[fx.second]);
     // tagged hand-offs: where the producer stores its {value, tag} words and what the consumer's rebuild polls
     {
         size_t ll_total = 0;
@@ -1556,7 +1574,10 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
         if (phases[pi].x_kind != q4::kRebuildH) continue;
         const uint32_t pr = pair_of_stage[phase_stage[pi] - 1];
         phases[pi].src0 = hbuf + h_off[pr];
-        phases[pi].src1 = reset + 256 + (size_t)pr * 4;
+        phases[pi].src1 = nullptr;
+        phases[pi].src_tagged = 1;
+        for (size_t pj = 0; pj < pi; ++pj)
+            if (phase_role[pj] == 0 && phase_stage[pj] == phase_stage[pi] - 1) phases[pi].src_tag_phase = (uint32_t)pj;
     }
     void *phases_dev = nullptr, *jobs_dev = nullptr, *partials = nullptr, *counters = nullptr, *aux = nullptr, *peers_dev = nullptr, *trace = nullptr;
     e = build.alloc(&phases_dev, phases.size() * sizeof(q4::StackPhase), false);
@@ -1593,8 +1614,6 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     sp.halfs[0] = halfs[0];
     sp.halfs[1] = halfs[1];
     sp.local_bar = (unsigned int *)reset;
-    sp.amax_words = (unsigned int *)(reset + 256);
-    sp.n_amax = (uint32_t)n_pairs;
     sp.error_flag = (int *)rt->error_flag.ptr;
     sp.partials = (uint4 *)partials;
     sp.launch_seq = (unsigned int *)counters;

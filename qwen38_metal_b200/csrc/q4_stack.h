@@ -33,8 +33,7 @@ struct StackJob {
     // and every other rank's copy of a vector that the next stage's rebuild polls -- value and tag travel in one store,
     // so neither a fence nor a barrier stands between producer and consumer, on one GPU or across NVLink.
     unsigned long long *ll_out[kMaxPeers];  // indexed by row; null entries are skipped; all null: no hand-off
-    uint16_t *h_out;       // pair: bf16(silu(a) * b), indexed by row
-    unsigned int *amax;    // pair: running maximum of |h| as fp32 bits (zero at launch)
+    unsigned long long *h_out;  // pair: {bf16(silu(a) * b) of rows 2i and 2i+1, tag} as one 8-byte word, indexed by i
     uint32_t n;            // rows per side
     uint32_t rows_per_tile, b_row_offset;
     uint32_t w_stride, p_stride;  // bytes between rows of the weight / parameter arrays (multiples of 16)
@@ -66,10 +65,10 @@ struct StackPhase {
     uint64_t units;
     uint32_t wait_kind;           // wait for the latest arrival (this GPU's blocks / all ranks) before the phase
     uint32_t x_kind;              // how the activation is rebuilt after the wait (kRebuild*)
-    const void *src0, *src1;      // Bf16: bf16[k]; Swiglu: fp32 gate[k], up[k]; Rms: fp32 [src_parts][k]; H: bf16[k], amax word
+    const void *src0, *src1;      // Bf16: bf16[k]; F32: fp32[k]; Swiglu: fp32 gate[k], up[k]; Rms: fp32 [src_parts][k]; H: tagged words [k/2]
     uint32_t src_parts, src_part_stride;  // Rms: the vector is the sum, in order, of src_parts vectors this many bytes apart
     uint32_t src_tagged;          // Rms: the source vectors are {value, tag} words written by phase src_tag_phase of this
-    uint32_t src_tag_phase;       //      launch; the rebuild polls until every word carries that phase's tag
+    uint32_t src_tag_phase;       //      launch; the rebuild polls until every word carries that phase's tag (H: always)
     uint16_t *x_bf16_out;         // optional: block 0 stores the bf16 activation it built
     float *sum_out;               // optional (Rms): block 0 stores the summed fp32 vector
     float eps;
@@ -95,8 +94,6 @@ struct StackParams {
     uint32_t halfs[2];        // capacity of the two activation buffers in inputs (3 bytes each); the second may be 0
     unsigned int *local_bar;  // [0] arrivals of this GPU's blocks, [1] blocks that have finished; zero at launch, put back
                               // to zero by the last block of a launch
-    unsigned int *amax_words; // running maxima of the gate/up pairs (zero at launch, likewise)
-    uint32_t n_amax;
     int *error_flag;
     uint4 *partials;          // [kPartialSets][max_workers][32 lanes] of {sum a, tag, sum b, tag}
     unsigned int *launch_seq; // launches of this chain so far (read at the start, advanced at the end of the kernel)

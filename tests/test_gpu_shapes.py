@@ -288,12 +288,16 @@ def test_small_m_sweep_full_shapes_sampled(runtime, oracle, name, n, k, off):
     x = torch.empty(m_max * k, dtype=torch.bfloat16, device="cuda")
     runtime.synth_bf16(SEED, 8000 + k, m_max * k, x.data_ptr(), 0)
     xf = oracle.bf16_to_f32(x.view(torch.int16).cpu().numpy().view(np.uint16)).reshape(m_max, k)
+    # 512 weight rows at either end of the matrix, regenerated on the CPU; every comparison below is made on at least
+    # 512 values (512 rows at M = 1, 16 rows from M = 32), so each kernel family is held to its bar without allowance
+    span = 512
     samples = []
-    for r0 in (0, n - 16):
-        w, s, b = oracle.synth_q4(SEED, tensor, 16, k, row0=r0)
-        samples.append((r0, oracle.matmul_f64(xf, w, s, b, 16), oracle.matmul_bf16_tiles(xf, w, s, b, 16)))
+    for r0 in (0, n - span):
+        w, s, b = oracle.synth_q4(SEED, tensor, span, k, row0=r0)
+        samples.append((r0, oracle.matmul_f64(xf, w, s, b, span), oracle.matmul_bf16_tiles(xf, w, s, b, span, threads=8)))
     out = torch.zeros(m_max * n, dtype=torch.float32, device="cuda")
     for m in (1, 2, 4, 8, 16, 32, 64):
+        rows = max(16, span // m)
         for flag in (capi.FLAG_STREAM, capi.FLAG_TENSOR):
             out.zero_()
             runtime.matmul_batch_device(x.data_ptr(), capi.Q4B_BF16, m, k, [job], [out.data_ptr()], flag, 0)
@@ -301,14 +305,13 @@ def test_small_m_sweep_full_shapes_sampled(runtime, oracle, name, n, k, off):
             runtime.device_status()
             y = out[:m * n].cpu().numpy().reshape(m, n)
             for r0, exact, tiles in samples:
-                got = y[:, r0:r0 + 16]
+                got = y[:, r0:r0 + rows]
+                assert got.size >= 512
                 if flag == capi.FLAG_STREAM:
-                    assert oracle.rel_l2(got, exact[:m]) <= 1e-5, (m, r0)
+                    assert oracle.rel_l2(got, exact[:m, :rows]) <= 1e-5, (m, r0)
                 else:
-                    assert oracle.rel_l2(got, tiles[:m]) <= 2e-4, (m, r0)
-                    # against the exact oracle the distance is the bf16 rounding of w itself (about 1.5e-3; the
-                    # oracle's own 16-bit tile form is as far away), which scatters on a sample of a few dozen values
-                    assert oracle.rel_l2(got, exact[:m]) <= (2e-3 if got.size >= 512 else 3e-3), (m, r0)
+                    assert oracle.rel_l2(got, tiles[:m, :rows]) <= 2e-4, (m, r0)
+                    assert oracle.rel_l2(got, exact[:m, :rows]) <= 2e-3, (m, r0)
 
 
 @pytest.mark.parametrize("off", [0, 2], ids=["aligned", "at +2"])
