@@ -168,23 +168,18 @@ __device__ __forceinline__ void emit_block(const float (&v)[8], float scale, uin
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    uint32_t even[3] = {0, 0, 0}, odd[3] = {0, 0, 0};
+    // Signed digits from one addition: x' + 128 (1 + 256 + 65536) has the plain bytes d0 + 128, d1 + 128, d2 + 128
+    // (x' lies within +-2^22, so the sum is positive and below 2^24), and flipping bit 7 of a byte subtracts the 128.
+    uint32_t z[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int d0 = (xi[i] << 24) >> 24;
-        const int x1 = (xi[i] - d0) >> 8;
-        const int d1 = (x1 << 24) >> 24;
-        const int d2 = (x1 - d1) >> 8;
-        const uint32_t sh = 8u * (uint32_t)(i >> 1);
-        if (i & 1) {
-            odd[0] |= ((uint32_t)d0 & 0xffu) << sh;
-            odd[1] |= ((uint32_t)d1 & 0xffu) << sh;
-            odd[2] |= ((uint32_t)d2 & 0xffu) << sh;
-        } else {
-            even[0] |= ((uint32_t)d0 & 0xffu) << sh;
-            even[1] |= ((uint32_t)d1 & 0xffu) << sh;
-            even[2] |= ((uint32_t)d2 & 0xffu) << sh;
-        }
+    for (int i = 0; i < 8; ++i) z[i] = ((uint32_t)xi[i] + 0x00808080u) ^ 0x00808080u;
+    // plane c of the even inputs: byte c of z[0], z[2], z[4], z[6]; of the odd inputs: of z[1], z[3], z[5], z[7]
+    uint32_t even[3], odd[3];
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        const uint32_t sel = (uint32_t)c | ((4u + (uint32_t)c) << 4);
+        even[c] = __byte_perm(__byte_perm(z[0], z[2], sel), __byte_perm(z[4], z[6], sel), 0x5410u);
+        odd[c] = __byte_perm(__byte_perm(z[1], z[3], sel), __byte_perm(z[5], z[7], sel), 0x5410u);
     }
     if (in_range) {
         const uint32_t chunk = b >> 4, bb = b & 15u;
@@ -236,6 +231,77 @@ __device__ __forceinline__ void block_sum_max(float &sum, uint32_t &mx, float *r
     mx = top;
 }
 
+// Tagged vectors hold an fp32 value per 8-byte {value, tag} word; a block of 8 values is four 16-byte loads. The two
+// helpers below poll until every word of the wanted blocks carries `tag`. The wait is bounded; when it runs out the
+// error flag is raised and whatever was read is used (every block leaves at its next wait).
+__device__ __forceinline__ bool tagged_block_load(const uint4 *p0, uint32_t tag, uint4 (&q)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w) : "l"(p0 + i) : "memory");
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ok = ok && q[i].y == tag && q[i].w == tag;
+    return ok;
+}
+
+__device__ __forceinline__ bool tagged_wait_expired(const StackParams &sp, uint32_t &spins) {
+    if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
+        *sp.error_flag = 1;
+        return true;
+    }
+    __nanosleep(40);
+    return false;
+}
+
+// One block of 8 (if `have`), added to acc.
+__device__ __forceinline__ void add_tagged_block(const StackParams &sp, const uint8_t *vector, uint32_t b, bool have, uint32_t tag, float (&acc)[8]) {
+    if (!have) return;
+    const uint4 *p0 = reinterpret_cast<const uint4 *>(vector + (size_t)b * 64);
+    uint4 q[4];
+    uint32_t spins = 0;
+    while (!tagged_block_load(p0, tag, q))
+        if (tagged_wait_expired(sp, spins)) break;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += __uint_as_float(q[i].x);
+        acc[2 * i + 1] += __uint_as_float(q[i].z);
+    }
+}
+
+// Two blocks of 8 polled together: the loads of both are in flight at once, so a poll costs one round trip to L2
+// instead of two. The second block is optional.
+__device__ __forceinline__ void add_tagged_pair(const StackParams &sp, const uint8_t *vector, uint32_t b0, uint32_t b1, bool have1, uint32_t tag,
+                                                float (&acc0)[8], float (&acc1)[8]) {
+    if (!have1) {
+        add_tagged_block(sp, vector, b0, true, tag, acc0);
+        return;
+    }
+    const uint4 *p0 = reinterpret_cast<const uint4 *>(vector + (size_t)b0 * 64);
+    const uint4 *p1 = reinterpret_cast<const uint4 *>(vector + (size_t)b1 * 64);
+    uint4 q0[4], q1[4];
+    uint32_t spins = 0;
+    while (true) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q0[i].x), "=r"(q0[i].y), "=r"(q0[i].z), "=r"(q0[i].w) : "l"(p0 + i) : "memory");
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q1[i].x), "=r"(q1[i].y), "=r"(q1[i].z), "=r"(q1[i].w) : "l"(p1 + i) : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ok = ok && q0[i].y == tag && q0[i].w == tag && q1[i].y == tag && q1[i].w == tag;
+        if (ok) break;
+        if (tagged_wait_expired(sp, spins)) break;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        acc0[2 * i] += __uint_as_float(q0[i].x);
+        acc0[2 * i + 1] += __uint_as_float(q0[i].z);
+        acc1[2 * i] += __uint_as_float(q1[i].x);
+        acc1[2 * i + 1] += __uint_as_float(q1[i].z);
+    }
+}
+
 // bf16 vector | fp32 vector | bf16(silu(gate)*up) of two fp32 vectors | weightless RMS-norm of an fp32 vector given as
 // the sum of src_parts vectors (plain, or tagged words that are polled) | the hidden vector as a fused gate/up
 // epilogue left it (tagged pairs of bf16 values, polled; only this SM's slice is read and scaled by the slice's own
@@ -243,22 +309,67 @@ __device__ __forceinline__ void block_sum_max(float &sum, uint32_t &mx, float *r
 // [b_lo, b_hi): the 8-input blocks this SM holds (all of them, or the slice of a K-major phase; b_lo is a multiple of
 // 64 and X is offset so that block b_lo lands at the start of the buffer); [o_lo, o_hi): blocks this SM writes to the
 // optional bf16 copy.
-template <int WARPS>
+// ITERS: blocks of 8 a thread may hold (the caller picks the small instance when the vector is short: fewer registers
+// are live, and the polls of a thread's two blocks go out together).
+template <int WARPS, int ITERS>
 __device__ __forceinline__ void rebuild_general(const StackParams &sp, const StackPhase &P, const XBuf &X, float *red, uint32_t b_lo, uint32_t b_hi,
-                                                uint32_t o_lo, uint32_t o_hi, uint32_t src_tag) {
+                                                uint32_t o_lo, uint32_t o_hi, uint32_t src_tag, unsigned long long *tr) {
     constexpr uint32_t T = WARPS * 32;
     const uint32_t k = P.k;
     const uint32_t blocks = k / 8, blocks_p = P.kp / 8;
-    float v[kStackMaxIters][8];
+    float v[ITERS][8];
     float ss = 0.f;
     uint32_t amax = 0;
+    // Partial vectors of several ranks: every block first adds up ONE slice of them and publishes the sums as tagged
+    // words of their own; then all blocks read that one vector instead of all partial vectors (at 8 ranks: 40 KB per
+    // block instead of 320 KB). Eight lanes share a block of 8 values, one lane per rank, so all partial vectors are
+    // polled at once; the sum is then formed in rank order on every lane (the same order on every GPU).
+    uint32_t n_parts = P.src_parts;
+    const uint8_t *src_base = reinterpret_cast<const uint8_t *>(P.src0);
+    if (P.x_kind == kRebuildRms && P.src_tagged && P.src_sum) {
+        const uint32_t lo = blocks * blockIdx.x / gridDim.x, hi = blocks * (blockIdx.x + 1u) / gridDim.x;
+        const uint32_t part = threadIdx.x & 7u;
+        for (uint32_t b0 = lo; b0 < hi; b0 += T / 8) {
+            const uint32_t b = b0 + (threadIdx.x >> 3);
+            if (b0 + ((threadIdx.x & ~31u) >> 3) >= hi) continue;  // (uniform per warp) none of this warp's blocks exist
+            float mine[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            add_tagged_block(sp, src_base + (size_t)part * P.src_part_stride, b, b < hi && part < P.src_parts, src_tag, mine);
+            __syncwarp();
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (uint32_t r = 0; r < P.src_parts; ++r) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += __shfl_sync(0xffffffffu, mine[i], (int)((threadIdx.x & 24u) + r));
+            }
+            if (b < hi && part < 4) {
+                uint4 *dst = reinterpret_cast<uint4 *>(P.src_sum + (size_t)b * 64) + part;
+                const float lo_v = part == 0 ? acc[0] : part == 1 ? acc[2] : part == 2 ? acc[4] : acc[6];
+                const float hi_v = part == 0 ? acc[1] : part == 1 ? acc[3] : part == 2 ? acc[5] : acc[7];
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(lo_v)), "r"(src_tag), "r"(__float_as_uint(hi_v)),
+                             "r"(src_tag)
+                             : "memory");
+            }
+        }
+        src_base = P.src_sum;
+        n_parts = 1;
+    }
     // the hidden vector is read slice by slice (statistics of the slice); everything else needs the whole vector
     const uint32_t base = P.x_kind == kRebuildH ? b_lo : 0u, limit = P.x_kind == kRebuildH ? b_hi : blocks_p;
 #pragma unroll
-    for (int it = 0; it < kStackMaxIters; ++it) {
-        const uint32_t b = base + threadIdx.x + it * T;
+    for (int it = 0; it < ITERS; ++it)
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[it][i] = 0.f;
+    bool polled = false;
+    if (ITERS == 2 && P.x_kind == kRebuildRms && P.src_tagged) {
+        polled = true;
+        if (threadIdx.x < blocks) {
+            for (uint32_t part = 0; part < n_parts; ++part)
+                add_tagged_pair(sp, src_base + (size_t)part * P.src_part_stride, threadIdx.x, threadIdx.x + T, threadIdx.x + T < blocks, src_tag, v[0],
+                                v[ITERS - 1]);
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const uint32_t b = base + threadIdx.x + it * T;
         if (base + it * T >= limit) continue;  // (uniform) nothing left for any thread
         if (b < blocks && b < limit) {
             if (P.x_kind == kRebuildH) {
@@ -311,34 +422,12 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
                     v[it][i] = bf16_bits_to_float(float_to_bf16_bits(h));
                 }
             } else {
-                for (uint32_t part = 0; part < P.src_parts; ++part) {
-                    const uint8_t *base = reinterpret_cast<const uint8_t *>(P.src0) + (size_t)part * P.src_part_stride;
+                for (uint32_t part = 0; part < n_parts && !polled; ++part) {
+                    const uint8_t *vector = src_base + (size_t)part * P.src_part_stride;
                     if (P.src_tagged) {
-                        // {value, tag} words: wait (bounded) until all eight carry the producing phase's tag
-                        const uint4 *p0 = reinterpret_cast<const uint4 *>(base + (size_t)b * 64);
-                        uint4 q[4];
-                        uint32_t spins = 0;
-                        while (true) {
-                            bool ok = true;
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w) : "l"(p0 + i) : "memory");
-                                ok = ok && q[i].y == src_tag && q[i].w == src_tag;
-                            }
-                            if (ok) break;
-                            if (++spins > sp.spin_limit || *reinterpret_cast<volatile int *>(sp.error_flag)) {
-                                *sp.error_flag = 1;  // the values are wrong from here on; every block leaves at its next wait
-                                break;
-                            }
-                            __nanosleep(40);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            v[it][2 * i] += __uint_as_float(q[i].x);
-                            v[it][2 * i + 1] += __uint_as_float(q[i].z);
-                        }
+                        add_tagged_block(sp, vector, b, true, src_tag, v[it]);
                     } else {
-                        const float4 *p0 = reinterpret_cast<const float4 *>(base + (size_t)b * 32);
+                        const float4 *p0 = reinterpret_cast<const float4 *>(vector + (size_t)b * 32);
                         const float4 a0 = __ldcg(p0), a1 = __ldcg(p0 + 1);
                         v[it][0] += a0.x; v[it][1] += a0.y; v[it][2] += a0.z; v[it][3] += a0.w;
                         v[it][4] += a1.x; v[it][5] += a1.y; v[it][6] += a1.z; v[it][7] += a1.w;
@@ -356,28 +445,32 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
             for (int i = 0; i < 8; ++i) amax = max(amax, __float_as_uint(v[it][i]) & 0x7fffffffu);
         }
     }
+    if (tr) tr[7] = stack_ns();  // thread 0 has its source values
     block_sum_max<WARPS>(ss, amax, red);
+    if (tr) tr[8] = stack_ns();
     if (P.x_kind == kRebuildRms) {
         const float inv = rsqrtf(ss / (float)k + P.eps);
         // rounding is monotonic, so the largest rounded magnitude is the rounded largest magnitude
         amax = float_to_bf16_bits(__uint_as_float(amax) * inv) << 16;
 #pragma unroll
-        for (int it = 0; it < kStackMaxIters; ++it) {
+        for (int it = 0; it < ITERS; ++it) {
             if (base + it * T >= limit) continue;
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[it][i] = bf16_bits_to_float(float_to_bf16_bits(v[it][i] * inv));
         }
     }
+    if (tr) tr[9] = stack_ns();
     const int e = scale_exponent(amax);
     const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
     if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
 #pragma unroll
-    for (int it = 0; it < kStackMaxIters; ++it) {
+    for (int it = 0; it < ITERS; ++it) {
         const uint32_t b = base + threadIdx.x + it * T;
         if (base + it * T >= limit) continue;
         emit_block(v[it], scale, b, b >= b_lo && b < b_hi, X);
         if (P.x_bf16_out && b >= o_lo && b < o_hi && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = pack_bf16x8(v[it]);
     }
+    if (tr) tr[10] = stack_ns();
     __syncthreads();
 }
 
@@ -605,6 +698,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     float *xsum1 = xsum0 + sp.halfs[0] / 64 + 4;
     float *misc = xsum1 + sp.halfs[1] / 64 + 4;
     uint32_t *arrive_smem = reinterpret_cast<uint32_t *>(misc + 2);
+    uint32_t *units_done_smem = reinterpret_cast<uint32_t *>(misc + 70);  // warps of this block through with a phase, running count
     float *red = misc + 4;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * kStackRingBytes;
     const uint32_t pring = ring + kStages * kStageBytesAligned;
@@ -646,6 +740,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     request_phase(0);
     if (threadIdx.x == 0) {
         *arrive_smem = 0;
+        *units_done_smem = 0;
         *gbase_smem = sp.peers ? *reinterpret_cast<volatile unsigned long long *>(sp.peers->consumed) : 0ull;
         reinterpret_cast<uint32_t *>(misc)[3] = *reinterpret_cast<volatile unsigned int *>(sp.launch_seq);
     }
@@ -698,11 +793,19 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             // the bf16 copy of the activation is written by block 0, or by the first kparts blocks (one part each)
             const bool writes = blockIdx.x < ((P.kparts > 1u && P.sliced) ? P.kparts : 1u);
             const uint32_t o_lo = writes ? c_lo * 16u : 0u, o_hi = writes ? c_hi * 16u : 0u;
-            if (P.x_kind != kRebuildNone) rebuild_general<WARPS>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase);
+            if (P.x_kind != kRebuildNone) {
+                unsigned long long *tr = (sp.trace && threadIdx.x == 0) ? trace_slot() : nullptr;
+                const uint32_t held = P.x_kind == kRebuildH ? c_hi * 16u - cs4 * 16u : P.kp / 8u;
+                if (held <= 2u * WARPS * 32u)
+                    rebuild_general<WARPS, 2>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase, tr);
+                else
+                    rebuild_general<WARPS, kStackMaxIters>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase, tr);
+            }
             if (sp.trace && threadIdx.x == 0) trace_slot()[2] = stack_ns();
         }
 
         bool stored_to_peers = false;
+        uint32_t blocks_done = 0;
         uint32_t dbg_i = 0;
         uint32_t u = 0, u1 = 0;  // this warp's units of the phase (a phase has fewer than 2^32)
         if (worker < P.workers) {
@@ -822,6 +925,8 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                 const TileEnd te{sg.job, sg.tile_local, sg.tile_row, sg.c0v, sg.c1v};
                 u += sg.c1v - sg.c0v;
                 more = u < u1;
+                // (a hint, read while the last tile is being finished: how many blocks are through with this phase)
+                if (!more && (sp.flags & kFlagLateSkipsRequest)) blocks_done = *reinterpret_cast<volatile unsigned int *>(sp.local_bar + kProgressWord);
                 if (more) {
                     segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
                     segment_prologue(sg, ring, pring, lane);
@@ -837,6 +942,14 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             }
         }
         if (sp.trace && threadIdx.x == 0) trace_slot()[3] = stack_ns();
+        if (sp.trace && lane == 0) {
+            atomicMax(trace_slot() + 6, stack_ns());  // the block's last warp
+            if (warp == 0) {
+                uint32_t smid;
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                trace_slot()[5] = smid;
+            }
+        }
         if (sp.dbg && ph == sp.dbg_phase && lane == 0) {
             sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 62] = stack_ns();
             sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 63] = dbg_i;
@@ -847,7 +960,27 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             ++sync.local_gen;
             if (P.arrive_kind == kSyncGlobal) ++sync.global_gen;
         }
-        request_phase(ph + 1u);
+        // The next phase's first weights: requested now when nothing stands between this phase and the next one's
+        // units; after the rebuild when there is one (kFlagRequestAfterRebuild) -- the polls and shared-memory stores
+        // of a rebuild queue behind the copies a warp has in flight, which costs the last block to finish (the one
+        // all others are waiting for) several microseconds per phase.
+        //
+        // kFlagLateSkipsRequest does that only for the warps that finish when nearly every block is through with the
+        // phase: the blocks that are waiting anyway keep filling their rings during the wait. Blocks count themselves
+        // in one word (the last warp of a block adds one per phase); the count is a hint and orders nothing.
+        bool request_later = (sp.flags & kFlagRequestAfterRebuild) != 0;
+        if (sp.flags & kFlagLateSkipsRequest) {
+            if (lane == 0) {
+                const uint32_t through = atomicAdd(units_done_smem, 1u) + 1u;
+                if (through % WARPS == 0) atomicAdd(sp.local_bar + kProgressWord, 1u);
+            }
+            const uint32_t margin = (sp.flags >> 8) & 0xffu;
+            request_later = blocks_done >= ph * gridDim.x + gridDim.x - margin && blocks_done < (ph + 1u) * gridDim.x + gridDim.x;
+        }
+        if (request_later && ph + 1u < sp.n_phases && sp.phases[ph + 1u].x_kind != kRebuildNone)
+            prefetched = false;  // (the phase's own start requests them)
+        else
+            request_phase(ph + 1u);
     }
 
     // ---- logits -> token: per-block candidates, barrier, block 0 picks (ties to the lowest index) ----
@@ -931,6 +1064,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             __threadfence();
             sp.local_bar[0] = 0;
             sp.local_bar[1] = 0;
+            sp.local_bar[kProgressWord] = 0;
             if (sp.peers) *sp.peers->consumed = *gbase_smem + (unsigned long long)sync.global_gen * sp.peers->world;
             *sp.launch_seq = reinterpret_cast<uint32_t *>(misc)[3] + 1u;
         }

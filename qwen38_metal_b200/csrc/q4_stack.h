@@ -69,6 +69,8 @@ struct StackPhase {
     uint32_t src_parts, src_part_stride;  // Rms: the vector is the sum, in order, of src_parts vectors this many bytes apart
     uint32_t src_tagged;          // Rms: the source vectors are {value, tag} words written by phase src_tag_phase of this
     uint32_t src_tag_phase;       //      launch; the rebuild polls until every word carries that phase's tag (H: always)
+    uint8_t *src_sum;             // Rms over tagged partial vectors of several ranks: where the blocks publish the sum (tagged
+                                  // words, 8 bytes per element), or null to read the partial vectors directly
     uint16_t *x_bf16_out;         // optional: block 0 stores the bf16 activation it built
     float *sum_out;               // optional (Rms): block 0 stores the summed fp32 vector
     float eps;
@@ -119,9 +121,13 @@ struct InlineProgram {
     StackJob jobs[kMaxJobs];
 };
 
+constexpr uint32_t kFlagRequestAfterRebuild = 2u;  // a phase that rebuilds its activation requests its first weights after the rebuild
+constexpr uint32_t kFlagLateSkipsRequest = 4u;     // ... only for warps that finish a phase when all but (flags >> 8 & 255) blocks are through
+constexpr uint32_t kProgressWord = 32;             // local_bar[kProgressWord]: blocks through with a phase, summed over the launch
 constexpr uint32_t kFlagWarpFenceGpu = 1u;  // every warp fences at device scope before it arrives (default: block scope)
 
-constexpr uint32_t kTraceStamps = 8;  // wait begin, wait end, rebuild end, warp 0 units end, block's arrival, -, -, -
+constexpr uint32_t kTraceStamps = 16;  // wait begin, wait end, rebuild end, warp 0 units end, block's arrival, SM id, last warp's units end,
+                                      // thread 0 has read its source values (inside the rebuild)
 
 }  // namespace q4
 

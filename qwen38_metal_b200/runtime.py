@@ -358,16 +358,16 @@ class DecodeChain:
         return n.value
 
     def trace_read(self):
-        """(stamps [blocks][phases][8] uint64 ns, phase_info [phases]) of the last run; the chain must have been
+        """(stamps [blocks][phases][16] uint64 ns, phase_info [phases]) of the last run; the chain must have been
         created after CudaRuntime.trace_enable(True)."""
         phases = self.phase_count()
         sms = self._rt.device_info()["sm_count"]
-        stamps = np.zeros(sms * phases * 8, dtype=np.uint64)
+        stamps = np.zeros(sms * phases * 16, dtype=np.uint64)
         info = np.zeros(phases, dtype=np.uint32)
         nb, nph = C.c_uint32(), C.c_uint32()
         _check(self._rt._lib.q4b_chain_trace_read(self._h, stamps.ctypes.data_as(C.c_void_p), stamps.size, C.byref(nb),
                                                   C.byref(nph), info.ctypes.data_as(C.c_void_p), phases))
-        return stamps.reshape(nb.value, nph.value, 8), info
+        return stamps.reshape(nb.value, nph.value, 16), info
 
     def close(self) -> None:
         if self._h:
