@@ -320,38 +320,11 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
     float v[ITERS][8];
     float ss = 0.f;
     uint32_t amax = 0;
-    // Partial vectors of several ranks: every block first adds up ONE slice of them and publishes the sums as tagged
-    // words of their own; then all blocks read that one vector instead of all partial vectors (at 8 ranks: 40 KB per
-    // block instead of 320 KB). Eight lanes share a block of 8 values, one lane per rank, so all partial vectors are
-    // polled at once; the sum is then formed in rank order on every lane (the same order on every GPU).
-    uint32_t n_parts = P.src_parts;
+    // (The partial vectors of several ranks are read part after part by every block. Adding them up once per GPU and
+    // sharing the sum was tried and is slower at 2, 4 and 8 ranks: it makes every block wait for every other block's
+    // arrival at the rebuild, which a direct read does not.)
+    const uint32_t n_parts = P.src_parts;
     const uint8_t *src_base = reinterpret_cast<const uint8_t *>(P.src0);
-    if (P.x_kind == kRebuildRms && P.src_tagged && P.src_sum) {
-        const uint32_t lo = blocks * blockIdx.x / gridDim.x, hi = blocks * (blockIdx.x + 1u) / gridDim.x;
-        const uint32_t part = threadIdx.x & 7u;
-        for (uint32_t b0 = lo; b0 < hi; b0 += T / 8) {
-            const uint32_t b = b0 + (threadIdx.x >> 3);
-            if (b0 + ((threadIdx.x & ~31u) >> 3) >= hi) continue;  // (uniform per warp) none of this warp's blocks exist
-            float mine[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            add_tagged_block(sp, src_base + (size_t)part * P.src_part_stride, b, b < hi && part < P.src_parts, src_tag, mine);
-            __syncwarp();
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (uint32_t r = 0; r < P.src_parts; ++r) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] += __shfl_sync(0xffffffffu, mine[i], (int)((threadIdx.x & 24u) + r));
-            }
-            if (b < hi && part < 4) {
-                uint4 *dst = reinterpret_cast<uint4 *>(P.src_sum + (size_t)b * 64) + part;
-                const float lo_v = part == 0 ? acc[0] : part == 1 ? acc[2] : part == 2 ? acc[4] : acc[6];
-                const float hi_v = part == 0 ? acc[1] : part == 1 ? acc[3] : part == 2 ? acc[5] : acc[7];
-                asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(lo_v)), "r"(src_tag), "r"(__float_as_uint(hi_v)),
-                             "r"(src_tag)
-                             : "memory");
-            }
-        }
-        src_base = P.src_sum;
-        n_parts = 1;
-    }
     // the hidden vector is read slice by slice (statistics of the slice); everything else needs the whole vector
     const uint32_t base = P.x_kind == kRebuildH ? b_lo : 0u, limit = P.x_kind == kRebuildH ? b_hi : blocks_p;
 #pragma unroll

@@ -133,13 +133,12 @@ struct q4b_runtime {
     std::vector<void *> arenas, peer_arenas;
     Pool trace, gemm_x, gemm_parts, error_flag;
     uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
-    uint32_t chain_offset_cost = 120;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
+    uint32_t chain_offset_cost = 140;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
     uint32_t chain_defer_split = 50;   // per cent of a stage's deferred rows that run behind its own barrier (the rest behind the next one)
     uint32_t chain_spin_limit = 1u << 21;  // polls before a chain's barrier wait gives up
     // Deferred projections (run behind a barrier's arrival) are off unless asked for: measured on B200 the extra runs
     // of chunks they create cost more than the barrier time they cover.
     bool chain_no_fusion = false, chain_no_deferral = true;
-    uint32_t chain_sum_ranks = 8;      // ranks from which the partial down outputs are added up once per GPU (two-step rebuild)
     bool chain_no_handoff = false;     // keep a barrier between a projection and the RMS-norm that consumes it
     bool chain_split_tiles = true;     // a phase with fewer tiles than warps gives every tile the same number of warps
     uint32_t chain_flags = 4u | (16u << 8);  // kFlagLateSkipsRequest, margin 16 blocks
@@ -530,7 +529,6 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     if (const char *mode = getenv("Q4B_CHAIN_SPLIT")) rt->chain_split_tiles = strcmp(mode, "equal") != 0;
     if (const char *fl = getenv("Q4B_CHAIN_FLAGS")) rt->chain_flags = (uint32_t)strtol(fl, nullptr, 10);
     if (const char *plain = getenv("Q4B_CHAIN_PLAIN")) rt->chain_no_fusion = strtol(plain, nullptr, 10) != 0;  // no gate/up fusion
-    if (const char *sr = getenv("Q4B_CHAIN_SUM_RANKS")) rt->chain_sum_ranks = (uint32_t)strtol(sr, nullptr, 10);
     if (const char *hand = getenv("Q4B_CHAIN_HANDOFF")) rt->chain_no_handoff = strtol(hand, nullptr, 10) == 0;
     if (const char *defer = getenv("Q4B_CHAIN_DEFER")) rt->chain_no_deferral = strtol(defer, nullptr, 10) == 0;
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
@@ -1569,13 +1567,6 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
                     j.ll_out[r] = slot ? (unsigned long long *)(slot + copy) : nullptr;
                 }
                 C.src0 = (const uint8_t *)stages[si + 1].src0 + copy;
-                if (peers->world >= rt->chain_sum_ranks) {
-                    // from this many ranks on, the blocks add up the partial vectors once and share the sum
-                    uint8_t *sum = nullptr;
-                    e = build.alloc((void **)&sum, (size_t)j.n * 8 + 256, true);
-                    if (e != cudaSuccess) return fail_cuda(e, "decode chain allocation");
-                    C.src_sum = sum;
-                }
             }
         }
     }

@@ -69,8 +69,6 @@ struct StackPhase {
     uint32_t src_parts, src_part_stride;  // Rms: the vector is the sum, in order, of src_parts vectors this many bytes apart
     uint32_t src_tagged;          // Rms: the source vectors are {value, tag} words written by phase src_tag_phase of this
     uint32_t src_tag_phase;       //      launch; the rebuild polls until every word carries that phase's tag (H: always)
-    uint8_t *src_sum;             // Rms over tagged partial vectors of several ranks: where the blocks publish the sum (tagged
-                                  // words, 8 bytes per element), or null to read the partial vectors directly
     uint16_t *x_bf16_out;         // optional: block 0 stores the bf16 activation it built
     float *sum_out;               // optional (Rms): block 0 stores the summed fp32 vector
     float eps;
