@@ -143,14 +143,6 @@ struct XBuf {
     float *inv;    // inverse of the power-of-two scaling
 };
 
-// The activation is held as 23-bit fixed point: x' = round(x * 2^e) with 2^e putting the largest magnitude into
-// [2^21, 2^22). A bf16 value within 2^14 of the maximum is represented exactly, smaller ones to 2^-22 of the maximum.
-// e = 0 for an all-zero vector.
-__device__ __forceinline__ int scale_exponent(uint32_t amax_bits) {
-    const int e = 21 - ((int)((amax_bits >> 23) & 0xffu) - 127);
-    return amax_bits == 0 ? 0 : max(-100, min(100, e));
-}
-
 // x' is stored as three signed 8-bit digits, x' = d0 + 256 d1 + 65536 d2 with every digit in [-128, 127], one 128-byte
 // plane per digit and chunk. Inside a plane the byte order is the one the tensor-core B fragment of the integer MMA
 // (m16n8k32) wants, given that lane t of a quad feeds its own 32 consecutive nibbles of a weight row as A operand:
@@ -629,12 +621,6 @@ __device__ __forceinline__ uint32_t phase_worker(const StackPhase &P, uint32_t w
     return tile < P.tiles ? tile * P.kparts + blockIdx.x % P.kparts : 0xffffffffu;
 }
 
-__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // One chunk on the integer tensor-core path: d = sum over the chunk of q * digit for rows g (d[0], d[1]) and g+8 (d[2],
 // d[3]) and the lane's two result columns. A packed word becomes two byte registers with three logic instructions
 // (even nibbles: w & 0x0f0f0f0f, odd nibbles: (w >> 4) & 0x0f0f0f0f); the products are exact integers.
@@ -655,9 +641,6 @@ __device__ __forceinline__ void chunk_mma_i8(const uint4 &cwa, const uint4 &cwb,
     mma_u8s8_16832(d, la[2], lb[2], la[3], lb[3], xr[1].x, xr[1].y);
     mma_u8s8_16832(d, ha[2], hb[2], ha[3], hb[3], xr[1].z, xr[1].w);
 }
-
-// exact for |i| < 2^22
-__device__ __forceinline__ float small_int_to_float(int i) { return __int_as_float(i + 0x4B400000) - 12582912.0f; }
 
 template <int WARPS>
 __device__ __forceinline__ void stack_body(const StackParams &sp) {

@@ -88,6 +88,12 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
     return v;
 }
 
+__device__ __forceinline__ uint32_t lds_u32(uint32_t smem_addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ uint2 lds_v2(uint32_t smem_addr) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(smem_addr) : "memory");
@@ -193,5 +199,27 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 }
 
 __device__ __forceinline__ float silu(float v) { return v * (1.0f / (1.0f + __expf(-v))); }
+
+// ---- integer tensor-core path (persistent decode kernel, short-batch kernel) ----
+
+// The activation is held as 23-bit fixed point: x' = round(x * 2^e) with 2^e putting the largest magnitude into
+// [2^21, 2^22). A bf16 value within 2^14 of the maximum is represented exactly, smaller ones to 2^-22 of the maximum.
+// e = 0 for an all-zero vector.
+__device__ __forceinline__ int scale_exponent(uint32_t amax_bits) {
+    const int e = 21 - ((int)((amax_bits >> 23) & 0xffu) - 127);
+    return amax_bits == 0 ? 0 : max(-100, min(100, e));
+}
+
+
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+
+// exact for |i| < 2^22
+__device__ __forceinline__ float small_int_to_float(int i) { return __int_as_float(i + 0x4B400000) - 12582912.0f; }
+
 
 }  // namespace q4

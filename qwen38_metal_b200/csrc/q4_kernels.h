@@ -54,6 +54,32 @@ struct GemvParams {
 
 constexpr int kMaxPeers = 8;
 
+// Short-batch kernel (q4_gemv_rows.cu): up to 16 activation rows, all tensors on 16-byte boundaries, K % 128 == 0.
+struct RowsJob {
+    const uint8_t *w, *s, *b;
+    float *out;            // [m][out_stride] fp32
+    uint32_t n;            // output rows
+    uint32_t out_stride;
+    uint32_t tile_begin;   // first 16-row tile of this job in the launch
+    uint32_t pad;
+};
+
+struct RowsParams {
+    RowsJob jobs[kMaxJobs];
+    uint32_t n_jobs;
+    uint32_t m;            // activation rows, 1..16
+    const void *x;         // [m][k] bf16 or fp32, 16-byte aligned
+    uint32_t x_is_f32;
+    uint32_t k, groups, cpt;  // inputs, k / 64, k / 128
+    uint32_t parts;        // runs the K range is cut into (q4k_rows_plan)
+    uint32_t part_chunks;  // chunks of the longest run
+    uint32_t tiles;        // 16-row tiles of all jobs
+    uint32_t accumulate;
+    float *partials;       // [parts][8 or 16][tiles * 16] fp32, used when parts > 1
+    unsigned int *counters;  // [tiles], zero between launches
+    unsigned long long *trace;  // optional [warps of the grid][4] globaltimer stamps (start, digits ready, first tile streamed, done)
+};
+
 }  // namespace q4
 
 extern "C" {
@@ -61,6 +87,9 @@ cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t
                           uint16_t *xp, float *xsum, float *row_inv, cudaStream_t stream);
 cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int aligned, cudaStream_t stream);  // one warp per block
 uint32_t q4k_gemv_occupancy(int column_tiles, int aligned);  // resident warps per SM, 0 on error
+
+uint32_t q4k_rows_plan(uint32_t m, uint32_t k, uint32_t tiles, uint32_t sm_count, uint32_t *part_chunks);  // parts, 0: unsupported
+cudaError_t q4k_rows(const q4::RowsParams *params, uint32_t sm_count, cudaStream_t stream);
 
 cudaError_t q4k_swiglu(const float *gate, const float *up, uint64_t count, float *out_f32, uint16_t *out_bf16,
                        cudaStream_t stream);

@@ -132,7 +132,8 @@ struct q4b_runtime {
     uint32_t max_workers = 0;
     std::vector<void *> arenas, peer_arenas;
     Pool trace, gemm_x, gemm_parts, error_flag;
-    uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over
+    uint32_t gemm_min_m = 16;  // activation rows from which the tensor-core GEMM takes over (when the short-batch kernel does not apply)
+    uint32_t rows_max_m = 16;  // activation rows per launch of the short-batch kernel (0: never use it)
     uint32_t chain_offset_cost = 140;  // per cent: cost of a byte-offset projection's chunk against an aligned one (decode chain)
     uint32_t chain_defer_split = 50;   // per cent of a stage's deferred rows that run behind its own barrier (the rest behind the next one)
     uint32_t chain_spin_limit = 1u << 21;  // polls before a chain's barrier wait gives up
@@ -146,6 +147,7 @@ struct q4b_runtime {
     uint64_t prof_flops = 0;
     bool tracing = false;
     uint32_t trace_workers = 0;
+    Pool rows_partials, rows_counters;
     Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
     Pool outs[q4::kMaxJobs];
     HostPool results;  // staging for downloads (host-buffer entry points)
@@ -442,11 +444,102 @@ int enqueue_gemm(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, ui
     return Q4B_OK;
 }
 
-// Any m, any number of jobs: tensor-core GEMM from gemm_min_m rows, else launches the streaming kernel accepts.
+// Short batches on the integer tensor-core path (q4_gemv_rows.cu). Returns -1 when the call does not meet the kernel's
+// conditions (the caller falls back to the general streaming kernel), else a status.
+int launch_rows(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m, uint32_t k, const Resolved *jobs, uint32_t n_jobs,
+                float *const *outs, uint32_t flags, cudaStream_t stream) {
+    if (m < 1 || m > 16 || k % 512u != 0 || ((uintptr_t)x_dev & 15u)) return -1;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        if ((((uintptr_t)jobs[i].w | (uintptr_t)jobs[i].s | (uintptr_t)jobs[i].b) & 15u) != 0 || jobs[i].n == 0) return -1;
+        tiles += (jobs[i].n + 15u) / 16u;
+    }
+    uint32_t part_chunks = 0;
+    const uint32_t parts = q4k_rows_plan(m, k, tiles, (uint32_t)rt->sm_count, &part_chunks);
+    if (parts == 0) return -1;
+    q4::RowsParams p;
+    memset(&p, 0, sizeof p);
+    uint64_t prof_bytes = 0, prof_rows = 0;
+    uint32_t t0 = 0;
+    for (uint32_t i = 0; i < n_jobs; ++i) {
+        q4::RowsJob &j = p.jobs[i];
+        j.w = jobs[i].w;
+        j.s = jobs[i].s;
+        j.b = jobs[i].b;
+        j.out = outs[i];
+        j.n = jobs[i].n;
+        j.out_stride = jobs[i].n;
+        j.tile_begin = t0;
+        t0 += (jobs[i].n + 15u) / 16u;
+        prof_bytes += (uint64_t)jobs[i].n * (k / 2 + (uint64_t)(k / 64) * 4) + (uint64_t)m * jobs[i].n * 4;
+        prof_rows += jobs[i].n;
+    }
+    p.n_jobs = n_jobs;
+    p.m = m;
+    p.x = x_dev;
+    p.x_is_f32 = x_dtype == Q4B_F32 ? 1u : 0u;
+    p.k = k;
+    p.groups = k / 64u;
+    p.cpt = k / 128u;
+    p.parts = parts;
+    p.part_chunks = part_chunks;
+    p.tiles = tiles;
+    p.accumulate = (flags & Q4B_FLAG_ACCUMULATE) ? 1u : 0u;
+    if (parts > 1) {
+        const size_t mp = m <= 8 ? 8 : 16;
+        Q4B_CUDA(rt->rows_partials.ensure((size_t)parts * mp * tiles * 16 * 4), "partial sum scratch");
+        const size_t had = rt->rows_counters.capacity;
+        Q4B_CUDA(rt->rows_counters.ensure((size_t)tiles * 4), "tile counter scratch");
+        if (rt->rows_counters.capacity != had) Q4B_CUDA(cudaMemsetAsync(rt->rows_counters.ptr, 0, rt->rows_counters.capacity, stream), "tile counter reset");
+        p.partials = (float *)rt->rows_partials.ptr;
+        p.counters = (unsigned int *)rt->rows_counters.ptr;
+    }
+    const uint32_t grid_warps = ((uint32_t)rt->sm_count / parts) * parts * 16u;
+    if (rt->tracing && grid_warps <= rt->max_workers) {
+        p.trace = (unsigned long long *)rt->trace.ptr;
+        rt->trace_workers = grid_warps;
+    }
+    if (int st = profile_open(rt, stream)) return st;
+    Q4B_CUDA(q4k_rows(&p, (uint32_t)rt->sm_count, stream), "q4_rows launch");
+    rt->launches++;
+    return profile_close(rt, stream, prof_bytes + (uint64_t)m * k * (x_dtype == Q4B_F32 ? 4 : 2), 2ull * m * prof_rows * k);
+}
+
+// Any m, any number of jobs: the short-batch kernel up to rows_max_m rows where it applies, the tensor-core GEMM from
+// gemm_min_m rows, else launches the streaming kernel accepts.
 int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, uint64_t k,
                    const std::vector<Resolved> &jobs, float *const *outs, uint32_t flags, cudaStream_t stream) {
-    const bool tensor = (flags & Q4B_FLAG_TENSOR) ? true : (flags & Q4B_FLAG_STREAM) ? false : m >= rt->gemm_min_m;
-    if (tensor) return enqueue_gemm(rt, x_dev, x_dtype, m, k, jobs, outs, flags, stream);
+    const bool want_tensor = (flags & Q4B_FLAG_TENSOR) != 0, want_stream = (flags & Q4B_FLAG_STREAM) != 0;
+    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
+    // Short batches (2 .. rows_max_m rows; any m when the caller asks for the streaming form) run on the integer
+    // tensor-core kernel when every launch of the call meets its conditions.
+    bool rows = !want_tensor && m >= 2 && rt->rows_max_m >= 2 && (want_stream || m <= rt->rows_max_m) && k % 512 == 0 &&
+                ((uintptr_t)x_dev & 15u) == 0;
+    for (size_t j = 0; j < jobs.size() && rows; ++j)
+        rows = (((uintptr_t)jobs[j].w | (uintptr_t)jobs[j].s | (uintptr_t)jobs[j].b) & 15u) == 0 && jobs[j].n != 0;
+    for (size_t j0 = 0; j0 < jobs.size() && rows; j0 += q4::kMaxJobs) {
+        uint32_t tiles = 0, part_chunks = 0;
+        for (size_t j = j0; j < jobs.size() && j < j0 + q4::kMaxJobs; ++j) tiles += (jobs[j].n + 15u) / 16u;
+        const uint32_t full = (uint32_t)(m < rt->rows_max_m ? m : rt->rows_max_m), rest = (uint32_t)(m % rt->rows_max_m);
+        rows = q4k_rows_plan(full, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks) != 0 &&
+               (m <= rt->rows_max_m || rest == 0 || q4k_rows_plan(rest, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks) != 0);
+    }
+    if (rows) {
+        for (uint64_t m0 = 0; m0 < m; m0 += rt->rows_max_m) {
+            const uint32_t mb = (uint32_t)((m - m0) < rt->rows_max_m ? (m - m0) : rt->rows_max_m);
+            const uint8_t *xb = (const uint8_t *)x_dev + m0 * k * esize;
+            for (size_t j0 = 0; j0 < jobs.size(); j0 += q4::kMaxJobs) {
+                const uint32_t nj = (uint32_t)((jobs.size() - j0) < (size_t)q4::kMaxJobs ? (jobs.size() - j0) : (size_t)q4::kMaxJobs);
+                float *o[q4::kMaxJobs];
+                for (uint32_t i = 0; i < nj; ++i) o[i] = outs[j0 + i] + m0 * jobs[j0 + i].n;
+                const int st = launch_rows(rt, xb, x_dtype, mb, (uint32_t)k, &jobs[j0], nj, o, flags, stream);
+                if (st == -1) return fail(Q4B_CUDA_ERROR, "short-batch launch refused a call its conditions admit");
+                if (st != Q4B_OK) return st;
+            }
+        }
+        return Q4B_OK;
+    }
+    if (want_tensor || (!want_stream && m >= rt->gemm_min_m)) return enqueue_gemm(rt, x_dev, x_dtype, m, k, jobs, outs, flags, stream);
     if (m == 1 && !(flags & Q4B_FLAG_ACCUMULATE) && rt->inline_max_halfs && k % 512 == 0 && k <= rt->inline_max_halfs && k <= q4k_stack_max_k()) {
         for (size_t j0 = 0; j0 < jobs.size(); j0 += q4::kMaxJobs) {
             const uint32_t nj = (uint32_t)((jobs.size() - j0) < (size_t)q4::kMaxJobs ? (jobs.size() - j0) : (size_t)q4::kMaxJobs);
@@ -455,7 +548,6 @@ int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, 
         return Q4B_OK;
     }
     const uint32_t rows_per_launch = x_dtype == Q4B_F32 ? 2u : 8u;
-    const size_t esize = x_dtype == Q4B_F32 ? 4 : 2;
     for (uint64_t m0 = 0; m0 < m; m0 += rows_per_launch) {
         const uint32_t mb = (uint32_t)((m - m0) < rows_per_launch ? (m - m0) : rows_per_launch);
         const uint8_t *xb = (const uint8_t *)x_dev + m0 * k * esize;
@@ -532,6 +624,10 @@ extern "C" int q4b_runtime_create(int device_ordinal, q4b_runtime **out) {
     if (const char *hand = getenv("Q4B_CHAIN_HANDOFF")) rt->chain_no_handoff = strtol(hand, nullptr, 10) == 0;
     if (const char *defer = getenv("Q4B_CHAIN_DEFER")) rt->chain_no_deferral = strtol(defer, nullptr, 10) == 0;
     if (const char *force = getenv("Q4B_FORCE_VARIANT")) rt->force_variant = force;
+    if (const char *rm = getenv("Q4B_ROWS_MAX_M")) {
+        const long v = strtol(rm, nullptr, 10);
+        if (v >= 0 && v <= 16) rt->rows_max_m = (uint32_t)v;
+    }
     if (rt->force_variant == "stream") rt->gemm_min_m = 0xffffffffu;   // never use the tensor-core GEMM
     if (rt->force_variant == "tensor") rt->gemm_min_m = 1;            // always use it
     if (const char *min_m = getenv("Q4B_GEMM_MIN_M")) {
@@ -595,7 +691,7 @@ extern "C" void q4b_runtime_destroy(q4b_runtime *rt) {
         if (s.ptr) cudaFree(s.ptr);
     for (void *p : rt->peer_arenas) cudaIpcCloseMemHandle(p);
     for (void *p : rt->arenas) cudaFree(p);
-    Pool *pools[] = {&rt->gemm_x, &rt->gemm_parts, &rt->error_flag, &rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
+    Pool *pools[] = {&rt->rows_partials, &rt->rows_counters, &rt->gemm_x, &rt->gemm_parts, &rt->error_flag, &rt->trace, &rt->x_in, &rt->xp, &rt->xsum, &rt->row_inv, &rt->partials, &rt->counters, &rt->logits, &rt->amax_v,
                      &rt->amax_i, &rt->tokens, &rt->gate, &rt->up, &rt->hidden};
     for (Pool *p : pools) p->release();
     for (Pool &p : rt->outs) p.release();
@@ -1793,6 +1889,21 @@ extern "C" int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, u
     for (const Resolved &r : resolved) fast += job_is_fast(r, (uint32_t)(k / 64)) ? 1u : 0u;
     if (m == 1 && rt->inline_max_halfs && k % 512 == 0 && k <= rt->inline_max_halfs && k <= q4k_stack_max_k()) {
         snprintf(text, text_len, "single_row_i8 one-phase persistent launch, jobs=%u (byte-addressed %u)", n_jobs, n_jobs - fast);
+        return Q4B_OK;
+    }
+    if (m >= 2 && m <= rt->rows_max_m && fast == n_jobs && k % 512 == 0) {
+        uint32_t tiles = 0, part_chunks = 0;
+        for (const Resolved &r : resolved) tiles += (r.n + 15u) / 16u;
+        const uint32_t mb = (uint32_t)(m < rt->rows_max_m ? m : rt->rows_max_m);
+        const uint32_t parts = q4k_rows_plan(mb, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks);
+        if (parts) {
+            snprintf(text, text_len, "rows_i8 (short batch, integer tensor cores) rows_per_launch=%u k_parts=%u chunks_per_part=%u jobs=%u (a 16-byte aligned activation is assumed)",
+                     mb, parts, part_chunks, n_jobs);
+            return Q4B_OK;
+        }
+    }
+    if (m >= rt->gemm_min_m) {
+        snprintf(text, text_len, "tensor_core_gemm (tcgen05) tile_m=%u jobs=%u", q4k_gemm_tile_m((uint32_t)m), n_jobs);
         return Q4B_OK;
     }
     const uint32_t rows = x_dtype == Q4B_F32 ? 2u : 8u;

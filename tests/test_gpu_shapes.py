@@ -54,7 +54,7 @@ def test_short_batch_widths_bf16(runtime, oracle, m):
     job = upload_matrix(runtime, *trip)
     out = runtime.q4_affine_matmul_mapped_batch(bits, m, [job])[0]
     assert out.shape == (m, n)
-    if m < 16:
+    if m <= 16:
         assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 1e-5
     else:  # tensor-core path: bf16 tiles
         assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 2e-3
@@ -176,7 +176,7 @@ def test_full_size_layer_set_by_linearity(runtime, oracle):
             assert oracle.rel_l2(y1[i][r0:r0 + 16], ref) <= 1e-5
 
 
-@pytest.mark.parametrize("m,n,k,offset", [(16, 200, 1024, 0), (17, 129, 128, 0), (64, 11, 128, 0), (100, 300, 640, 2),
+@pytest.mark.parametrize("m,n,k,offset", [(18, 200, 1024, 0), (17, 129, 128, 0), (64, 11, 128, 0), (100, 300, 640, 2),
                                            (256, 3, 128, 1), (300, 513, 1024, 0), (600, 128, 5120, 0), (33, 1000, 17408, 2)])
 def test_tensor_core_gemm_shapes(runtime, oracle, m, n, k, offset):
     """Prefill path (tcgen05): ragged M and N tiles, every tile width the dispatcher picks, misaligned tensors.
