@@ -63,3 +63,33 @@ Q4_HD bool q4_window_wanted(uint32_t t, uint32_t mis, bool has_b) {
 Q4_HD bool q4_fifth_window_wanted(uint32_t mis, bool has_b) { return has_b && mis != 0u; }
 // chunks of a row in which lane t (0..3) of a quad has an affine group: group 2*chunk + (t >> 1) < groups
 Q4_HD uint32_t q4_lane_chunks(uint32_t groups, uint32_t t) { return (groups + 1u - (t >> 1)) >> 1; }
+
+// Short-batch kernel: the K range (cpt chunks of 128 inputs, a multiple of four) is cut into `parts` runs that begin at
+// multiples of four chunks (parameters travel in 16-byte pieces of eight groups). First chunk of `part`; part may
+// equal parts (one past the last chunk).
+Q4_HD uint32_t q4_rows_part_begin(uint32_t cpt, uint32_t parts, uint32_t part) { return ((cpt / 4u) * part / parts) * 4u; }
+
+// How many parts to cut K into for `tiles` 16-row tiles on `sm_count` SMs of 16 warps when a block can hold at most
+// `cap` chunks of activation digits; 0 when no split fits. *part_chunks: chunks of the longest part.
+// Cost of a split in chunk times: every warp walks `rounds` tiles of the longest run, a tile costs about ten more
+// (pipeline ramp, partial sums, the last part's addition), and SMs without a block count against it.
+Q4_HD uint32_t q4_rows_plan(uint32_t cpt, uint32_t tiles, uint32_t sm_count, uint32_t cap, uint32_t *part_chunks) {
+    if (cpt == 0 || cpt % 4u != 0 || tiles == 0 || sm_count == 0) return 0;
+    const uint32_t quads = cpt / 4u;
+    uint32_t best = 0;
+    double best_cost = 0.0;
+    for (uint32_t parts = 1; parts <= quads && parts <= sm_count && parts <= 32u; ++parts) {
+        const uint32_t bpp = sm_count / parts, warps = bpp * 16u;
+        const uint32_t run = ((quads + parts - 1) / parts) * 4u;
+        if (run > cap) continue;
+        const uint32_t rounds = (tiles + warps - 1) / warps;
+        const double cost = (double)rounds * (10.0 + run) * sm_count / (double)(bpp * parts);
+        if (best == 0 || cost < best_cost * 0.98) {
+            best_cost = cost;
+            best = parts;
+        }
+    }
+    if (best == 0) return 0;
+    *part_chunks = ((quads + best - 1) / best) * 4u;
+    return best;
+}

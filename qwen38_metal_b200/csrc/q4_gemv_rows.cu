@@ -17,6 +17,7 @@
 // of that part, each with a private ring of eight 1 KB cp.async stages. Partial sums go to scratch; the LAST part to
 // finish a tile (one counter per tile, put back to zero by that warp) adds all parts in part order -- the result does
 // not depend on which part came last -- and stores the tile. No block ever waits for another one.
+#include "q4_decomp.h"
 #include "q4_device.cuh"
 #include "q4_kernels.h"
 
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t part = blockIdx.x % p.parts, gi = blockIdx.x / p.parts, blocks_per_part = gridDim.x / p.parts;
     // parts begin at multiples of four chunks (K % 512 == 0): parameters are copied in 16-byte pieces of eight groups
-    const uint32_t c_lo = ((p.cpt / 4u) * part / p.parts) * 4u, c_hi = ((p.cpt / 4u) * (part + 1u) / p.parts) * 4u, nch = c_hi - c_lo;
+    const uint32_t c_lo = q4_rows_part_begin(p.cpt, p.parts, part), c_hi = q4_rows_part_begin(p.cpt, p.parts, part + 1u), nch = c_hi - c_lo;
     uint8_t *xdig = smem + kRowsWarps * kRowsRingBytes;
     float *xsum = reinterpret_cast<float *>(xdig + (size_t)p.part_chunks * rows_chunk_bytes(MP));
     uint32_t *amax_s = reinterpret_cast<uint32_t *>(xsum + (size_t)p.part_chunks * 2u * MP);
@@ -332,34 +333,12 @@ static uint32_t rows_part_capacity(uint32_t mp) {
     return chunks >= 4 ? chunks : 0;
 }
 
-// How the K range of a launch is cut: the number of parts (0: the shape is not supported) and the largest part.
-// Constraints: a part's digits fit in shared memory beside the rings; preference: the split that keeps the most warps
-// busy (tiles * parts against whole rounds of the grid's warps), then the fewest parts.
+// How the K range of a launch is cut: the number of parts (0: the shape is not supported) and the longest part.
 extern "C" uint32_t q4k_rows_plan(uint32_t m, uint32_t k, uint32_t tiles, uint32_t sm_count, uint32_t *part_chunks) {
     if (m < 1 || m > 16 || k == 0 || k % 512u != 0 || tiles == 0) return 0;
-    const uint32_t mp = m <= 8 ? 8u : 16u, cpt = k / 128u;
-    const uint32_t cap = rows_part_capacity(mp);
+    const uint32_t cap = rows_part_capacity(m <= 8 ? 8u : 16u);
     if (cap == 0) return 0;
-    // cost of a split in chunk times: every warp walks `rounds` tiles of ceil(cpt / parts) chunks, and a tile costs
-    // about ten more (pipeline ramp, partial sums, the last part's addition); SMs without a block count against it
-    uint32_t best = 0;
-    double best_cost = 0.0;
-    const uint32_t quads = cpt / 4u;  // parts are whole runs of four chunks
-    for (uint32_t parts = 1; parts <= quads && parts <= sm_count && parts <= 32u; ++parts) {
-        const uint32_t bpp = sm_count / parts, warps = bpp * q4::kRowsWarps;
-        if (bpp == 0) break;
-        const uint32_t run = ((quads + parts - 1) / parts) * 4u;
-        if (run > cap) continue;
-        const uint32_t rounds = (tiles + warps - 1) / warps;
-        const double cost = (double)rounds * (10.0 + run) * sm_count / (double)(bpp * parts);
-        if (best == 0 || cost < best_cost * 0.98) {
-            best_cost = cost;
-            best = parts;
-        }
-    }
-    if (best == 0) return 0;
-    *part_chunks = ((quads + best - 1) / best) * 4u;
-    return best;
+    return q4_rows_plan(k / 128u, tiles, sm_count, cap, part_chunks);
 }
 
 extern "C" cudaError_t q4k_rows(const q4::RowsParams *params, uint32_t sm_count, cudaStream_t stream) {
