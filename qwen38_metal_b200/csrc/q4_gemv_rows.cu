@@ -71,13 +71,20 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     const uint32_t copy_off = 16u * (cr * 4u + (cq ^ (2u * ((cr >> 1) & 1u))));
     const uint64_t row_bytes = (uint64_t)p.k >> 1;
     const uint8_t *wa = nullptr, *wb = nullptr, *pw = nullptr;
+    // chunks are requested in order: wa, wb and pw walk along with the next chunk to request
     auto issue_chunk = [&](uint32_t c) {  // chunk c of the part (absolute index), into its ring stage
-        const uint32_t stage = ring + ((c - c_lo) % kRowsStages) * kRowsStageBytes;
+        const uint32_t rel = c - c_lo;
+        const uint32_t stage = ring + (rel % kRowsStages) * kRowsStageBytes;
         const bool pred = c < c_hi;
-        cp_async_16_pred(stage + copy_off, wa + (size_t)c * 64u, pred);
-        cp_async_16_pred(stage + 512u + copy_off, wb + (size_t)c * 64u, pred);
+        cp_async_16_pred(stage + copy_off, wa, pred);
+        cp_async_16_pred(stage + 512u + copy_off, wb, pred);
         // every fourth chunk: lane l copies the scales (l < 16) or biases of row l & 15 for the next eight groups
-        if (((c - c_lo) & 3u) == 0) cp_async_16_pred(pring + (((c - c_lo) >> 2) % kRowsParamStages) * kRowsParamBytes + lane * 16u, pw + (size_t)c * 4u, pred);
+        if ((rel & 3u) == 0) {
+            cp_async_16_pred(pring + ((rel >> 2) % kRowsParamStages) * kRowsParamBytes + lane * 16u, pw, pred);
+            pw += 16;
+        }
+        wa += 64;
+        wb += 64;
     };
     const RowsJob *job = nullptr;
     uint32_t row0 = 0;
@@ -87,10 +94,10 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
         job = &p.jobs[ji];
         row0 = (tile - job->tile_begin) * 16u;
         const uint32_t ra = min(row0 + cr, job->n - 1u), rb = min(row0 + 8u + cr, job->n - 1u);  // rows past n: read a valid row
-        wa = job->w + (uint64_t)ra * row_bytes + cq * 16u;
-        wb = job->w + (uint64_t)rb * row_bytes + cq * 16u;
+        wa = job->w + (uint64_t)ra * row_bytes + cq * 16u + (size_t)c_lo * 64u;
+        wb = job->w + (uint64_t)rb * row_bytes + cq * 16u + (size_t)c_lo * 64u;
         const uint32_t rp = min(row0 + (lane & 15u), job->n - 1u);
-        pw = ((lane >> 4) ? job->b : job->s) + ((size_t)rp * p.groups) * 2u;
+        pw = ((lane >> 4) ? job->b : job->s) + ((size_t)rp * p.groups) * 2u + (size_t)c_lo * 4u;
 #pragma unroll
         for (int i = 0; i < kRowsStages - 1; ++i) {
             issue_chunk(c_lo + i);
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
                     // the group's integer dot product q0 + 256 q1 + 65536 q2 (exact; |q0 + 256 q1| < 2^25 is rounded to fp32 once)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float dot = fmaf(small_int_to_float(q[2][i]), 65536.f, __int2float_rn(q[0][i] + (q[1][i] << 8)));
+                        const float dot = fmaf(__int2float_rn(q[2][i]), 65536.f, __int2float_rn(q[0][i] + (q[1][i] << 8)));
                         acc[nb][i] = fmaf(dot, i < 2 ? sa : sb, acc[nb][i]);
                     }
                     const uint2 xv = lds_v2(xs + (uint32_t)(grp * MP + nb * 8) * 4u);  // sums of x' of rows 2 t, 2 t + 1 of this block of 8

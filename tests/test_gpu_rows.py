@@ -77,3 +77,18 @@ def test_unaligned_tensors_take_the_general_kernel(runtime, oracle):
     job = upload_matrix(runtime, *trip, offset=2)
     out = runtime.q4_affine_matmul_mapped_batch(bits, m, [job])[0]
     assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *trip, n)) <= 1e-5
+
+
+@pytest.mark.parametrize("m", [2, 8, 16])
+def test_residual_form(runtime, oracle, m):
+    """out += x W^T (src/metal_runtime.rs matmul_add): the last K part adds to what the caller's buffer holds."""
+    k = 2048
+    trips = [oracle.synth_q4(SEED, 60 + i, n, k) for i, n in enumerate((333, 48))]
+    jobs = [upload_matrix(runtime, *t) for t in trips]
+    bits, xf = x_bf16(oracle, 60 + m, m, k)
+    res = [np.full((m, t[0].shape[0]), -0.25, dtype=np.float32) for t in trips]
+    plain = runtime.q4_affine_matmul_mapped_batch(bits, m, jobs)
+    added = runtime.q4_affine_matmul_add_mapped_batch(bits, m, jobs, res)
+    for out, add, t in zip(plain, added, trips):
+        assert oracle.rel_l2(out, oracle.matmul_factored_f32(xf, *t, t[0].shape[0])) <= 1e-5
+        assert np.allclose(add, out - 0.25, rtol=0, atol=1e-6)
