@@ -412,7 +412,6 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
     }
     if (tr) tr[7] = stack_ns();  // thread 0 has its source values
     block_sum_max<WARPS>(ss, amax, red);
-    if (tr) tr[8] = stack_ns();
     if (P.x_kind == kRebuildRms) {
         const float inv = rsqrtf(ss / (float)k + P.eps);
         // rounding is monotonic, so the largest rounded magnitude is the rounded largest magnitude
@@ -424,7 +423,6 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
             for (int i = 0; i < 8; ++i) v[it][i] = bf16_bits_to_float(float_to_bf16_bits(v[it][i] * inv));
         }
     }
-    if (tr) tr[9] = stack_ns();
     const int e = scale_exponent(amax);
     const float scale = __uint_as_float((uint32_t)(e + 127) << 23);
     if (threadIdx.x == 0) *X.inv = __uint_as_float((uint32_t)(127 - e) << 23);
@@ -435,7 +433,6 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
         emit_block(v[it], scale, b, b >= b_lo && b < b_hi, X);
         if (P.x_bf16_out && b >= o_lo && b < o_hi && b < blocks) *reinterpret_cast<uint4 *>(P.x_bf16_out + (size_t)b * 8) = pack_bf16x8(v[it]);
     }
-    if (tr) tr[10] = stack_ns();
     __syncthreads();
 }
 
@@ -762,7 +759,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
 
         bool stored_to_peers = false;
         uint32_t blocks_done = 0;
-        uint32_t dbg_i = 0;
         uint32_t u = 0, u1 = 0;  // this warp's units of the phase (a phase has fewer than 2^32)
         if (worker < P.workers) {
             const Q4Split split{P.units, P.cpt, P.workers};
@@ -801,10 +797,8 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                     const uint32_t stage0 = ring + half * (4 * kStageBytesAligned) + lane * 16u;
                     const uint32_t other0 = ring + (half ^ 1u) * (4 * kStageBytesAligned) + lane * 16u;
                     const uint32_t pstage = pring + half * 1024u;
-                    if (sp.dbg && ph == sp.dbg_phase && lane == 0 && dbg_i < 30) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 2 * dbg_i] = stack_ns();
                     cp_async_wait<1>();  // this half's group has landed; the other half's may be pending
                     __syncwarp();        // parameters (and neighbouring weight windows) were copied by other lanes
-                    if (sp.dbg && ph == sp.dbg_phase && lane == 0 && dbg_i < 30) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 2 * dbg_i++ + 1] = stack_ns();
                     uint4 psa = lds_v4(pstage + g * 16u), psb = lds_v4(pstage + (g + 8u) * 16u);
                     uint4 pba = lds_v4(pstage + 256u + g * 16u), pbb = lds_v4(pstage + 256u + (g + 8u) * 16u);
                     if (sg.mis_p) {
@@ -877,7 +871,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                 // latency. After the last run the order is the other way round: results and arrival first -- other
                 // blocks wait for them -- then the next phase's first weights (pushing 8 KB per warp into a memory
                 // system that every warp floods at the same moment takes a few microseconds).
-                if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 56] = stack_ns();
                 const TileEnd te{sg.job, sg.tile_local, sg.tile_row, sg.c0v, sg.c1v};
                 u += sg.c1v - sg.c0v;
                 more = u < u1;
@@ -887,7 +880,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                     segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
                     segment_prologue(sg, ring, pring, lane);
                 }
-                if (sp.dbg && ph == sp.dbg_phase && lane == 0) sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 57] = stack_ns();
                 // digits back together: a lane's columns are digits (0, 1) of its group for even t, (2, none) for odd t
                 const float w0 = (t & 1u) ? 65536.f : 1.f, w1 = (t & 1u) ? 0.f : 256.f;
                 // ... and the power-of-two scaling of this SM's activation undone (exact) before sums of different SMs meet:
@@ -905,10 +897,6 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                 asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
                 trace_slot()[5] = smid;
             }
-        }
-        if (sp.dbg && ph == sp.dbg_phase && lane == 0) {
-            sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 62] = stack_ns();
-            sp.dbg[((size_t)blockIdx.x * WARPS + warp) * 64 + 63] = dbg_i;
         }
 
         if (P.arrive_kind != kSyncNone) {

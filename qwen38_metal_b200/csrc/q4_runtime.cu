@@ -1725,13 +1725,6 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     sp.best = best_dev;
     sp.peers = (const q4::StackPeers *)peers_dev;
     sp.trace = (unsigned long long *)trace;
-    if (rt->tracing && getenv("Q4B_CHAIN_DBG_PHASE")) {
-        void *dbg = nullptr;
-        if (build.alloc(&dbg, (size_t)grid_warps * 64 * 8, true) == cudaSuccess) {
-            sp.dbg = (unsigned long long *)dbg;
-            sp.dbg_phase = (uint32_t)strtol(getenv("Q4B_CHAIN_DBG_PHASE"), nullptr, 10);
-        }
-    }
     c->rt = rt;
     c->reset_region = reset;
     c->reset_bytes = reset_bytes;
@@ -1801,17 +1794,6 @@ extern "C" int q4b_chain_run(q4b_chain *chain, const void *x_host, uint32_t *tok
     if (int st = finish(rt, s)) return st;
     *token_host = token;
     if (best_host && chain->best) *best_host = best;
-    return Q4B_OK;
-}
-
-// development aid: per-warp stamps around every wait for weights in one phase (Q4B_CHAIN_DBG_PHASE at creation)
-extern "C" int q4b_chain_debug_read(q4b_chain *chain, uint64_t *out, uint64_t capacity_words) {
-    if (!chain || !out || !chain->params.dbg) return fail(Q4B_UNSUPPORTED, "no debug stamps were recorded");
-    DeviceGuard guard(chain->rt->device);
-    const uint64_t words = (uint64_t)chain->params.max_workers * 64;
-    if (capacity_words < words) return fail(Q4B_WRONG_LENGTH, "debug buffer has %llu elements, expected %llu", (unsigned long long)capacity_words, (unsigned long long)words);
-    Q4B_CUDA(cudaDeviceSynchronize(), "device synchronize");
-    Q4B_CUDA(cudaMemcpy(out, chain->params.dbg, words * 8, cudaMemcpyDeviceToHost), "debug download");
     return Q4B_OK;
 }
 

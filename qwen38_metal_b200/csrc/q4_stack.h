@@ -108,8 +108,6 @@ struct StackParams {
     float *best;
     const StackPeers *peers;  // null on one GPU
     unsigned long long *trace;  // optional [blocks][n_phases][8] device-clock stamps
-    unsigned long long *dbg;    // optional [warps of the grid][64]: stamps around every wait for weights in phase dbg_phase
-    uint32_t dbg_phase;
 };
 
 // A program of one phase inside the kernel parameters (q4_stack_inline_kernel).
