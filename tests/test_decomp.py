@@ -143,3 +143,27 @@ def test_short_batch_k_split_prefers_one_round(shim):
     longest = C.c_uint32(0)
     assert shim.shim_rows_plan(136, 320, 148, 24, C.byref(longest)) == 7 and longest.value == 20
     assert shim.shim_rows_plan(40, 2176, 148, 24, C.byref(longest)) == 2 and longest.value == 20
+
+
+def test_signed_digits_from_one_addition():
+    """The kernels' digit trick: for |x| <= 2^22, the bytes of (x + 0x808080) ^ 0x808080 are the signed 8-bit digits
+    d0, d1, d2 with x = d0 + 256 d1 + 65536 d2 (the activation's fixed-point form on the integer tensor-core path)."""
+    import numpy as np
+
+    rng = np.random.default_rng(7)
+    x = np.concatenate([rng.integers(-(1 << 22), (1 << 22) + 1, size=200_000), np.array([0, 1, -1, 127, 128, -128, -129, 32767, 32768, -32768, -32769, (1 << 22), -(1 << 22)])]).astype(np.int64)
+    z = ((x + 0x808080) & 0xFFFFFFFF) ^ 0x808080
+    d = [((z >> (8 * i)) & 0xFF).astype(np.uint8).view(np.int8).astype(np.int64) for i in range(3)]
+    assert np.array_equal(d[0] + 256 * d[1] + 65536 * d[2], x)
+    assert (z >> 24 == 0).all()
+    # a group's integer dot product put together the way the short-batch kernel does it: q0 + (q1 << 8) in int32,
+    # + 65536 q2 in fp32; q_d = sum over 64 inputs of w * d_d with 0 <= w <= 15
+    w = rng.integers(0, 16, size=(2000, 64)).astype(np.int64)
+    xs = rng.integers(-(1 << 22), (1 << 22) + 1, size=(2000, 64)).astype(np.int64)
+    zs = ((xs + 0x808080) & 0xFFFFFFFF) ^ 0x808080
+    q = [(w * ((zs >> (8 * i)) & 0xFF).astype(np.uint8).view(np.int8).astype(np.int64)).sum(axis=1) for i in range(3)]
+    assert (np.abs(q[0] + (q[1] << 8)) < (1 << 31)).all() and (np.abs(q[2]) < (1 << 22)).all()
+    exact = (w * xs).sum(axis=1)
+    assert np.array_equal(q[0] + 256 * q[1] + 65536 * q[2], exact)
+    approx = np.float32(q[2]) * np.float32(65536.0) + (q[0] + (q[1] << 8)).astype(np.float32)
+    assert np.all(np.abs(approx.astype(np.float64) - exact) <= np.abs(exact) * 2.0 ** -22 + 4.0)
