@@ -139,7 +139,10 @@ int q4b_offset_is_aligned(q4b_runtime *rt, uint32_t shard_id, uint64_t byte_offs
 int q4b_matvec_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t k, const q4b_job *jobs,
                      uint32_t n_jobs, float *const *outputs);
 /* q4_affine_matmul_mapped_batch, src/metal_runtime.rs:3683-3792: x is [m][k] row-major;
- * outputs[i] is [m][jobs[i].output_rows] row-major. */
+ * outputs[i] is [m][jobs[i].output_rows] row-major. Which kernel runs (the reference's dispatcher,
+ * src/metal_runtime.rs:24-77, picks by m too): m = 1 the decode kernel; 2 <= m <= 16 the short-batch kernel when
+ * k % 512 == 0 and all tensors are 16-byte aligned, else the general streaming kernel (m < 16); from there on the
+ * tensor-core GEMM, which rounds activations and dequantised weights to bf16. q4b_describe_dispatch names the choice. */
 int q4b_matmul_batch(q4b_runtime *rt, const void *x, int x_dtype, uint64_t m, uint64_t k, const q4b_job *jobs,
                      uint32_t n_jobs, float *const *outputs);
 /* q4_affine_argmax_mapped_batch, src/metal_runtime.rs:3797-3891: tokens[m]; ties -> lowest index. */
