@@ -175,6 +175,17 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
         const uint32_t idx = threadIdx.x + i * T;
         const bool live = idx < padded8;
         const uint32_t mrow = live ? idx / span8 : 0u, b8 = live ? idx - mrow * span8 : 0u;
+        if (mrow >= p.m) {
+            // (uniform per warp: a row's blocks are a multiple of 64) rows past m hold zeros
+            if (live) {
+                const uint32_t chunk = b8 >> 4, grp = (b8 >> 3) & 1u, b = b8 & 7u;
+                uint8_t *dst = xdig + (size_t)chunk * rows_chunk_bytes(MP) + (size_t)grp * 3u * MP * 64u + (size_t)mrow * 64u + 16u * (b >> 1) + 8u * (b & 1u);
+#pragma unroll
+                for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2 *>(dst + (size_t)d * MP * 64u) = make_uint2(0u, 0u);
+                if (b == 0) xsum[(chunk * 2u + grp) * MP + mrow] = 0.f;
+            }
+            continue;
+        }
         float v[8];
         unpack8(raw[i], v);
         const float scale = __uint_as_float((uint32_t)(scale_exponent(amax_s[mrow]) + 127) << 23);
