@@ -69,21 +69,24 @@ Q4_HD uint32_t q4_lane_chunks(uint32_t groups, uint32_t t) { return (groups + 1u
 // equal parts (one past the last chunk).
 Q4_HD uint32_t q4_rows_part_begin(uint32_t cpt, uint32_t parts, uint32_t part) { return ((cpt / 4u) * part / parts) * 4u; }
 
-// How many parts to cut K into for `tiles` 16-row tiles on `sm_count` SMs of 16 warps when a block can hold at most
-// `cap` chunks of activation digits; 0 when no split fits. *part_chunks: chunks of the longest part.
-// Cost of a split in chunk times: every warp walks `rounds` tiles of the longest run, a tile costs about ten more
-// (pipeline ramp, partial sums, the last part's addition), and SMs without a block count against it.
-Q4_HD uint32_t q4_rows_plan(uint32_t cpt, uint32_t tiles, uint32_t sm_count, uint32_t cap, uint32_t *part_chunks) {
-    if (cpt == 0 || cpt % 4u != 0 || tiles == 0 || sm_count == 0) return 0;
-    const uint32_t quads = cpt / 4u;
+// How many parts to cut K into for `tiles` 16-row tiles on `sm_count` SMs of 16 warps, each warp walking `tw` tiles at
+// a time, when a block can hold at most `cap` chunks of activation digits; 0 when no split fits. *part_chunks: chunks
+// of the longest part; *cost_out: the estimate the choice was made by.
+// Cost of a split in chunk times: every warp walks `rounds` items of the longest run, a chunk of two tiles costs 1.75
+// (measured; the activation's fragments are read once for both), an item costs about ten more per tile pair or single
+// tile (pipeline ramp, partial sums, the last part's addition), and SMs without a block count against it.
+Q4_HD uint32_t q4_rows_plan(uint32_t cpt, uint32_t tiles, uint32_t sm_count, uint32_t cap, uint32_t tw, uint32_t *part_chunks, double *cost_out) {
+    if (cpt == 0 || cpt % 4u != 0 || tiles == 0 || sm_count == 0 || tw == 0) return 0;
+    const uint32_t quads = cpt / 4u, items = (tiles + tw - 1u) / tw;
+    const double per_chunk = tw == 1u ? 1.0 : 1.75, per_item = tw == 1u ? 10.0 : 12.0;
     uint32_t best = 0;
     double best_cost = 0.0;
     for (uint32_t parts = 1; parts <= quads && parts <= sm_count && parts <= 32u; ++parts) {
         const uint32_t bpp = sm_count / parts, warps = bpp * 16u;
         const uint32_t run = ((quads + parts - 1) / parts) * 4u;
         if (run > cap) continue;
-        const uint32_t rounds = (tiles + warps - 1) / warps;
-        const double cost = (double)rounds * (10.0 + run) * sm_count / (double)(bpp * parts);
+        const uint32_t rounds = (items + warps - 1) / warps;
+        const double cost = (double)rounds * (per_item + run * per_chunk) * sm_count / (double)(bpp * parts);
         if (best == 0 || cost < best_cost * 0.98) {
             best_cost = cost;
             best = parts;
@@ -91,5 +94,6 @@ Q4_HD uint32_t q4_rows_plan(uint32_t cpt, uint32_t tiles, uint32_t sm_count, uin
     }
     if (best == 0) return 0;
     *part_chunks = ((quads + best - 1) / best) * 4u;
+    if (cost_out) *cost_out = best_cost;
     return best;
 }

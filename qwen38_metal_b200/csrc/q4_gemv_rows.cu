@@ -24,20 +24,24 @@
 namespace q4 {
 
 constexpr int kRowsWarps = 16;
-constexpr int kRowsStages = 8;
-constexpr int kRowsStageBytes = 1024;  // 16 weight rows x 64 packed bytes
-constexpr int kRowsParamStages = 3;    // scales and biases travel per four chunks (16 rows x 2 arrays x 16 bytes), up to 8 chunks ahead
-constexpr int kRowsParamBytes = 512;
-constexpr int kRowsRingBytes = kRowsStages * kRowsStageBytes + kRowsParamStages * kRowsParamBytes;
+constexpr int kRowsStageBytes = 1024;  // one chunk of one tile: 16 weight rows x 64 packed bytes
 constexpr int kRowsPerThread = 8;      // blocks of 8 inputs a thread converts at most (bounds a part: rows x chunks <= 256)
+
+// A warp walks TW tiles at a time (1 or 2): with two, the B fragments (activation digits) are read from shared memory
+// once for 32 weight rows. The ring of a warp is 8 KB either way: 8 stages of one chunk, or 4 stages of a chunk of both
+// tiles. Scales and biases travel per four chunks (16 rows x 2 arrays x 16 bytes per tile): three such stages cover
+// the 7 chunks a one-tile warp is ahead, two the 3 chunks of a two-tile warp.
+__host__ __device__ constexpr uint32_t rows_stages(uint32_t tw) { return 8u / tw; }
+__host__ __device__ constexpr uint32_t rows_param_stages(uint32_t tw) { return tw == 1u ? 3u : 2u; }
+__host__ __device__ constexpr uint32_t rows_ring_bytes(uint32_t tw) { return 8u * kRowsStageBytes + rows_param_stages(tw) * 512u * tw; }
 
 // Shared memory of one chunk's digits: [group 2][digit 3][activation row MP][64 bytes]. The 64 bytes of a (group, digit,
 // row) hold the 64 inputs of the group in the order lane t of a quad wants them as B registers of the group's two MMAs:
 // byte 16 t + 8 j + 4 odd + i  <->  input 16 t + 8 j + 2 i + odd   (t: quad lane, j: MMA of the group, i: byte).
 __host__ __device__ constexpr uint32_t rows_chunk_bytes(uint32_t mp) { return 2u * 3u * mp * 64u; }
 
-__host__ __device__ inline size_t rows_smem_bytes(uint32_t mp, uint32_t part_chunks) {
-    return (size_t)kRowsWarps * kRowsRingBytes + (size_t)part_chunks * rows_chunk_bytes(mp) +
+__host__ __device__ inline size_t rows_smem_bytes(uint32_t mp, uint32_t part_chunks, uint32_t tw) {
+    return (size_t)kRowsWarps * rows_ring_bytes(tw) + (size_t)part_chunks * rows_chunk_bytes(mp) +
            (size_t)part_chunks * 2u * mp * 4u + 2u * mp * 4u + 64u;
 }
 
@@ -47,59 +51,84 @@ __device__ __forceinline__ unsigned long long rows_ns() {
     return t;
 }
 
-template <int NB>
+template <int NB, int TW>
 __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __grid_constant__ RowsParams p) {
     constexpr uint32_t MP = 8 * NB;
     constexpr uint32_t T = kRowsWarps * 32;
+    constexpr uint32_t S = rows_stages(TW), PS = rows_param_stages(TW);
+    constexpr uint32_t kStage = kRowsStageBytes * TW, kParamStage = 512u * TW;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t part = blockIdx.x % p.parts, gi = blockIdx.x / p.parts, blocks_per_part = gridDim.x / p.parts;
     // parts begin at multiples of four chunks (K % 512 == 0): parameters are copied in 16-byte pieces of eight groups
     const uint32_t c_lo = q4_rows_part_begin(p.cpt, p.parts, part), c_hi = q4_rows_part_begin(p.cpt, p.parts, part + 1u), nch = c_hi - c_lo;
-    uint8_t *xdig = smem + kRowsWarps * kRowsRingBytes;
+    uint8_t *xdig = smem + kRowsWarps * rows_ring_bytes(TW);
     float *xsum = reinterpret_cast<float *>(xdig + (size_t)p.part_chunks * rows_chunk_bytes(MP));
     uint32_t *amax_s = reinterpret_cast<uint32_t *>(xsum + (size_t)p.part_chunks * 2u * MP);
     float *inv_s = reinterpret_cast<float *>(amax_s + MP);
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * kRowsRingBytes;
-    const uint32_t pring = ring + kRowsStages * kRowsStageBytes;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * rows_ring_bytes(TW);
+    const uint32_t pring = ring + S * kStage;
 
-    // ---- a tile's weights: lane l copies 16 bytes of row l >> 2 (and of the row eight further down) per chunk ----
-    // The four 16-byte quarters of a row are stored with quarter q at q ^ (2 * bit 1 of the row), so that the 8-byte
-    // reads below (lane (g, t): bytes 8 t.. of a group) touch every bank once per half-warp.
+    // ---- an item's weights (TW tiles): lane l copies 16 bytes of row l >> 2 (and of the row eight further down) per
+    // chunk and tile. The four 16-byte quarters of a row are stored with quarter q at q ^ (2 * bit 1 of the row), so
+    // that the 8-byte reads below (lane (g, t): bytes 8 t.. of a group) touch every bank once per half-warp.
     const uint32_t cr = lane >> 2, cq = lane & 3u;
     const uint32_t copy_off = 16u * (cr * 4u + (cq ^ (2u * ((cr >> 1) & 1u))));
     const uint64_t row_bytes = (uint64_t)p.k >> 1;
-    const uint8_t *wa = nullptr, *wb = nullptr, *pw = nullptr;
+    const uint8_t *wa[TW], *wb[TW], *pw[TW];
+    const RowsJob *job[TW];
+    uint32_t row0[TW];
+    bool tile_live[TW];
+#pragma unroll
+    for (int w = 0; w < TW; ++w) {
+        wa[w] = wb[w] = pw[w] = nullptr;
+        job[w] = nullptr;
+        row0[w] = 0;
+        tile_live[w] = false;
+    }
     // chunks are requested in order: wa, wb and pw walk along with the next chunk to request
     auto issue_chunk = [&](uint32_t c) {  // chunk c of the part (absolute index), into its ring stage
         const uint32_t rel = c - c_lo;
-        const uint32_t stage = ring + (rel % kRowsStages) * kRowsStageBytes;
+        const uint32_t stage = ring + (rel % S) * kStage;
         const bool pred = c < c_hi;
-        cp_async_16_pred(stage + copy_off, wa, pred);
-        cp_async_16_pred(stage + 512u + copy_off, wb, pred);
+#pragma unroll
+        for (int w = 0; w < TW; ++w) {
+            cp_async_16_pred(stage + w * kRowsStageBytes + copy_off, wa[w], pred);
+            cp_async_16_pred(stage + w * kRowsStageBytes + 512u + copy_off, wb[w], pred);
+            wa[w] += 64;
+            wb[w] += 64;
+        }
         // every fourth chunk: lane l copies the scales (l < 16) or biases of row l & 15 for the next eight groups
         if ((rel & 3u) == 0) {
-            cp_async_16_pred(pring + ((rel >> 2) % kRowsParamStages) * kRowsParamBytes + lane * 16u, pw, pred);
-            pw += 16;
-        }
-        wa += 64;
-        wb += 64;
-    };
-    const RowsJob *job = nullptr;
-    uint32_t row0 = 0;
-    auto open_tile = [&](uint32_t tile) {
-        uint32_t ji = 0;
-        while (ji + 1 < p.n_jobs && tile >= p.jobs[ji + 1].tile_begin) ++ji;
-        job = &p.jobs[ji];
-        row0 = (tile - job->tile_begin) * 16u;
-        const uint32_t ra = min(row0 + cr, job->n - 1u), rb = min(row0 + 8u + cr, job->n - 1u);  // rows past n: read a valid row
-        wa = job->w + (uint64_t)ra * row_bytes + cq * 16u + (size_t)c_lo * 64u;
-        wb = job->w + (uint64_t)rb * row_bytes + cq * 16u + (size_t)c_lo * 64u;
-        const uint32_t rp = min(row0 + (lane & 15u), job->n - 1u);
-        pw = ((lane >> 4) ? job->b : job->s) + ((size_t)rp * p.groups) * 2u + (size_t)c_lo * 4u;
 #pragma unroll
-        for (int i = 0; i < kRowsStages - 1; ++i) {
+            for (int w = 0; w < TW; ++w) {
+                cp_async_16_pred(pring + ((rel >> 2) % PS) * kParamStage + w * 512u + lane * 16u, pw[w], pred);
+                pw[w] += 16;
+            }
+        }
+    };
+    // item i of a part = tiles TW * i .. TW * i + TW - 1 (a tile past the last one repeats the last: computed, never stored)
+    const uint32_t items = (p.tiles + TW - 1) / TW;
+    auto open_item = [&](uint32_t it) {
+#pragma unroll
+        for (int w = 0; w < TW; ++w) {
+            const uint32_t want = it * TW + w;
+            tile_live[w] = want < p.tiles;
+            const uint32_t tile = tile_live[w] ? want : p.tiles - 1u;
+            uint32_t ji = 0;
+            while (ji + 1 < p.n_jobs && tile >= p.jobs[ji + 1].tile_begin) ++ji;
+            job[w] = &p.jobs[ji];
+            row0[w] = (tile - job[w]->tile_begin) * 16u;
+            const uint32_t n = job[w]->n;
+            const uint32_t ra = min(row0[w] + cr, n - 1u), rb = min(row0[w] + 8u + cr, n - 1u);  // rows past n: read a valid row
+            wa[w] = job[w]->w + (uint64_t)ra * row_bytes + cq * 16u + (size_t)c_lo * 64u;
+            wb[w] = job[w]->w + (uint64_t)rb * row_bytes + cq * 16u + (size_t)c_lo * 64u;
+            const uint32_t rp = min(row0[w] + (lane & 15u), n - 1u);
+            pw[w] = ((lane >> 4) ? job[w]->b : job[w]->s) + ((size_t)rp * p.groups) * 2u + (size_t)c_lo * 4u;
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < S - 1; ++i) {
             issue_chunk(c_lo + i);
             cp_async_commit();
         }
@@ -107,7 +136,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     unsigned long long *tr = (p.trace && lane == 0) ? p.trace + ((size_t)blockIdx.x * kRowsWarps + warp) * 4 : nullptr;
     if (tr) tr[0] = rows_ns();
     bool first_tile = true;
-    uint32_t tile = gi * kRowsWarps + warp;
+    uint32_t item = gi * kRowsWarps + warp;
 
     // ---- the part's digits for every row ----
     const uint32_t span8 = nch * 16u;  // blocks of 8 inputs per row in this part
@@ -136,7 +165,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     // the first weights travel while the block converts the activation -- requested once every warp of the block has
     // its activation loads out: those would otherwise queue behind 7 KB of copies per warp
     __syncthreads();
-    if (tile < p.tiles) open_tile(tile);
+    if (item < items) open_item(item);
     auto unpack8 = [&](const uint4 (&r)[2], float (&v)[8]) {
         if (p.x_is_f32) {
             v[0] = __uint_as_float(r[0].x); v[1] = __uint_as_float(r[0].y); v[2] = __uint_as_float(r[0].z); v[3] = __uint_as_float(r[0].w);
@@ -225,53 +254,66 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     const uint32_t rd_swz = 2u * ((g >> 1) & 1u);
     const uint32_t rd0 = 16u * (g * 4u + ((0u + (t >> 1)) ^ rd_swz)) + 8u * (t & 1u);
     const uint32_t rd1 = 16u * (g * 4u + ((2u + (t >> 1)) ^ rd_swz)) + 8u * (t & 1u);
-    for (; tile < p.tiles; tile += blocks_per_part * kRowsWarps) {
-        float acc[NB][4];
+    for (; item < items; item += blocks_per_part * kRowsWarps) {
+        float acc[TW][NB][4];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
+        for (int w = 0; w < TW; ++w)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) acc[w][nb][0] = acc[w][nb][1] = acc[w][nb][2] = acc[w][nb][3] = 0.f;
         for (uint32_t c = c_lo; c < c_hi; ++c) {
-            issue_chunk(c + kRowsStages - 1);
+            issue_chunk(c + S - 1);
             cp_async_commit();
-            cp_async_wait<kRowsStages - 1>();
+            cp_async_wait<S - 1>();
             __syncwarp();
-            const uint32_t stage = ring + ((c - c_lo) % kRowsStages) * kRowsStageBytes;
-            const uint32_t pst = pring + (((c - c_lo) >> 2) % kRowsParamStages) * kRowsParamBytes + ((c - c_lo) & 3u) * 4u;
-            const uint32_t sa_c = lds_u32(pst + g * 16u), sb_c = lds_u32(pst + (g + 8u) * 16u);
-            const uint32_t ba_c = lds_u32(pst + 256u + g * 16u), bb_c = lds_u32(pst + 256u + (g + 8u) * 16u);
+            const uint32_t stage = ring + ((c - c_lo) % S) * kStage;
+            const uint32_t pst = pring + (((c - c_lo) >> 2) % PS) * kParamStage + ((c - c_lo) & 3u) * 4u;
             const uint32_t xc = xdig_addr + (c - c_lo) * rows_chunk_bytes(MP);
             const uint32_t xs = xsum_addr + (c - c_lo) * (2u * MP * 4u);
 #pragma unroll
             for (int grp = 0; grp < 2; ++grp) {
-                const uint2 wA = lds_v2(stage + (grp ? rd1 : rd0)), wB = lds_v2(stage + 512u + (grp ? rd1 : rd0));
-                const uint32_t m4 = 0x0f0f0f0fu;
-                const uint32_t a_lo0 = wA.x & m4, a_hi0 = (wA.x >> 4) & m4, a_lo1 = wA.y & m4, a_hi1 = (wA.y >> 4) & m4;
-                const uint32_t b_lo0 = wB.x & m4, b_hi0 = (wB.x >> 4) & m4, b_lo1 = wB.y & m4, b_hi1 = (wB.y >> 4) & m4;
-                const float sa = bf16_bits_to_float(grp ? (sa_c >> 16) : (sa_c & 0xffffu));
-                const float sb = bf16_bits_to_float(grp ? (sb_c >> 16) : (sb_c & 0xffffu));
-                const float ba = bf16_bits_to_float(grp ? (ba_c >> 16) : (ba_c & 0xffffu));
-                const float bb = bf16_bits_to_float(grp ? (bb_c >> 16) : (bb_c & 0xffffu));
+                // the activation's digits of this group: read once, used by every tile of the item
+                uint4 xf[NB][3];
+                uint2 xv[NB];
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
-                    int q[3][4];
 #pragma unroll
-                    for (int d = 0; d < 3; ++d) {
-                        const uint4 xf = lds_v4(xc + (uint32_t)((grp * 3 + d) * MP + nb * 8) * 64u);
-                        q[d][0] = q[d][1] = q[d][2] = q[d][3] = 0;
-                        mma_u8s8_16832(q[d], a_lo0, b_lo0, a_hi0, b_hi0, xf.x, xf.y);
-                        mma_u8s8_16832(q[d], a_lo1, b_lo1, a_hi1, b_hi1, xf.z, xf.w);
-                    }
-                    // the group's integer dot product q0 + 256 q1 + 65536 q2 (exact; |q0 + 256 q1| < 2^25 is rounded to fp32 once)
+                    for (int d = 0; d < 3; ++d) xf[nb][d] = lds_v4(xc + (uint32_t)((grp * 3 + d) * MP + nb * 8) * 64u);
+                    xv[nb] = lds_v2(xs + (uint32_t)(grp * MP + nb * 8) * 4u);  // sums of x' of rows 2 t, 2 t + 1 of this block of 8
+                }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float dot = fmaf(__int2float_rn(q[2][i]), 65536.f, __int2float_rn(q[0][i] + (q[1][i] << 8)));
-                        acc[nb][i] = fmaf(dot, i < 2 ? sa : sb, acc[nb][i]);
+                for (int w = 0; w < TW; ++w) {
+                    const uint32_t wst = stage + w * kRowsStageBytes, pwst = pst + w * 512u;
+                    const uint2 wA = lds_v2(wst + (grp ? rd1 : rd0)), wB = lds_v2(wst + 512u + (grp ? rd1 : rd0));
+                    const uint32_t m4 = 0x0f0f0f0fu;
+                    const uint32_t a_lo0 = wA.x & m4, a_hi0 = (wA.x >> 4) & m4, a_lo1 = wA.y & m4, a_hi1 = (wA.y >> 4) & m4;
+                    const uint32_t b_lo0 = wB.x & m4, b_hi0 = (wB.x >> 4) & m4, b_lo1 = wB.y & m4, b_hi1 = (wB.y >> 4) & m4;
+                    const uint32_t sa_c = lds_u32(pwst + g * 16u), sb_c = lds_u32(pwst + (g + 8u) * 16u);
+                    const uint32_t ba_c = lds_u32(pwst + 256u + g * 16u), bb_c = lds_u32(pwst + 256u + (g + 8u) * 16u);
+                    const float sa = bf16_bits_to_float(grp ? (sa_c >> 16) : (sa_c & 0xffffu));
+                    const float sb = bf16_bits_to_float(grp ? (sb_c >> 16) : (sb_c & 0xffffu));
+                    const float ba = bf16_bits_to_float(grp ? (ba_c >> 16) : (ba_c & 0xffffu));
+                    const float bb = bf16_bits_to_float(grp ? (bb_c >> 16) : (bb_c & 0xffffu));
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        int q[3][4];
+#pragma unroll
+                        for (int d = 0; d < 3; ++d) {
+                            q[d][0] = q[d][1] = q[d][2] = q[d][3] = 0;
+                            mma_u8s8_16832(q[d], a_lo0, b_lo0, a_hi0, b_hi0, xf[nb][d].x, xf[nb][d].y);
+                            mma_u8s8_16832(q[d], a_lo1, b_lo1, a_hi1, b_hi1, xf[nb][d].z, xf[nb][d].w);
+                        }
+                        // the group's integer dot product q0 + 256 q1 + 65536 q2 (exact; |q0 + 256 q1| < 2^25 is rounded to fp32 once)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float dot = fmaf(__int2float_rn(q[2][i]), 65536.f, __int2float_rn(q[0][i] + (q[1][i] << 8)));
+                            acc[w][nb][i] = fmaf(dot, i < 2 ? sa : sb, acc[w][nb][i]);
+                        }
+                        const float x0 = __uint_as_float(xv[nb].x), x1 = __uint_as_float(xv[nb].y);
+                        acc[w][nb][0] = fmaf(x0, ba, acc[w][nb][0]);
+                        acc[w][nb][1] = fmaf(x1, ba, acc[w][nb][1]);
+                        acc[w][nb][2] = fmaf(x0, bb, acc[w][nb][2]);
+                        acc[w][nb][3] = fmaf(x1, bb, acc[w][nb][3]);
                     }
-                    const uint2 xv = lds_v2(xs + (uint32_t)(grp * MP + nb * 8) * 4u);  // sums of x' of rows 2 t, 2 t + 1 of this block of 8
-                    const float x0 = __uint_as_float(xv.x), x1 = __uint_as_float(xv.y);
-                    acc[nb][0] = fmaf(x0, ba, acc[nb][0]);
-                    acc[nb][1] = fmaf(x1, ba, acc[nb][1]);
-                    acc[nb][2] = fmaf(x0, bb, acc[nb][2]);
-                    acc[nb][3] = fmaf(x1, bb, acc[nb][3]);
                 }
             }
             __syncwarp();  // every lane is done with the stage before the next iteration refills the one before it
@@ -280,57 +322,67 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
         __syncwarp();
         if (tr && first_tile) tr[2] = rows_ns();
         first_tile = false;
-        // the next tile's first weights travel while this one is finished
-        const RowsJob *done_job = job;
-        const uint32_t done_row0 = row0, done_tile = tile;
-        if (tile + blocks_per_part * kRowsWarps < p.tiles) open_tile(tile + blocks_per_part * kRowsWarps);
-
-        // ---- digits together, the part's scaling undone; then the tile's parts ----
-        float val[NB][4];
+        // the next item's first weights travel while this one is finished
+        const RowsJob *done_job[TW];
+        uint32_t done_row0[TW];
+        bool done_live[TW];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float inv = inv_s[nb * 8 + 2 * t + (i & 1)];
-                val[nb][i] = acc[nb][i] * inv;
-            }
-        const uint32_t rows_total = p.tiles * 16u;
-        bool last = true;
-        if (p.parts > 1u) {
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t mcol = nb * 8 + 2 * t + (i & 1), r = g + 8u * (i >> 1);
-                    p.partials[((size_t)part * MP + mcol) * rows_total + (size_t)done_tile * 16u + r] = val[nb][i];
-                }
-            __threadfence();
-            __syncwarp();
-            unsigned int before = 0;
-            if (lane == 0) before = atomicAdd(p.counters + done_tile, 1u);
-            before = __shfl_sync(0xffffffffu, before, 0);
-            last = before + 1u == p.parts;
-            if (last) {
-                __threadfence();
-                if (lane == 0) p.counters[done_tile] = 0;  // ready for the next launch
-            }
+        for (int w = 0; w < TW; ++w) {
+            done_job[w] = job[w];
+            done_row0[w] = row0[w];
+            done_live[w] = tile_live[w];
         }
-        if (last) {
+        const uint32_t done_item = item;
+        if (item + blocks_per_part * kRowsWarps < items) open_item(item + blocks_per_part * kRowsWarps);
+
+        // ---- the part's scaling undone; then the tile's parts ----
+        const uint32_t rows_total = p.tiles * 16u;
+#pragma unroll
+        for (int w = 0; w < TW; ++w) {
+            if (!done_live[w]) continue;  // (uniform)
+            const uint32_t done_tile = done_item * TW + w;
+            float val[NB][4];
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t mcol = nb * 8 + 2 * t + (i & 1), r = g + 8u * (i >> 1);
-                    if (mcol >= p.m || done_row0 + r >= done_job->n) continue;
-                    float sum = val[nb][i];
-                    if (p.parts > 1u) {
-                        sum = 0.f;
-                        for (uint32_t q = 0; q < p.parts; ++q)  // part order, whoever came last
-                            sum += __ldcg(p.partials + ((size_t)q * MP + mcol) * rows_total + (size_t)done_tile * 16u + r);
+                for (int i = 0; i < 4; ++i) val[nb][i] = acc[w][nb][i] * inv_s[nb * 8 + 2 * t + (i & 1)];
+            bool last = true;
+            if (p.parts > 1u) {
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t mcol = nb * 8 + 2 * t + (i & 1), r = g + 8u * (i >> 1);
+                        p.partials[((size_t)part * MP + mcol) * rows_total + (size_t)done_tile * 16u + r] = val[nb][i];
                     }
-                    float *dst = done_job->out + (size_t)mcol * done_job->out_stride + done_row0 + r;
-                    *dst = p.accumulate ? *dst + sum : sum;
+                __threadfence();
+                __syncwarp();
+                unsigned int before = 0;
+                if (lane == 0) before = atomicAdd(p.counters + done_tile, 1u);
+                before = __shfl_sync(0xffffffffu, before, 0);
+                last = before + 1u == p.parts;
+                if (last) {
+                    __threadfence();
+                    if (lane == 0) p.counters[done_tile] = 0;  // ready for the next launch
                 }
+            }
+            if (last) {
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t mcol = nb * 8 + 2 * t + (i & 1), r = g + 8u * (i >> 1);
+                        if (mcol >= p.m || done_row0[w] + r >= done_job[w]->n) continue;
+                        float sum = val[nb][i];
+                        if (p.parts > 1u) {
+                            sum = 0.f;
+                            for (uint32_t q = 0; q < p.parts; ++q)  // part order, whoever came last
+                                sum += __ldcg(p.partials + ((size_t)q * MP + mcol) * rows_total + (size_t)done_tile * 16u + r);
+                        }
+                        float *dst = done_job[w]->out + (size_t)mcol * done_job[w]->out_stride + done_row0[w] + r;
+                        *dst = p.accumulate ? *dst + sum : sum;
+                    }
+            }
         }
     }
     cp_async_wait<0>();
@@ -339,41 +391,57 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
 
 }  // namespace q4
 
-// Largest part (in chunks) a block can hold for `mp` padded activation rows, 0 if not even four chunks fit.
-static uint32_t rows_part_capacity(uint32_t mp) {
+// Largest part (in chunks) a block can hold for `mp` padded activation rows and `tw` tiles per warp, 0 if not even
+// four chunks fit.
+static uint32_t rows_part_capacity(uint32_t mp, uint32_t tw) {
     int dev = 0, optin = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     uint32_t chunks = 0;
-    while (q4::rows_smem_bytes(mp, chunks + 1) <= (size_t)optin && (chunks + 1) * mp <= 256u) ++chunks;
+    while (q4::rows_smem_bytes(mp, chunks + 1, tw) <= (size_t)optin && (chunks + 1) * mp <= 256u) ++chunks;
     return chunks >= 4 ? chunks : 0;
 }
 
-// How the K range of a launch is cut: the number of parts (0: the shape is not supported) and the longest part.
-extern "C" uint32_t q4k_rows_plan(uint32_t m, uint32_t k, uint32_t tiles, uint32_t sm_count, uint32_t *part_chunks) {
+// How the K range of a launch is cut: the number of parts (0: the shape is not supported), the longest part, and how
+// many tiles a warp walks at a time (two share the activation's fragments; up to 8 rows only).
+extern "C" uint32_t q4k_rows_plan(uint32_t m, uint32_t k, uint32_t tiles, uint32_t sm_count, uint32_t *part_chunks, uint32_t *tiles_per_warp) {
     if (m < 1 || m > 16 || k == 0 || k % 512u != 0 || tiles == 0) return 0;
-    const uint32_t cap = rows_part_capacity(m <= 8 ? 8u : 16u);
-    if (cap == 0) return 0;
-    return q4_rows_plan(k / 128u, tiles, sm_count, cap, part_chunks);
+    const uint32_t mp = m <= 8 ? 8u : 16u;
+    uint32_t best = 0;
+    double best_cost = 0.0;
+    for (uint32_t tw = 1; tw <= (mp == 8 ? 2u : 1u); ++tw) {
+        const uint32_t cap = rows_part_capacity(mp, tw);
+        if (cap == 0) continue;
+        uint32_t chunks = 0;
+        double cost = 0.0;
+        const uint32_t parts = q4_rows_plan(k / 128u, tiles, sm_count, cap, tw, &chunks, &cost);
+        if (parts && (best == 0 || cost < best_cost * 0.98)) {
+            best = parts;
+            best_cost = cost;
+            *part_chunks = chunks;
+            *tiles_per_warp = tw;
+        }
+    }
+    return best;
+}
+
+template <int NB, int TW>
+static cudaError_t rows_launch(const q4::RowsParams &p, uint32_t grid, size_t smem, cudaStream_t stream) {
+    const cudaError_t e = cudaFuncSetAttribute(q4::q4_rows_kernel<NB, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    q4::q4_rows_kernel<NB, TW><<<grid, q4::kRowsWarps * 32, smem, stream>>>(p);
+    return cudaGetLastError();
 }
 
 extern "C" cudaError_t q4k_rows(const q4::RowsParams *params, uint32_t sm_count, cudaStream_t stream) {
-    q4::RowsParams p = *params;
+    const q4::RowsParams &p = *params;
     const uint32_t mp = p.m <= 8 ? 8u : 16u;
-    const size_t smem = q4::rows_smem_bytes(mp, p.part_chunks);
+    if (p.tiles_per_warp != 1u && !(p.tiles_per_warp == 2u && mp == 8u)) return cudaErrorInvalidValue;
+    const size_t smem = q4::rows_smem_bytes(mp, p.part_chunks, p.tiles_per_warp);
     const uint32_t grid = (sm_count / p.parts) * p.parts;
     if (grid == 0) return cudaErrorInvalidValue;
-    cudaError_t e;
-    if (mp == 8) {
-        e = cudaFuncSetAttribute(q4::q4_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        q4::q4_rows_kernel<1><<<grid, q4::kRowsWarps * 32, smem, stream>>>(p);
-    } else {
-        e = cudaFuncSetAttribute(q4::q4_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        q4::q4_rows_kernel<2><<<grid, q4::kRowsWarps * 32, smem, stream>>>(p);
-    }
-    return cudaGetLastError();
+    if (mp == 16) return rows_launch<2, 1>(p, grid, smem, stream);
+    return p.tiles_per_warp == 2u ? rows_launch<1, 2>(p, grid, smem, stream) : rows_launch<1, 1>(p, grid, smem, stream);
 }

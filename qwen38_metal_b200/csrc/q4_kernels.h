@@ -73,6 +73,7 @@ struct RowsParams {
     uint32_t k, groups, cpt;  // inputs, k / 64, k / 128
     uint32_t parts;        // runs the K range is cut into (q4k_rows_plan)
     uint32_t part_chunks;  // chunks of the longest run
+    uint32_t tiles_per_warp;  // 1, or 2 (up to 8 rows): two tiles share the activation's fragments
     uint32_t tiles;        // 16-row tiles of all jobs
     uint32_t accumulate;
     float *partials;       // [parts][8 or 16][tiles * 16] fp32, used when parts > 1
@@ -88,7 +89,7 @@ cudaError_t q4k_prepare_x(const void *x, int x_is_f32, uint32_t m_rows, uint32_t
 cudaError_t q4k_gemv(const q4::GemvParams *params, int column_tiles, int aligned, cudaStream_t stream);  // one warp per block
 uint32_t q4k_gemv_occupancy(int column_tiles, int aligned);  // resident warps per SM, 0 on error
 
-uint32_t q4k_rows_plan(uint32_t m, uint32_t k, uint32_t tiles, uint32_t sm_count, uint32_t *part_chunks);  // parts, 0: unsupported
+uint32_t q4k_rows_plan(uint32_t m, uint32_t k, uint32_t tiles, uint32_t sm_count, uint32_t *part_chunks, uint32_t *tiles_per_warp);  // parts, 0: unsupported
 cudaError_t q4k_rows(const q4::RowsParams *params, uint32_t sm_count, cudaStream_t stream);
 
 cudaError_t q4k_swiglu(const float *gate, const float *up, uint64_t count, float *out_f32, uint16_t *out_bf16,

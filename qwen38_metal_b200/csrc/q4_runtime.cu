@@ -454,8 +454,8 @@ int launch_rows(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m, uin
         if ((((uintptr_t)jobs[i].w | (uintptr_t)jobs[i].s | (uintptr_t)jobs[i].b) & 15u) != 0 || jobs[i].n == 0) return -1;
         tiles += (jobs[i].n + 15u) / 16u;
     }
-    uint32_t part_chunks = 0;
-    const uint32_t parts = q4k_rows_plan(m, k, tiles, (uint32_t)rt->sm_count, &part_chunks);
+    uint32_t part_chunks = 0, tiles_per_warp = 1;
+    const uint32_t parts = q4k_rows_plan(m, k, tiles, (uint32_t)rt->sm_count, &part_chunks, &tiles_per_warp);
     if (parts == 0) return -1;
     q4::RowsParams p;
     memset(&p, 0, sizeof p);
@@ -483,6 +483,7 @@ int launch_rows(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m, uin
     p.cpt = k / 128u;
     p.parts = parts;
     p.part_chunks = part_chunks;
+    p.tiles_per_warp = tiles_per_warp;
     p.tiles = tiles;
     p.accumulate = (flags & Q4B_FLAG_ACCUMULATE) ? 1u : 0u;
     if (parts > 1) {
@@ -518,11 +519,11 @@ int enqueue_matmul(q4b_runtime *rt, const void *x_dev, int x_dtype, uint64_t m, 
     for (size_t j = 0; j < jobs.size() && rows; ++j)
         rows = (((uintptr_t)jobs[j].w | (uintptr_t)jobs[j].s | (uintptr_t)jobs[j].b) & 15u) == 0 && jobs[j].n != 0;
     for (size_t j0 = 0; j0 < jobs.size() && rows; j0 += q4::kMaxJobs) {
-        uint32_t tiles = 0, part_chunks = 0;
+        uint32_t tiles = 0, part_chunks = 0, tw = 1;
         for (size_t j = j0; j < jobs.size() && j < j0 + q4::kMaxJobs; ++j) tiles += (jobs[j].n + 15u) / 16u;
         const uint32_t full = (uint32_t)(m < rt->rows_max_m ? m : rt->rows_max_m), rest = (uint32_t)(m % rt->rows_max_m);
-        rows = q4k_rows_plan(full, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks) != 0 &&
-               (m <= rt->rows_max_m || rest == 0 || q4k_rows_plan(rest, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks) != 0);
+        rows = q4k_rows_plan(full, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks, &tw) != 0 &&
+               (m <= rt->rows_max_m || rest == 0 || q4k_rows_plan(rest, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks, &tw) != 0);
     }
     if (rows) {
         for (uint64_t m0 = 0; m0 < m; m0 += rt->rows_max_m) {
@@ -1874,13 +1875,13 @@ extern "C" int q4b_describe_dispatch(q4b_runtime *rt, int x_dtype, uint64_t m, u
         return Q4B_OK;
     }
     if (m >= 2 && m <= rt->rows_max_m && fast == n_jobs && k % 512 == 0) {
-        uint32_t tiles = 0, part_chunks = 0;
+        uint32_t tiles = 0, part_chunks = 0, tw = 1;
         for (const Resolved &r : resolved) tiles += (r.n + 15u) / 16u;
         const uint32_t mb = (uint32_t)(m < rt->rows_max_m ? m : rt->rows_max_m);
-        const uint32_t parts = q4k_rows_plan(mb, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks);
+        const uint32_t parts = q4k_rows_plan(mb, (uint32_t)k, tiles, (uint32_t)rt->sm_count, &part_chunks, &tw);
         if (parts) {
-            snprintf(text, text_len, "rows_i8 (short batch, integer tensor cores) rows_per_launch=%u k_parts=%u chunks_per_part=%u jobs=%u (a 16-byte aligned activation is assumed)",
-                     mb, parts, part_chunks, n_jobs);
+            snprintf(text, text_len, "rows_i8 (short batch, integer tensor cores) rows_per_launch=%u k_parts=%u chunks_per_part=%u tiles_per_warp=%u jobs=%u (a 16-byte aligned activation is assumed)",
+                     mb, parts, part_chunks, tw, n_jobs);
             return Q4B_OK;
         }
     }

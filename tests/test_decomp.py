@@ -27,7 +27,7 @@ def shim():
     lib.shim_rows_part_begin.restype = C.c_uint32
     lib.shim_rows_part_begin.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32]
     lib.shim_rows_plan.restype = C.c_uint32
-    lib.shim_rows_plan.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]
+    lib.shim_rows_plan.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]
     return lib
 
 
@@ -119,13 +119,14 @@ def test_byte_addressed_variant_never_reads_outside_the_tensors(shim, k, mis):
 @pytest.mark.parametrize("k", [512, 1024, 5120, 17408, 32768])
 @pytest.mark.parametrize("tiles", [1, 13, 320, 1088, 2176, 15520])
 @pytest.mark.parametrize("cap", [12, 24])
-def test_short_batch_k_split(shim, k, tiles, cap):
+@pytest.mark.parametrize("tw", [1, 2])
+def test_short_batch_k_split(shim, k, tiles, cap, tw):
     """The short-batch kernel's cut of the K range: parts begin at multiples of four chunks, are never empty, never
     longer than what a block can hold, and together cover every chunk exactly once; the chosen split keeps whole
     blocks per part on a 148-SM GPU."""
     cpt = k // 128
     longest = C.c_uint32(0)
-    parts = shim.shim_rows_plan(cpt, tiles, 148, cap, C.byref(longest))
+    parts = shim.shim_rows_plan(cpt, tiles, 148, cap, tw, C.byref(longest))
     if (cpt // 4 + 31) // 32 * 4 > cap and parts == 0:
         return  # even 32 parts are too long for the block: the caller falls back to the general kernel
     assert 1 <= parts <= 32 and parts <= cpt // 4
@@ -141,8 +142,10 @@ def test_short_batch_k_split_prefers_one_round(shim):
     """The benchmark's shapes: the down projection (320 tiles, K = 17408) is cut seven ways so that every warp of
     the grid has exactly one tile; gate and up together (2176 tiles, K = 5120) in two parts, two tiles per warp."""
     longest = C.c_uint32(0)
-    assert shim.shim_rows_plan(136, 320, 148, 24, C.byref(longest)) == 7 and longest.value == 20
-    assert shim.shim_rows_plan(40, 2176, 148, 24, C.byref(longest)) == 2 and longest.value == 20
+    assert shim.shim_rows_plan(136, 320, 148, 24, 1, C.byref(longest)) == 7 and longest.value == 20
+    assert shim.shim_rows_plan(40, 2176, 148, 24, 1, C.byref(longest)) == 2 and longest.value == 20
+    # two tiles per warp: gate and up together are one item per warp of a two-part grid
+    assert shim.shim_rows_plan(40, 2176, 148, 21, 2, C.byref(longest)) == 2 and longest.value == 20
 
 
 def test_signed_digits_from_one_addition():
