@@ -57,6 +57,9 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     constexpr uint32_t T = kRowsWarps * 32;
     constexpr uint32_t S = rows_stages(TW), PS = rows_param_stages(TW);
     constexpr uint32_t kStage = kRowsStageBytes * TW, kParamStage = 512u * TW;
+    // stages requested before the activation is converted, the rest right after (measured: one is best up to 8 rows,
+    // all of them for 16, whose conversion is twice as long)
+    constexpr uint32_t kEarly = NB == 1 ? 1u : S - 1u;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -127,8 +130,11 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
             const uint32_t rp = min(row0[w] + (lane & 15u), n - 1u);
             pw[w] = ((lane >> 4) ? job[w]->b : job[w]->s) + ((size_t)rp * p.groups) * 2u + (size_t)c_lo * 4u;
         }
+    };
+    auto prologue = [&](uint32_t first, uint32_t end) {  // the chunks [first, end) of the S - 1 a warp is ahead
 #pragma unroll
         for (uint32_t i = 0; i < S - 1; ++i) {
+            if (i < first || i >= end) continue;
             issue_chunk(c_lo + i);
             cp_async_commit();
         }
@@ -165,7 +171,10 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     // the first weights travel while the block converts the activation -- requested once every warp of the block has
     // its activation loads out: those would otherwise queue behind 7 KB of copies per warp
     __syncthreads();
-    if (item < items) open_item(item);
+    if (item < items) {
+        open_item(item);
+        prologue(0, kEarly);
+    }
     auto unpack8 = [&](const uint4 (&r)[2], float (&v)[8]) {
         if (p.x_is_f32) {
             v[0] = __uint_as_float(r[0].x); v[1] = __uint_as_float(r[0].y); v[2] = __uint_as_float(r[0].z); v[3] = __uint_as_float(r[0].w);
@@ -246,6 +255,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
     __syncthreads();
 
     if (tr) tr[1] = rows_ns();
+    if (item < items) prologue(kEarly, S - 1);
 
     // ---- tiles ----
     const uint32_t xdig_addr = (uint32_t)__cvta_generic_to_shared(xdig) + g * 64u + t * 16u;
@@ -333,7 +343,10 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 1) q4_rows_kernel(const __gri
             done_live[w] = tile_live[w];
         }
         const uint32_t done_item = item;
-        if (item + blocks_per_part * kRowsWarps < items) open_item(item + blocks_per_part * kRowsWarps);
+        if (item + blocks_per_part * kRowsWarps < items) {
+            open_item(item + blocks_per_part * kRowsWarps);
+            prologue(0, S - 1);
+        }
 
         // ---- the part's scaling undone; then the tile's parts ----
         const uint32_t rows_total = p.tiles * 16u;
