@@ -317,8 +317,10 @@ __device__ __forceinline__ void rebuild_general(const StackParams &sp, const Sta
     // arrival at the rebuild, which a direct read does not.)
     const uint32_t n_parts = P.src_parts;
     const uint8_t *src_base = reinterpret_cast<const uint8_t *>(P.src0);
-    // the hidden vector is read slice by slice (statistics of the slice); everything else needs the whole vector
-    const uint32_t base = P.x_kind == kRebuildH ? b_lo : 0u, limit = P.x_kind == kRebuildH ? b_hi : blocks_p;
+    // a block reads the slice it holds (all of the vector unless the phase is K-major) and scales it by the slice's own
+    // maximum; only the RMS-norm needs the whole vector (its sum of squares)
+    const bool whole = P.x_kind == kRebuildRms;
+    const uint32_t base = whole ? 0u : b_lo, limit = whole ? blocks_p : b_hi;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it)
 #pragma unroll
@@ -639,7 +641,10 @@ __device__ __forceinline__ void chunk_mma_i8(const uint4 &cwa, const uint4 &cwb,
     mma_u8s8_16832(d, ha[2], hb[2], ha[3], hb[3], xr[1].z, xr[1].w);
 }
 
-template <int WARPS>
+// LONG: the instance that can rebuild vectors of more than two blocks of 8 per thread (an unsliced hidden vector,
+// K > 8192). Its 40 value registers push the streaming loop into spills (128 registers, 90 bytes of spill stores);
+// chains that never need it (params.long_rebuild == 0) run the other instance: 122 registers, no spills.
+template <int WARPS, bool LONG>
 __device__ __forceinline__ void stack_body(const StackParams &sp) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -748,11 +753,15 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             const uint32_t o_lo = writes ? c_lo * 16u : 0u, o_hi = writes ? c_hi * 16u : 0u;
             if (P.x_kind != kRebuildNone) {
                 unsigned long long *tr = (sp.trace && threadIdx.x == 0) ? trace_slot() : nullptr;
-                const uint32_t held = P.x_kind == kRebuildH ? c_hi * 16u - cs4 * 16u : P.kp / 8u;
-                if (held <= 2u * WARPS * 32u)
+                const uint32_t held = P.x_kind == kRebuildRms ? P.kp / 8u : c_hi * 16u - cs4 * 16u;
+                if (held <= 2u * WARPS * 32u) {
                     rebuild_general<WARPS, 2>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase, tr);
-                else
+                } else if constexpr (LONG) {
                     rebuild_general<WARPS, kStackMaxIters>(sp, P, X, red, cs4 * 16u, c_hi * 16u, o_lo, o_hi, tag_base + P.src_tag_phase, tr);
+                } else {
+                    if (threadIdx.x == 0) *sp.error_flag = 1;  // the host picked the wrong instance: report, compute nothing
+                    __syncthreads();
+                }
             }
             if (sp.trace && threadIdx.x == 0) trace_slot()[2] = stack_ns();
         }
@@ -1015,21 +1024,21 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     }
 }
 
-template <int WARPS>
+template <int WARPS, bool LONG>
 __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_kernel(const __grid_constant__ StackParams sp) {
-    stack_body<WARPS>(sp);
+    stack_body<WARPS, LONG>(sp);
 }
 
 // The same kernel for a program of ONE phase that travels in the kernel parameters: a single grouped decode launch
 // (q4b_matvec_batch and friends) builds its activation, streams its projections and stores its results in one launch,
 // without a device-side program or a host-to-device copy in front of it.
-template <int WARPS>
+template <int WARPS, bool LONG>
 __global__ void __launch_bounds__(WARPS * 32, 1) q4_stack_inline_kernel(const __grid_constant__ InlineProgram prog) {
     StackParams sp = prog.params;
     sp.phases = &prog.phase;
     sp.jobs = prog.jobs;
     sp.n_phases = 1;
-    stack_body<WARPS>(sp);
+    stack_body<WARPS, LONG>(sp);
 }
 
 }  // namespace q4
@@ -1043,6 +1052,27 @@ constexpr int kStackWarps = 16;
 }  // namespace
 
 extern "C" uint32_t q4k_stack_warps(void) { return kStackWarps; }
+
+// 1 when a phase's rebuild holds more than two blocks of 8 inputs per thread, i.e. needs the kernel instance with the
+// long rebuild (the device applies the same rule to pick the rebuild)
+extern "C" int q4k_stack_phase_is_long(const q4::StackPhase *P) {
+    if (P->x_kind == q4::kRebuildNone) return 0;
+    uint32_t held = P->kp / 8u;
+    if (P->x_kind != q4::kRebuildRms) {
+        held = 0;
+        const uint32_t parts = (P->kparts > 1u && P->sliced) ? P->kparts : 1u;
+        for (uint32_t part = 0; part < parts; ++part) {
+            uint32_t c_lo = 0, c_hi = P->kp / 128u;
+            if (parts > 1u) {
+                c_lo = P->cpt * part / parts;
+                c_hi = P->cpt * (part + 1u) / parts;
+            }
+            const uint32_t blocks = (c_hi - (c_lo & ~3u)) * 16u;
+            held = blocks > held ? blocks : held;
+        }
+    }
+    return held > 2u * kStackWarps * 32u ? 1 : 0;
+}
 extern "C" uint32_t q4k_stack_max_k(void) { return q4::kStackMaxIters * kStackWarps * 32 * 8; }
 
 extern "C" size_t q4k_stack_smem_bytes(uint32_t halfs0, uint32_t halfs1) {
@@ -1051,44 +1081,42 @@ extern "C" size_t q4k_stack_smem_bytes(uint32_t halfs0, uint32_t halfs1) {
 }
 
 // 0 when the kernel cannot be made resident with one block per SM for these activation sizes
-extern "C" int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1) {
-    const size_t smem = q4k_stack_smem_bytes(halfs0, halfs1);
-    if (cudaFuncSetAttribute(q4::q4_stack_kernel<kStackWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+template <typename Kernel>
+static int stack_resident(Kernel kernel, size_t smem) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4::q4_stack_kernel<kStackWarps>, kStackWarps * 32, smem) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kStackWarps * 32, smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return blocks >= 1 ? 1 : 0;
+}
+
+extern "C" int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1) {
+    const size_t smem = q4k_stack_smem_bytes(halfs0, halfs1);
+    return stack_resident(q4::q4_stack_kernel<kStackWarps, false>, smem) && stack_resident(q4::q4_stack_kernel<kStackWarps, true>, smem);
 }
 
 extern "C" cudaError_t q4k_stack_launch(const q4::StackParams *params, int sm_count, cudaStream_t stream) {
     q4::StackParams sp = *params;
     void *args[] = {&sp};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(q4::q4_stack_kernel<kStackWarps>), dim3(sm_count), dim3(kStackWarps * 32),
-                                       args, q4k_stack_smem_bytes(sp.halfs[0], sp.halfs[1]), stream);
+    void *kernel = sp.long_rebuild ? reinterpret_cast<void *>(q4::q4_stack_kernel<kStackWarps, true>)
+                                   : reinterpret_cast<void *>(q4::q4_stack_kernel<kStackWarps, false>);
+    return cudaLaunchCooperativeKernel(kernel, dim3(sm_count), dim3(kStackWarps * 32), args, q4k_stack_smem_bytes(sp.halfs[0], sp.halfs[1]), stream);
 }
 
 extern "C" int q4k_stack_inline_supported(uint32_t halfs) {
     const size_t smem = q4k_stack_smem_bytes(halfs, 0);
-    if (cudaFuncSetAttribute(q4::q4_stack_inline_kernel<kStackWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, q4::q4_stack_inline_kernel<kStackWarps>, kStackWarps * 32, smem) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    return blocks >= 1 ? 1 : 0;
+    return stack_resident(q4::q4_stack_inline_kernel<kStackWarps, false>, smem) && stack_resident(q4::q4_stack_inline_kernel<kStackWarps, true>, smem);
 }
 
 extern "C" cudaError_t q4k_stack_launch_inline(const q4::InlineProgram *program, int sm_count, cudaStream_t stream) {
     q4::InlineProgram prog = *program;
     void *args[] = {&prog};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void *>(q4::q4_stack_inline_kernel<kStackWarps>), dim3(sm_count),
-                                       dim3(kStackWarps * 32), args, q4k_stack_smem_bytes(prog.params.halfs[0], 0), stream);
+    void *kernel = prog.params.long_rebuild ? reinterpret_cast<void *>(q4::q4_stack_inline_kernel<kStackWarps, true>)
+                                            : reinterpret_cast<void *>(q4::q4_stack_inline_kernel<kStackWarps, false>);
+    return cudaLaunchCooperativeKernel(kernel, dim3(sm_count), dim3(kStackWarps * 32), args, q4k_stack_smem_bytes(prog.params.halfs[0], 0), stream);
 }

@@ -340,6 +340,7 @@ int launch_single_row(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t 
     sp.max_workers = grid_warps;
     sp.spin_limit = rt->chain_spin_limit;
     sp.flags = rt->chain_flags;
+    sp.long_rebuild = (uint32_t)q4k_stack_phase_is_long(&prog.phase);
     if (int st = profile_open(rt, stream)) return st;
     Q4B_CUDA(q4k_stack_launch_inline(&prog, rt->sm_count, stream), "decode launch");
     rt->launches++;
@@ -1710,6 +1711,7 @@ extern "C" int q4b_chain_create(q4b_runtime *rt, const q4b_stage *stages, uint32
     sp.n_phases = (uint32_t)phases.size();
     sp.halfs[0] = halfs[0];
     sp.halfs[1] = halfs[1];
+    for (const q4::StackPhase &P : phases) sp.long_rebuild |= (uint32_t)q4k_stack_phase_is_long(&P);
     sp.local_bar = (unsigned int *)reset;
     sp.error_flag = (int *)rt->error_flag.ptr;
     sp.partials = (uint4 *)partials;

@@ -107,6 +107,7 @@ struct StackParams {
     uint32_t *token;
     float *best;
     const StackPeers *peers;  // null on one GPU
+    uint32_t long_rebuild;    // some phase rebuilds a vector of more than two blocks of 8 per thread (picks the kernel instance)
     unsigned long long *trace;  // optional [blocks][n_phases][8] device-clock stamps
 };
 
@@ -132,6 +133,7 @@ uint32_t q4k_stack_warps(void);
 uint32_t q4k_stack_max_k(void);       // longest activation the Bf16/Swiglu/Rms rebuilds handle
 size_t q4k_stack_smem_bytes(uint32_t halfs0, uint32_t halfs1);
 int q4k_stack_supported(uint32_t halfs0, uint32_t halfs1);
+int q4k_stack_phase_is_long(const q4::StackPhase *phase);
 cudaError_t q4k_stack_launch(const q4::StackParams *params, int sm_count, cudaStream_t stream);
 int q4k_stack_inline_supported(uint32_t halfs);
 cudaError_t q4k_stack_launch_inline(const q4::InlineProgram *program, int sm_count, cudaStream_t stream);
