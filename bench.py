@@ -540,8 +540,8 @@ def run_ours(args) -> int:
                                 "frac_of_8TBs": value / world / NOMINAL_HBM_GBS, "launches": args.steps,
                                 "avg_launch_us": ms * 1e3 / args.steps, "bytes_per_launch": total_bytes // world,
                                 # dram__bytes_read+write of one launch: captured with ncu on the 4-layer stack
-                                # (1.5855 + 0.0286 GB for 1.5297 GB algorithmic) and scaled by the bytes of this launch
-                                "traffic": int(total_bytes // world * 1.0552),
+                                # (1.5806 + 0.0165 GB for 1.5297 GB algorithmic) and scaled by the bytes of this launch
+                                "traffic": int(total_bytes // world * 1.0441),
                                 "traffic_source": "ncu capture of a 4-layer launch, scaled by algorithmic bytes (profiles/)"}
             line["launch_per_stage_graph"] = {"value": total_bytes * args.steps / (ms_graph * 1e-3) / 1e9, "unit": UNIT,
                                               "ms_per_step": ms_graph / args.steps, "gpu_launches": launches_per_token}
