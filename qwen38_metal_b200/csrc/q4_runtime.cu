@@ -142,7 +142,7 @@ struct q4b_runtime {
     bool chain_no_fusion = false, chain_no_deferral = true;
     bool chain_no_handoff = false;     // keep a barrier between a projection and the RMS-norm that consumes it
     bool chain_split_tiles = true;     // a phase with fewer tiles than warps gives every tile the same number of warps
-    uint32_t chain_flags = 4u | (16u << 8);  // kFlagLateSkipsRequest, margin 16 blocks
+    uint32_t chain_flags = 0;
     uint64_t failures = 0;             // bounded waits that ran out (finish() saw the error flag)
     uint64_t prof_flops = 0;
     bool tracing = false;
