@@ -148,6 +148,7 @@ struct q4b_runtime {
     bool tracing = false;
     uint32_t trace_workers = 0;
     Pool rows_partials, rows_counters;
+    uint64_t rows_failures_seen = 0;  // rt->failures when the short-batch tile counters were last known to be zero
     Pool x_in, xp, xsum, row_inv, partials, counters, logits, amax_v, amax_i, tokens, gate, up, hidden;
     Pool outs[q4::kMaxJobs];
     HostPool results;  // staging for downloads (host-buffer entry points)
@@ -492,7 +493,12 @@ int launch_rows(q4b_runtime *rt, const void *x_dev, int x_dtype, uint32_t m, uin
         Q4B_CUDA(rt->rows_partials.ensure((size_t)parts * mp * tiles * 16 * 4), "partial sum scratch");
         const size_t had = rt->rows_counters.capacity;
         Q4B_CUDA(rt->rows_counters.ensure((size_t)tiles * 4), "tile counter scratch");
-        if (rt->rows_counters.capacity != had) Q4B_CUDA(cudaMemsetAsync(rt->rows_counters.ptr, 0, rt->rows_counters.capacity, stream), "tile counter reset");
+        // the counters are put back to zero by the kernel itself; after a failed command on this runtime (a launch may
+        // have been cut short) and for a fresh buffer they are cleared here
+        if (rt->rows_counters.capacity != had || rt->rows_failures_seen != rt->failures) {
+            Q4B_CUDA(cudaMemsetAsync(rt->rows_counters.ptr, 0, rt->rows_counters.capacity, stream), "tile counter reset");
+            rt->rows_failures_seen = rt->failures;
+        }
         p.partials = (float *)rt->rows_partials.ptr;
         p.counters = (unsigned int *)rt->rows_counters.ptr;
     }
