@@ -656,6 +656,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     float *xsum1 = xsum0 + sp.halfs[0] / 64 + 4;
     float *misc = xsum1 + sp.halfs[1] / 64 + 4;
     uint32_t *arrive_smem = reinterpret_cast<uint32_t *>(misc + 2);
+    uint32_t *units_done_smem = reinterpret_cast<uint32_t *>(misc + 70);  // warps of this block through with a phase, running count
     float *red = misc + 4;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + warp * kStackRingBytes;
     const uint32_t pring = ring + kStages * kStageBytesAligned;
@@ -697,6 +698,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
     request_phase(0);
     if (threadIdx.x == 0) {
         *arrive_smem = 0;
+        *units_done_smem = 0;
         *gbase_smem = sp.peers ? *reinterpret_cast<volatile unsigned long long *>(sp.peers->consumed) : 0ull;
         reinterpret_cast<uint32_t *>(misc)[3] = *reinterpret_cast<volatile unsigned int *>(sp.launch_seq);
     }
@@ -765,6 +767,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
         }
 
         bool stored_to_peers = false;
+        uint32_t blocks_done = 0;
         uint32_t u = 0, u1 = 0;  // this warp's units of the phase (a phase has fewer than 2^32)
         if (worker < P.workers) {
             const Q4Split split{P.units, P.cpt, P.workers};
@@ -880,6 +883,8 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
                 const TileEnd te{sg.job, sg.tile_local, sg.tile_row, sg.c0v, sg.c1v};
                 u += sg.c1v - sg.c0v;
                 more = u < u1;
+                // (a hint, read while the last tile is being finished: how many blocks are through with this phase)
+                if (!more && (sp.flags & kFlagLateSkipsRequest)) blocks_done = *reinterpret_cast<volatile unsigned int *>(sp.local_bar + kProgressWord);
                 if (more) {
                     segment_setup(P, sp.jobs, u, u1, job_rel, lane, sg);
                     segment_prologue(sg, ring, pring, lane);
@@ -908,10 +913,23 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             ++sync.local_gen;
             if (P.arrive_kind == kSyncGlobal) ++sync.global_gen;
         }
-        // The next phase's first weights are requested now, so that the rings fill while the block waits for the
-        // slowest block. (kFlagRequestAfterRebuild moves the request behind the next phase's rebuild, whose polls and
-        // shared-memory stores otherwise queue behind these copies: measured slower, the rings then start empty.)
-        const bool request_later = (sp.flags & kFlagRequestAfterRebuild) != 0;
+        // The next phase's first weights: requested now when nothing stands between this phase and the next one's
+        // units; after the rebuild when there is one (kFlagRequestAfterRebuild) -- the polls and shared-memory stores
+        // of a rebuild queue behind the copies a warp has in flight, which costs the last block to finish (the one
+        // all others are waiting for) several microseconds per phase.
+        //
+        // kFlagLateSkipsRequest does that only for the warps that finish when nearly every block is through with the
+        // phase: the blocks that are waiting anyway keep filling their rings during the wait. Blocks count themselves
+        // in one word (the last warp of a block adds one per phase); the count is a hint and orders nothing.
+        bool request_later = (sp.flags & kFlagRequestAfterRebuild) != 0;
+        if (sp.flags & kFlagLateSkipsRequest) {
+            if (lane == 0) {
+                const uint32_t through = atomicAdd(units_done_smem, 1u) + 1u;
+                if (through % WARPS == 0) atomicAdd(sp.local_bar + kProgressWord, 1u);
+            }
+            const uint32_t margin = (sp.flags >> 8) & 0xffu;
+            request_later = blocks_done >= ph * gridDim.x + gridDim.x - margin && blocks_done < (ph + 1u) * gridDim.x + gridDim.x;
+        }
         if (request_later && ph + 1u < sp.n_phases && sp.phases[ph + 1u].x_kind != kRebuildNone)
             prefetched = false;  // (the phase's own start requests them)
         else
@@ -999,6 +1017,7 @@ __device__ __forceinline__ void stack_body(const StackParams &sp) {
             __threadfence();
             sp.local_bar[0] = 0;
             sp.local_bar[1] = 0;
+            sp.local_bar[kProgressWord] = 0;
             if (sp.peers) *sp.peers->consumed = *gbase_smem + (unsigned long long)sync.global_gen * sp.peers->world;
             *sp.launch_seq = reinterpret_cast<uint32_t *>(misc)[3] + 1u;
         }

@@ -119,6 +119,8 @@ struct InlineProgram {
 };
 
 constexpr uint32_t kFlagRequestAfterRebuild = 2u;  // a phase that rebuilds its activation requests its first weights after the rebuild
+constexpr uint32_t kFlagLateSkipsRequest = 4u;     // ... only for warps that finish a phase when all but (flags >> 8 & 255) blocks are through
+constexpr uint32_t kProgressWord = 32;             // local_bar[kProgressWord]: blocks through with a phase, summed over the launch
 constexpr uint32_t kFlagWarpFenceGpu = 1u;  // every warp fences at device scope before it arrives (default: block scope)
 
 constexpr uint32_t kTraceStamps = 16;  // wait begin, wait end, rebuild end, warp 0 units end, block's arrival, SM id, last warp's units end,
