@@ -348,3 +348,25 @@ def test_fused_mlp_full_width_sampled(runtime, oracle, off):
         for r0 in (0, (n // 2) & ~15, n - 16):
             wd = oracle.synth_q4(SEED, 813, 16, inter, row0=r0)
             assert oracle.rel_l2(y[rows][:, r0:r0 + 16], mm(h, wd, 16)) <= bar, (form, r0)
+
+
+@pytest.mark.parametrize("n,k", [(40000, 9216), (1024, 20480)])
+def test_single_row_long_activation(runtime, oracle, n, k):
+    """One activation row longer than 8192 inputs: with many rows the launch is not K-major and every block rebuilds
+    the whole activation (the kernel instance with the long rebuild); with few rows it is K-major and a block builds
+    only its slice. Weights generated in HBM, sampled rows regenerated on the CPU."""
+    from qwen38_metal_b200.runtime import MappedQ4AffineJob
+
+    wb = runtime.alloc_shard(n * k // 2)
+    sb = runtime.alloc_shard(n * (k // 64) * 2)
+    bb = runtime.alloc_shard(n * (k // 64) * 2)
+    job = MappedQ4AffineJob(wb, 0, sb, 0, bb, 0, n, True)
+    runtime.synth_q4(SEED, 900 + k % 89, 0.02, 0, n, k, job)
+    bits, xf = x_bf16(oracle, 90, 1, k)
+    out = runtime.q4_affine_matvec_mapped_batch(bits, [job])[0]
+    again = runtime.q4_affine_matvec_mapped_batch(bits, [job])[0]
+    assert out.shape == (n,) and np.array_equal(out, again)
+    for r0 in (0, (n // 2) & ~15, n - 16):
+        w, s, b = oracle.synth_q4(SEED, 900 + k % 89, 16, k, row0=r0)
+        ref = oracle.matmul_factored_f32(xf, w, s, b, 16)[0]
+        assert oracle.rel_l2(out[r0:r0 + 16], ref) <= 1e-5
