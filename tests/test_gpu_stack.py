@@ -218,3 +218,41 @@ def test_mid_width_chain_with_and_without_deferred_projections(oracle, defer, mo
         chain.close()
     finally:
         rt.close()
+
+
+def test_chain_with_a_hidden_width_above_8192(runtime, oracle):
+    """A hidden width of 9216: the RMS-norm rebuild holds more than two blocks of 8 inputs per thread, so the chain runs
+    on the kernel instance with the long rebuild. One layer, compared stage by stage with the per-stage path."""
+    import torch
+
+    from qwen38_metal_b200.stack import SyntheticStack
+
+    layers, hidden, inter, vocab = 1, 9216, 1024, 1000
+    rows = (96, 32, 16, 48, 1024, 1024)
+    stack = SyntheticStack(runtime, layers=layers, hidden=hidden, inter=inter, vocab=vocab, layer_rows=rows,
+                           seed=81, misalign=2)
+    stream = torch.cuda.current_stream().cuda_stream
+    stack.reset_input(stream)
+    torch.cuda.synchronize()
+    x0 = stack.x.clone()
+    stack.decode_token(stream)
+    runtime.device_status()
+    ref_d, ref_outs, ref_x = stack.d.clone(), [o.clone() for o in stack.outs], stack.x.clone()
+    ref_token = int(stack.token.item())
+    chain = stack.build_chain()
+    for _ in range(2):
+        stack.x.copy_(x0)
+        stack.d.zero_()
+        torch.cuda.synchronize()
+        chain.run(stream)
+        runtime.device_status()
+        assert oracle.rel_l2(stack.d.cpu().numpy(), ref_d.cpu().numpy()) <= 1e-5
+        for got, ref in zip(stack.outs, ref_outs):
+            assert oracle.rel_l2(got.cpu().numpy(), ref.cpu().numpy()) <= 1e-5
+        assert oracle.rel_l2(stack.x.float().cpu().numpy(), ref_x.float().cpu().numpy()) <= 1e-2
+        logits = stack.logits.cpu().numpy()
+        assert int(stack.token.item()) == int(np.argmax(logits))
+        order = np.sort(logits)
+        if order[-1] - order[-2] > 1e-2 * abs(order[-1]):
+            assert int(stack.token.item()) == ref_token
+    chain.close()
