@@ -1803,13 +1803,24 @@ extern "C" int q4b_chain_run(q4b_chain *chain, const void *x_host, uint32_t *tok
         cudaStreamSynchronize(s);
         return st;
     }
-    uint32_t token = 0;
-    float best = 0.f;
-    Q4B_CUDA(cudaMemcpyAsync(&token, chain->token, 4, cudaMemcpyDeviceToHost, s), "token download");
-    if (best_host && chain->best) Q4B_CUDA(cudaMemcpyAsync(&best, chain->best, 4, cudaMemcpyDeviceToHost, s), "logit download");
-    if (int st = finish(rt, s)) return st;
-    *token_host = token;
-    if (best_host && chain->best) *best_host = best;
+    // token, logit and the error flag come back through one pinned staging block and ONE synchronisation (three
+    // downloads into pageable memory would each wait for the stream)
+    Q4B_CUDA(rt->results.ensure(64), "result staging");
+    uint8_t *h = (uint8_t *)rt->results.ptr;
+    Q4B_CUDA(cudaMemcpyAsync(h, chain->token, 4, cudaMemcpyDeviceToHost, s), "token download");
+    if (best_host && chain->best) Q4B_CUDA(cudaMemcpyAsync(h + 4, chain->best, 4, cudaMemcpyDeviceToHost, s), "logit download");
+    Q4B_CUDA(cudaMemcpyAsync(h + 8, rt->error_flag.ptr, 4, cudaMemcpyDeviceToHost, s), "status download");
+    const cudaError_t e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(Q4B_COMMAND_FAILED, "CUDA command failed: %s", cudaGetErrorString(e));
+    int flag = 0;
+    memcpy(&flag, h + 8, 4);
+    if (flag) {
+        cudaMemset(rt->error_flag.ptr, 0, sizeof flag);
+        rt->failures++;
+        return fail(Q4B_COMMAND_FAILED, "a kernel gave up on a bounded wait (pipeline stalled); results are invalid");
+    }
+    memcpy(token_host, h, 4);
+    if (best_host && chain->best) memcpy(best_host, h + 4, 4);
     return Q4B_OK;
 }
 
